@@ -1,0 +1,237 @@
+"""ctypes binding of libgpt2_linear.so — the B200 (sm_100a) linear-layer GEMM path of gpt2.cu.
+
+The library itself (C ABI: include/gpt2_linear.h) is the product; this module only loads it and
+gives the tests and the benchmark a thin, typed way to call it with raw device pointers (for
+example torch tensors' ``data_ptr()``). There is no fallback of any kind: if the shared library
+is missing, import fails; if there is no sm_100 GPU, every compute call returns
+``ERR_NO_DEVICE`` / ``ERR_NOT_INIT`` and the helpers here raise.
+
+The directory name contains a dot, so import it through ``__graft_entry__.load_package()``
+(which registers it as module ``gpt2cu_b200``).
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libgpt2_linear.so")
+
+OK = 0
+ERR_NO_DEVICE = -1
+ERR_BAD_ARG = -2
+ERR_CUDA = -3
+ERR_NOT_INIT = -4
+ERR_TOO_LARGE = -5
+ERR_SCHEDULE = -6
+DEV_TIMEOUT = 1
+
+MODE_TF32 = 0
+MODE_TF32X3 = 1
+EPI_GELU_DUAL = 1
+
+OP_FORWARD = 0
+OP_BACKWARD_INPUT = 1
+OP_BACKWARD_WEIGHT = 2
+
+DEP_NONE = 0
+DEP_ROWBLOCK = 1
+DEP_WHOLE_OP = 2
+MAX_DEPS = 2
+
+# every symbol include/gpt2_linear.h declares
+EXPORTS = [
+    "gpt2_linear_init", "gpt2_linear_shutdown", "gpt2_linear_version", "gpt2_linear_launch_count",
+    "gpt2_linear_last_status",
+    "gpt2_linear_forward", "gpt2_linear_backward_input", "gpt2_linear_backward_weight",
+    "gpt2_linear_forward_host", "gpt2_linear_backward_input_host", "gpt2_linear_backward_weight_host",
+    "gpt2_schedule_create", "gpt2_schedule_destroy", "gpt2_schedule_validate", "gpt2_schedule_describe",
+    "gpt2_megakernel_run", "gpt2_megakernel_status", "gpt2_schedule_debug_set_expected",
+]
+
+
+class Opts(ctypes.Structure):
+    """struct gpt2_linear_opts"""
+    _fields_ = [
+        ("mode", ctypes.c_int),
+        ("flags", ctypes.c_uint),
+        ("split_k", ctypes.c_int),
+        ("deterministic", ctypes.c_int),
+        ("out2", ctypes.c_void_p),
+        ("force_simt", ctypes.c_int),
+    ]
+
+
+class Dep(ctypes.Structure):
+    """struct gpt2l_dep"""
+    _fields_ = [("producer", ctypes.c_int), ("kind", ctypes.c_int)]
+
+
+class Op(ctypes.Structure):
+    """struct gpt2l_op"""
+    _fields_ = [
+        ("kind", ctypes.c_int),
+        ("layer", ctypes.c_int),
+        ("B", ctypes.c_int), ("S", ctypes.c_int), ("K", ctypes.c_int), ("N", ctypes.c_int),
+        ("out", ctypes.c_void_p),
+        ("out_bias", ctypes.c_void_p),
+        ("a", ctypes.c_void_p),
+        ("b", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p),
+        ("opts", Opts),
+        ("deps", Dep * MAX_DEPS),
+    ]
+
+
+class LinearError(RuntimeError):
+    def __init__(self, fn, code):
+        super().__init__(f"{fn} returned {code}")
+        self.code = code
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python gpt2.cu_b200/build.py` "
+            "(there is no fallback implementation)")
+    lib = ctypes.CDLL(LIB_PATH)
+    P, I, V = ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p
+    OP = ctypes.POINTER(Opts)
+    lib.gpt2_linear_init.argtypes = [I]
+    lib.gpt2_linear_init.restype = I
+    lib.gpt2_linear_shutdown.argtypes = []
+    lib.gpt2_linear_shutdown.restype = None
+    lib.gpt2_linear_version.restype = I
+    lib.gpt2_linear_launch_count.restype = ctypes.c_longlong
+    lib.gpt2_linear_last_status.argtypes = [ctypes.POINTER(I * 6)]
+    lib.gpt2_linear_last_status.restype = I
+    for name in ("gpt2_linear_forward", "gpt2_linear_forward_host"):
+        f = getattr(lib, name)
+        f.argtypes = [P, P, P, P, I, I, I, I, OP, V]
+        f.restype = I
+    for name in ("gpt2_linear_backward_input", "gpt2_linear_backward_input_host"):
+        f = getattr(lib, name)
+        f.argtypes = [P, P, P, I, I, I, I, OP, V]
+        f.restype = I
+    for name in ("gpt2_linear_backward_weight", "gpt2_linear_backward_weight_host"):
+        f = getattr(lib, name)
+        f.argtypes = [P, P, P, P, I, I, I, I, OP, V]
+        f.restype = I
+    lib.gpt2_schedule_create.argtypes = [ctypes.POINTER(Op), I, ctypes.POINTER(I)]
+    lib.gpt2_schedule_create.restype = V
+    lib.gpt2_schedule_destroy.argtypes = [V]
+    lib.gpt2_schedule_destroy.restype = None
+    lib.gpt2_schedule_validate.argtypes = [ctypes.POINTER(Op), I, I]
+    lib.gpt2_schedule_validate.restype = I
+    lib.gpt2_schedule_describe.argtypes = [ctypes.POINTER(Op), I, I, ctypes.POINTER(I * 3)]
+    lib.gpt2_schedule_describe.restype = I
+    lib.gpt2_megakernel_run.argtypes = [V, V]
+    lib.gpt2_megakernel_run.restype = I
+    lib.gpt2_megakernel_status.argtypes = [V]
+    lib.gpt2_megakernel_status.restype = I
+    lib.gpt2_schedule_debug_set_expected.argtypes = [V, I, I, I, I]
+    lib.gpt2_schedule_debug_set_expected.restype = I
+    return lib
+
+
+lib = _load()
+
+
+def check(fn, code):
+    if code != 0:
+        raise LinearError(fn, code)
+
+
+def init(device=0):
+    """gpt2_linear_init; raises when there is no sm_100 device (no fallback exists)."""
+    check("gpt2_linear_init", lib.gpt2_linear_init(device))
+
+
+def make_opts(mode=MODE_TF32, flags=0, split_k=0, deterministic=0, out2=None, force_simt=0):
+    return Opts(mode, flags, split_k, deterministic, out2, force_simt)
+
+
+def _p(t):
+    """device (or host) pointer of a torch tensor / numpy array / int / None"""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    return t.ctypes.data
+
+
+def forward(out, x, w, b, B, S, K, N, opts=None, stream=None, host=False):
+    fn = lib.gpt2_linear_forward_host if host else lib.gpt2_linear_forward
+    return fn(_p(out), _p(x), _p(w), _p(b), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def backward_input(g_in, g_out, w, B, S, K, N, opts=None, stream=None, host=False):
+    fn = lib.gpt2_linear_backward_input_host if host else lib.gpt2_linear_backward_input
+    return fn(_p(g_in), _p(g_out), _p(w), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def backward_weight(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=None, host=False):
+    fn = lib.gpt2_linear_backward_weight_host if host else lib.gpt2_linear_backward_weight
+    return fn(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def last_status():
+    rec = (ctypes.c_int * 6)()
+    st = lib.gpt2_linear_last_status(ctypes.byref(rec))
+    return st, list(rec)
+
+
+def make_op(kind, B, S, K, N, out, a, b, bias=None, out_bias=None, opts=None, deps=(), layer=0):
+    """One entry of a megakernel schedule. deps = [(producer_index, DEP_*), ...]"""
+    op = Op()
+    op.kind, op.layer, op.B, op.S, op.K, op.N = kind, layer, B, S, K, N
+    op.out, op.out_bias, op.a, op.b, op.bias = _p(out), _p(out_bias), _p(a), _p(b), _p(bias)
+    op.opts = opts if opts is not None else make_opts()
+    for i, (prod, kind_) in enumerate(deps):
+        op.deps[i].producer = prod
+        op.deps[i].kind = kind_
+    return op
+
+
+class Schedule:
+    """Owns a gpt2l_schedule (device op array, counters) built from a list of Op."""
+
+    def __init__(self, ops):
+        self.n = len(ops)
+        self.arr = (Op * self.n)(*ops)
+        err = ctypes.c_int(0)
+        self.handle = lib.gpt2_schedule_create(self.arr, self.n, ctypes.byref(err))
+        if not self.handle:
+            raise LinearError("gpt2_schedule_create", err.value)
+
+    def run(self, stream=None):
+        return lib.gpt2_megakernel_run(self.handle, stream)
+
+    def status(self):
+        return lib.gpt2_megakernel_status(self.handle)
+
+    def debug_set_expected(self, op, dep, expected, wait_limit_ms=0):
+        return lib.gpt2_schedule_debug_set_expected(self.handle, op, dep, expected, wait_limit_ms)
+
+    def close(self):
+        if self.handle:
+            lib.gpt2_schedule_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def validate_schedule(ops, grid):
+    arr = (Op * len(ops))(*ops)
+    return lib.gpt2_schedule_validate(arr, len(ops), grid)
+
+
+def describe_schedule(ops, num_sms):
+    arr = (Op * len(ops))(*ops)
+    counts = (ctypes.c_int * 3)()
+    code = lib.gpt2_schedule_describe(arr, len(ops), num_sms, ctypes.byref(counts))
+    return code, list(counts)

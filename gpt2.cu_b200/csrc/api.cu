@@ -1,0 +1,304 @@
+// C ABI of libgpt2_linear.so: device context, the three linear-layer calls (device and
+// host-buffer flavours). Declarations and the reference interfaces they replace are in
+// include/gpt2_linear.h.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "linear_internal.h"
+
+namespace g2l {
+
+constexpr int MAX_DEVICES = 16;
+static DeviceCtx g_ctx[MAX_DEVICES];
+static std::mutex g_mu;        // context table and the shared split-K workspace
+static std::mutex g_stage_mu;  // host-call staging buffers (held for a whole *_host call)
+constexpr size_t SEM_COUNT = 1u << 20;  // split-K arrival counters (one per output tile and lane quarter)
+
+DeviceCtx *ctx_current(int *err) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    (void)cudaGetLastError();
+    *err = GPT2L_ERR_NO_DEVICE;
+    return nullptr;
+  }
+  if (!g_ctx[dev].ready) {
+    *err = GPT2L_ERR_NOT_INIT;
+    return nullptr;
+  }
+  *err = GPT2L_OK;
+  return &g_ctx[dev];
+}
+
+static int ensure_bytes(float **buf, size_t *have, size_t need) {
+  if (need <= *have) return GPT2L_OK;
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr;
+  *have = 0;
+  // grow in 64 MiB steps so that repeated slightly larger requests do not reallocate
+  size_t want = (need + (64u << 20) - 1) / (64u << 20) * (64u << 20);
+  if (cudaMalloc(reinterpret_cast<void **>(buf), want) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return GPT2L_ERR_CUDA;
+  }
+  *have = want;
+  return GPT2L_OK;
+}
+
+static int run_gemm(GemmDesc &d, cudaStream_t st) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (d.M <= 0 || d.K <= 0 || d.N <= 0 || !d.out || !d.a || !d.b) return GPT2L_ERR_BAD_ARG;
+  if (d.opts.mode != GPT2L_MODE_TF32 && d.opts.mode != GPT2L_MODE_TF32X3) return GPT2L_ERR_BAD_ARG;
+  if ((long long)d.M * d.N >= (1ll << 40) || (long long)d.M * d.K >= (1ll << 40)) return GPT2L_ERR_TOO_LARGE;
+  if (d.opts.force_simt || !tma_eligible(d)) {
+    if (d.opts.flags & GPT2L_EPI_GELU_DUAL) return GPT2L_ERR_BAD_ARG;
+    return launch_simt(d, st);
+  }
+  // bias gradient: fused into the kernel (column sums of the staged g_out blocks) unless a
+  // fixed summation order is requested, which the stand-alone column-sum kernel provides.
+  float *fused_bias = d.out_bias;
+  if (d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.out_bias && d.opts.deterministic) {
+    fused_bias = nullptr;
+  }
+  GemmDesc dd = d;
+  dd.out_bias = fused_bias;
+  GemmOp op;
+  err = build_op(dd, ctx->num_sms, &op);
+  if (err) return err;
+  if (op.splits > 1) {
+    if (op.atomic_out) {
+      if (cudaMemsetAsync(op.C, 0, (size_t)op.Mc * op.Nc * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
+    } else {
+      std::lock_guard<std::mutex> lk(g_mu);
+      if ((size_t)op.tiles_m * op.tiles_n * 4 > ctx->ws_sem_count) return GPT2L_ERR_TOO_LARGE;
+      err = ensure_bytes(&ctx->ws, &ctx->ws_bytes, op_workspace_bytes(op));
+      if (err) return err;
+      op.ws = ctx->ws;
+      op.ws_sem = ctx->ws_sem;
+    }
+    if (op.colsum && cudaMemsetAsync(op.colsum, 0, (size_t)op.Nc * sizeof(float), st) != cudaSuccess)
+      return GPT2L_ERR_CUDA;
+  }
+  err = launch_single(ctx, op, st);
+  if (err) return err;
+  if (d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.out_bias && !fused_bias)
+    return launch_colsum(d.out_bias, d.b, d.M, d.N, st);
+  return GPT2L_OK;
+}
+
+static gpt2_linear_opts opts_or_default(const gpt2_linear_opts *o) {
+  gpt2_linear_opts r;
+  memset(&r, 0, sizeof(r));
+  if (o) r = *o;
+  return r;
+}
+
+static int read_status(DeviceCtx *ctx, Status *out, bool clear) {
+  if (cudaMemcpy(ctx->h_status, ctx->d_status, sizeof(Status), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  *out = *ctx->h_status;
+  if (clear && out->status != 0) cudaMemset(ctx->d_status, 0, sizeof(Status));
+  return GPT2L_OK;
+}
+
+}  // namespace g2l
+
+using namespace g2l;
+
+extern "C" {
+
+int gpt2_linear_version(void) { return 100; }
+
+long long gpt2_linear_launch_count(void) { return launch_count_value(); }
+
+int gpt2_linear_init(int device) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    return GPT2L_ERR_NO_DEVICE;
+  }
+  if (device < 0 || device >= n || device >= MAX_DEVICES) return GPT2L_ERR_BAD_ARG;
+  if (cudaSetDevice(device) != cudaSuccess) return GPT2L_ERR_CUDA;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceCtx &c = g_ctx[device];
+  if (c.ready) return GPT2L_OK;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return GPT2L_ERR_CUDA;
+  if (prop.major != 10) return GPT2L_ERR_NO_DEVICE;  // tcgen05 / TMEM exist on sm_100 only
+  if (!get_encode_fn()) return GPT2L_ERR_CUDA;
+  int e = set_kernel_attributes();
+  if (e) return e;
+  c.device = device;
+  c.num_sms = prop.multiProcessorCount;
+  if (cudaMalloc(reinterpret_cast<void **>(&c.d_status), sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;
+  cudaMemset(c.d_status, 0, sizeof(Status));
+  if (cudaMallocHost(reinterpret_cast<void **>(&c.h_status), sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;
+  if (cudaMalloc(reinterpret_cast<void **>(&c.ws_sem), SEM_COUNT * sizeof(unsigned)) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  cudaMemset(c.ws_sem, 0, SEM_COUNT * sizeof(unsigned));
+  c.ws_sem_count = SEM_COUNT;
+  c.ready = true;
+  return GPT2L_OK;
+}
+
+void gpt2_linear_shutdown(void) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  int cur = -1;
+  cudaGetDevice(&cur);
+  for (int d = 0; d < MAX_DEVICES; ++d) {
+    DeviceCtx &c = g_ctx[d];
+    if (!c.ready) continue;
+    cudaSetDevice(d);
+    cudaDeviceSynchronize();
+    cudaFree(c.d_status);
+    cudaFreeHost(c.h_status);
+    cudaFree(c.ws_sem);
+    if (c.ws) cudaFree(c.ws);
+    for (int i = 0; i < 4; ++i)
+      if (c.stage[i]) cudaFree(c.stage[i]);
+    c = DeviceCtx();
+  }
+  if (cur >= 0) cudaSetDevice(cur);
+  (void)cudaGetLastError();
+}
+
+int gpt2_linear_last_status(int out[6]) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  Status s;
+  err = read_status(ctx, &s, true);
+  if (err) return err;
+  if (out) {
+    out[0] = s.status; out[1] = s.op; out[2] = s.counter; out[3] = s.seen; out[4] = s.expected; out[5] = s.where;
+  }
+  return s.status;
+}
+
+int gpt2_linear_forward(float *out, const float *in, const float *w, const float *b, int B, int S, int K, int N,
+                        const gpt2_linear_opts *opts, gpt2l_stream_t stream) {
+  if (B <= 0 || S <= 0) return GPT2L_ERR_BAD_ARG;
+  if ((long long)B * S > 0x7fffffffll) return GPT2L_ERR_TOO_LARGE;
+  GemmDesc d;
+  d.kind = GPT2L_OP_FORWARD;
+  d.M = B * S; d.K = K; d.N = N;
+  d.out = out; d.out_bias = nullptr; d.a = in; d.b = w; d.bias = b;
+  d.opts = opts_or_default(opts);
+  return run_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+int gpt2_linear_backward_input(float *g_in, const float *g_out, const float *w, int B, int S, int K, int N,
+                               const gpt2_linear_opts *opts, gpt2l_stream_t stream) {
+  if (B <= 0 || S <= 0) return GPT2L_ERR_BAD_ARG;
+  if ((long long)B * S > 0x7fffffffll) return GPT2L_ERR_TOO_LARGE;
+  GemmDesc d;
+  d.kind = GPT2L_OP_BACKWARD_INPUT;
+  d.M = B * S; d.K = K; d.N = N;
+  d.out = g_in; d.out_bias = nullptr; d.a = g_out; d.b = w; d.bias = nullptr;
+  d.opts = opts_or_default(opts);
+  return run_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+int gpt2_linear_backward_weight(float *g_w, float *g_b, const float *g_out, const float *in, int B, int S, int K,
+                                int N, const gpt2_linear_opts *opts, gpt2l_stream_t stream) {
+  if (B <= 0 || S <= 0) return GPT2L_ERR_BAD_ARG;
+  if ((long long)B * S > 0x7fffffffll) return GPT2L_ERR_TOO_LARGE;
+  GemmDesc d;
+  d.kind = GPT2L_OP_BACKWARD_WEIGHT;
+  d.M = B * S; d.K = K; d.N = N;
+  d.out = g_w; d.out_bias = g_b; d.a = in; d.b = g_out; d.bias = nullptr;
+  d.opts = opts_or_default(opts);
+  return run_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------
+// host-buffer flavours
+// ---------------------------------------------------------------------------------------
+static int stage_in(DeviceCtx *ctx, int slot, const float *host, size_t count, cudaStream_t st) {
+  int e = ensure_bytes(&ctx->stage[slot], &ctx->stage_bytes[slot], count * sizeof(float));
+  if (e) return e;
+  if (host &&
+      cudaMemcpyAsync(ctx->stage[slot], host, count * sizeof(float), cudaMemcpyHostToDevice, st) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  return GPT2L_OK;
+}
+
+static int finish_host(DeviceCtx *ctx, cudaStream_t st) {
+  if (cudaStreamSynchronize(st) != cudaSuccess) return GPT2L_ERR_CUDA;
+  Status s;
+  int e = read_status(ctx, &s, true);
+  if (e) return e;
+  return s.status;
+}
+
+int gpt2_linear_forward_host(float *out, const float *in, const float *w, const float *b, int B, int S, int K,
+                             int N, const gpt2_linear_opts *opts, gpt2l_stream_t stream) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (!out || !in || !w || B <= 0 || S <= 0 || K <= 0 || N <= 0) return GPT2L_ERR_BAD_ARG;
+  if (opts && (opts->flags & GPT2L_EPI_GELU_DUAL)) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t M = (size_t)B * S;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  if ((err = stage_in(ctx, 0, in, M * K, st))) return err;
+  if ((err = stage_in(ctx, 1, w, (size_t)K * N, st))) return err;
+  if ((err = stage_in(ctx, 2, nullptr, M * N, st))) return err;
+  if (b && (err = stage_in(ctx, 3, b, (size_t)N, st))) return err;
+  err = gpt2_linear_forward(ctx->stage[2], ctx->stage[0], ctx->stage[1], b ? ctx->stage[3] : nullptr, B, S, K, N,
+                            opts, stream);
+  if (err) return err;
+  if (cudaMemcpyAsync(out, ctx->stage[2], M * N * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  return finish_host(ctx, st);
+}
+
+int gpt2_linear_backward_input_host(float *g_in, const float *g_out, const float *w, int B, int S, int K, int N,
+                                    const gpt2_linear_opts *opts, gpt2l_stream_t stream) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (!g_in || !g_out || !w || B <= 0 || S <= 0 || K <= 0 || N <= 0) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t M = (size_t)B * S;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  if ((err = stage_in(ctx, 0, g_out, M * N, st))) return err;
+  if ((err = stage_in(ctx, 1, w, (size_t)K * N, st))) return err;
+  if ((err = stage_in(ctx, 2, nullptr, M * K, st))) return err;
+  err = gpt2_linear_backward_input(ctx->stage[2], ctx->stage[0], ctx->stage[1], B, S, K, N, opts, stream);
+  if (err) return err;
+  if (cudaMemcpyAsync(g_in, ctx->stage[2], M * K * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  return finish_host(ctx, st);
+}
+
+int gpt2_linear_backward_weight_host(float *g_w, float *g_b, const float *g_out, const float *in, int B, int S,
+                                     int K, int N, const gpt2_linear_opts *opts, gpt2l_stream_t stream) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (!g_w || !g_out || !in || B <= 0 || S <= 0 || K <= 0 || N <= 0) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t M = (size_t)B * S;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  if ((err = stage_in(ctx, 0, in, M * K, st))) return err;
+  if ((err = stage_in(ctx, 1, g_out, M * N, st))) return err;
+  if ((err = stage_in(ctx, 2, nullptr, (size_t)K * N, st))) return err;
+  if (g_b && (err = stage_in(ctx, 3, nullptr, (size_t)N, st))) return err;
+  err = gpt2_linear_backward_weight(ctx->stage[2], g_b ? ctx->stage[3] : nullptr, ctx->stage[1], ctx->stage[0], B,
+                                    S, K, N, opts, stream);
+  if (err) return err;
+  if (cudaMemcpyAsync(g_w, ctx->stage[2], (size_t)K * N * sizeof(float), cudaMemcpyDeviceToHost, st) !=
+      cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  if (g_b && cudaMemcpyAsync(g_b, ctx->stage[3], (size_t)N * sizeof(float), cudaMemcpyDeviceToHost, st) !=
+                 cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  return finish_host(ctx, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,158 @@
+// Internal declarations shared by the translation units of libgpt2_linear.so.
+// Nothing in here is part of the C ABI (see include/gpt2_linear.h for that).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gpt2_linear.h"
+
+namespace g2l {
+
+// ---- tile geometry of the tcgen05 kernel ------------------------------------------
+constexpr int BM = 128;      // UMMA M (one TMEM lane per output row)
+constexpr int BK = 32;       // fp32 elements per k-block = one 128-byte swizzle row
+constexpr int MAX_BN = 256;  // UMMA N upper bound
+constexpr int UMMA_K = 8;    // kind::tf32
+constexpr int A_TILE_BYTES = BM * BK * 4;      // 16 KiB
+constexpr int B_TILE_BYTES = MAX_BN * BK * 4;  // 32 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int STAGES_1X = 4;  // TF32: 4 x 48 KiB
+constexpr int STAGES_3X = 2;  // 3xTF32: 2 x (48 KiB hi + 48 KiB lo)
+constexpr int RING_BYTES = STAGES_1X * STAGE_BYTES;  // 192 KiB in both modes
+constexpr int NUM_ACC = 2;                           // TMEM accumulator double buffer
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 320;  // 10 warps: producer, mma, 4 transform, 4 epilogue
+constexpr int EPI_WARP0 = 6;
+constexpr int XFORM_WARP0 = 2;
+constexpr int NUM_XFORM_WARPS = 4;
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int SMEM_CTRL_BYTES = 512;  // mbarriers + tmem pointer + abort flag
+constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + RING_BYTES + SMEM_CTRL_BYTES;
+
+constexpr int MAX_WAITS = GPT2L_MAX_DEPS;
+
+// where a bounded wait gave up (status record field `where`)
+enum WaitSite {
+  SITE_NONE = 0,
+  SITE_DEP_COUNTER = 1,
+  SITE_SMEM_EMPTY = 2,
+  SITE_SMEM_FULL = 3,
+  SITE_SMEM_READY = 4,
+  SITE_TMEM_EMPTY = 5,
+  SITE_TMEM_FULL = 6,
+  SITE_SPLITK_TURNSTILE = 7
+};
+
+// Device status record: one per device (single-op calls) or per schedule.
+struct Status {
+  int status;    // 0 ok, bit0 timeout
+  int op;        // op index whose wait expired
+  int counter;   // dependency counter index or mbarrier stage
+  int seen;      // last value read
+  int expected;  // value waited for
+  int where;     // WaitSite
+};
+
+// One GEMM as the kernel sees it: C[Mc][Nc] = A . B (+ bias), reduction length Kc.
+// A is "K-major" when its reduction index is contiguous in memory ([Mc][Kc] row-major) and
+// "MN-major" when its Mc index is contiguous ([Kc][Mc] row-major); likewise B with Nc.
+struct alignas(64) GemmOp {
+  CUtensorMap tmA;  // box {32, 128} (K-major) or {32, 32} (MN-major)
+  CUtensorMap tmB;  // box {32, bn}  (K-major) or {32, 32} (MN-major)
+  float *C;
+  float *C2;            // gelu(C) when flags & GPT2L_EPI_GELU_DUAL
+  const float *bias;    // [Nc] or null
+  float *colsum;        // wgrad: g_b[Nc] or null (column sums of B over the reduction)
+  float *ws;            // deterministic split-K: partial tiles [n_tiles][BM*bn]
+  float *ws_colsum;     // deterministic split-K: [splits][Nc]
+  unsigned *ws_sem;     // deterministic split-K: per output tile arrival counter
+  long long ldc;
+  int Mc, Nc, Kc;
+  int a_mn, b_mn;       // 1 = MN-major
+  int bn;               // 64 / 128 / 256
+  int tiles_m, tiles_n, splits, kb_total, kb_per_split;
+  int tile_base;        // global index of this op's first tile
+  int n_tiles;          // tiles_m * tiles_n * splits
+  int mode;             // gpt2l_mode
+  unsigned flags;
+  int atomic_out;       // split-K partials combined with red.add into a zeroed C
+  int wait_ctr[MAX_WAITS];       // first counter index, -1 = none
+  int wait_kind[MAX_WAITS];      // GPT2L_DEP_*
+  int wait_expected[MAX_WAITS];  // arrivals to wait for
+  int pub_rb_base;      // counter index of row block 0 (or -1)
+  int pub_op_ctr;       // op-level counter index (or -1)
+  unsigned idesc;       // tcgen05 instruction descriptor
+  int op_index;
+  int layer;
+};
+
+struct LaunchParams {
+  const GemmOp *ops;  // device array, or nullptr to use the by-value op
+  int n_ops;
+  int total_tiles;
+  Status *status;
+  unsigned *counters;
+  long long wait_limit_ns;
+};
+
+// host-side description used to build a GemmOp
+struct GemmDesc {
+  int kind;  // gpt2l_op_kind
+  int M, K, N;
+  float *out;
+  float *out_bias;
+  const float *a;
+  const float *b;
+  const float *bias;
+  gpt2_linear_opts opts;
+};
+
+struct DeviceCtx {
+  bool ready = false;
+  int device = -1;
+  int num_sms = 0;
+  Status *d_status = nullptr;       // device
+  Status *h_status = nullptr;       // pinned host mirror
+  float *ws = nullptr;              // split-K workspace
+  size_t ws_bytes = 0;
+  unsigned *ws_sem = nullptr;
+  size_t ws_sem_count = 0;
+  // host-call staging
+  float *stage[4] = {nullptr, nullptr, nullptr, nullptr};
+  size_t stage_bytes[4] = {0, 0, 0, 0};
+};
+
+DeviceCtx *ctx_current(int *err);
+
+// --- linear_tcgen05.cu ---
+// Can this GEMM go through TMA + tcgen05? (16-byte aligned pointers and row strides)
+bool tma_eligible(const GemmDesc &d);
+// Fills `op` (tensor maps, tiling, idesc). `num_sms` guides the tile width / split choice.
+// Workspace pointers and dependency fields are left for the caller.
+int build_op(const GemmDesc &d, int num_sms, GemmOp *op);
+// The host-only part of build_op (no tensor maps, no CUDA calls): shapes, tiling, descriptor bits.
+int plan_op(const GemmDesc &d, int num_sms, GemmOp *op);
+long long launch_count_value();
+// bytes of deterministic split-K workspace the op needs (0 if none)
+size_t op_workspace_bytes(const GemmOp &op);
+int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream);
+int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid,
+                bool any_3x, Status *d_status, unsigned *d_counters, long long wait_limit_ns,
+                cudaStream_t stream);
+int set_kernel_attributes();
+void count_launch(int n = 1);
+
+// --- linear_simt.cu ---
+int launch_simt(const GemmDesc &d, cudaStream_t stream);
+int launch_colsum(float *out, const float *x, int rows, int cols, cudaStream_t stream);
+
+// --- driver entry point for tensor-map encoding ---
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn();
+
+}  // namespace g2l

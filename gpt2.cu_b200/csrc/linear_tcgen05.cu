@@ -1,0 +1,775 @@
+// The sm_100a GEMM kernel behind all three linear-layer calls and the megakernel.
+//
+// One persistent, warp-specialised kernel:  C[Mc][Nc] = A . B (+ bias), fp32 in HBM,
+// TF32 (or 3xTF32) on the tcgen05 tensor cores, fp32 accumulators in tensor memory.
+//
+//   warp 0      TMA producer: waits for the tile's dependency counters, then streams
+//               128 x 32 (A) and bn x 32 (B) fp32 blocks into a shared-memory ring with
+//               cp.async.bulk.tensor (no multicast), signalling `full[s]`.
+//   warp 1      allocates the 512 TMEM columns; one lane issues tcgen05.mma.kind::tf32
+//               (128 x bn x 8 per instruction, 4 per k-block), commits to `empty[s]`, and
+//               after the last k-block commits to `tmem_full[acc]`.
+//   warps 2-5   operand transform: in 3xTF32 mode split each landed stage into hi + lo
+//               copies; in backward_weight they also add up the columns of the B block
+//               (the bias gradient) for the tile row that owns it.
+//   warps 6-9   epilogue: tcgen05.ld the accumulator (warp w reads TMEM lanes 32*(w%4)..),
+//               add bias / GELU dual store / split-K combine, store fp32, then publish the
+//               tile on the dependency counters with a release reduction.
+//
+// Operand layouts. A k-block is 32 fp32 = 128 bytes wide. An operand whose reduction index
+// is contiguous in HBM ("K-major") lands as rows of 128 bytes with the 128-byte swizzle
+// (16-byte chunk index XOR row%8). An operand whose output index is contiguous ("MN-major":
+// W in forward, both operands in backward_weight) lands as 32 x 32 boxes with the 128-byte
+// swizzle on 32-byte atoms (32-byte chunk index XOR row%4) — the only shared-memory layout
+// tcgen05 accepts for MN-major 32-bit operands.
+//
+// Every wait in here is bounded: on expiry the CTA records where it gave up in the status
+// record, raises an abort flag that every other loop polls, and the kernel unwinds (TMEM
+// is freed) instead of hanging.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+
+#include "linear_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace g2l {
+
+using namespace ptx;
+
+// ------------------------------------------------------------------------------------
+// shared-memory control block
+// ------------------------------------------------------------------------------------
+struct Ctrl {
+  uint64_t full[STAGES_1X];
+  uint64_t empty[STAGES_1X];
+  uint64_t ready[STAGES_1X];
+  uint64_t tmem_full[NUM_ACC];
+  uint64_t tmem_empty[NUM_ACC];
+  uint32_t tmem_base;
+  int abort;
+};
+static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
+
+struct Tile {
+  int m_tile, n_tile, split;
+  int kb0, kb1;
+};
+
+// Advances `cursor` to the op that owns global tile `t` and decodes the tile.
+// Order inside an op: n fastest, then m, then split — tiles that run at the same time share
+// the same k-range of both operands in L2.
+__device__ __forceinline__ const GemmOp *decode_tile(const GemmOp *ops, int n_ops, int t, int &cursor,
+                                                     Tile &tc) {
+  while (cursor + 1 < n_ops && t >= ops[cursor].tile_base + ops[cursor].n_tiles) ++cursor;
+  const GemmOp *op = ops + cursor;
+  int local = t - op->tile_base;
+  tc.n_tile = local % op->tiles_n;
+  int rest = local / op->tiles_n;
+  tc.m_tile = rest % op->tiles_m;
+  tc.split = rest / op->tiles_m;
+  tc.kb0 = tc.split * op->kb_per_split;
+  int kb1 = tc.kb0 + op->kb_per_split;
+  tc.kb1 = kb1 < op->kb_total ? kb1 : op->kb_total;
+  return op;
+}
+
+__device__ __noinline__ void raise_timeout(Ctrl *ctrl, const LaunchParams &p, int site, int op, int idx,
+                                           int seen, int expected) {
+  *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+  if (atomicCAS(&p.status->status, 0, GPT2L_DEV_TIMEOUT) == 0) {
+    p.status->op = op;
+    p.status->counter = idx;
+    p.status->seen = seen;
+    p.status->expected = expected;
+    p.status->where = site;
+    __threadfence();
+  }
+}
+
+// true = the phase completed; false = abort (ours or another CTA's) or the limit ran out.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl *ctrl, const LaunchParams &p,
+                                         int site, int op, int idx) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 127u) == 0) {
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
+      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
+        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+        return false;
+      }
+      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
+        raise_timeout(ctrl, p, site, op, idx, -1, (int)parity);
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded acquire-poll on a dependency counter.
+__device__ __forceinline__ bool wait_counter(const unsigned *ctr, unsigned expected, Ctrl *ctrl,
+                                             const LaunchParams &p, int op, int idx) {
+  unsigned v = ld_acquire(ctr);
+  if (v >= expected) return true;
+  const long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    __nanosleep(64);
+    v = ld_acquire(ctr);
+    if (v >= expected) return true;
+    if ((++spins & 15u) == 0) {
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
+      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
+        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+        return false;
+      }
+      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
+        raise_timeout(ctrl, p, SITE_DEP_COUNTER, op, idx, (int)v, (int)expected);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;  // sqrt(2/pi)
+  float u = k * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// ------------------------------------------------------------------------------------
+// the kernel
+// ------------------------------------------------------------------------------------
+template <bool X3>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int NST = X3 ? STAGES_3X : STAGES_1X;
+  constexpr int STAGE_STRIDE = X3 ? 2 * STAGE_BYTES : STAGE_BYTES;
+  constexpr int LO_OFFSET = STAGE_BYTES;  // 3x: lo copies sit behind the hi copies of a stage
+
+  const GemmOp *ops = p.ops ? p.ops : &op0;
+  const int n_ops = p.ops ? p.n_ops : 1;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t ring = (raw + 1023u) & ~1023u;
+  uint8_t *ring_ptr = smem_raw + (ring - raw);
+  Ctrl *ctrl = reinterpret_cast<Ctrl *>(ring_ptr + RING_BYTES);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES_1X; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1 + NUM_XFORM_WARPS);
+      mbar_init(smem_u32(&ctrl->ready[s]), NUM_XFORM_WARPS);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[a]), NUM_EPI_WARPS);
+    }
+    ctrl->abort = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(&ctrl->tmem_base);
+
+  if (warp == 0) {
+    // =============================== TMA producer ===============================
+    int cursor = 0;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      Tile tc;
+      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      // ---- dependency counters: do not touch the operands before their producers are done
+      bool waited = false;
+#pragma unroll
+      for (int w = 0; w < MAX_WAITS; ++w) {
+        const int base = op->wait_ctr[w];
+        if (base < 0) continue;
+        const int idx = base + (op->wait_kind[w] == GPT2L_DEP_ROWBLOCK ? tc.m_tile : 0);
+        int okl = 1;
+        if (lane == 0)
+          okl = wait_counter(p.counters + idx, (unsigned)op->wait_expected[w], ctrl, p, op->op_index, idx);
+        ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+        waited = true;
+        if (!ok) break;
+      }
+      if (!ok) break;
+      if (waited) fence_proxy_async_all();  // producers wrote with plain stores; TMA reads next
+
+      const int m0 = tc.m_tile * BM;
+      const int n0 = tc.n_tile * op->bn;
+      const int a_mn = op->a_mn, b_mn = op->b_mn, bn = op->bn;
+      const uint32_t tx_bytes = (uint32_t)(A_TILE_BYTES + bn * BK * 4);
+      for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
+        const int s = it % NST;
+        const uint32_t ph = (it / NST) & 1u;
+        int okl = 1;
+        if (lane == 0)
+          okl = wait_bar(smem_u32(&ctrl->empty[s]), ph ^ 1u, ctrl, p, SITE_SMEM_EMPTY, op->op_index, s);
+        ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t bar = smem_u32(&ctrl->full[s]);
+          const uint32_t a_dst = ring + s * STAGE_STRIDE;
+          const uint32_t b_dst = a_dst + A_TILE_BYTES;
+          mbar_arrive_expect_tx(bar, tx_bytes);
+          const int k0 = kb * BK;
+          if (!a_mn) {
+            tma_load_2d(a_dst, &op->tmA, bar, k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + c * 4096, &op->tmA, bar, m0 + c * 32, k0);
+          }
+          if (!b_mn) {
+            tma_load_2d(b_dst, &op->tmB, bar, k0, n0);
+          } else {
+            for (int c = 0; c < bn / 32; ++c) tma_load_2d(b_dst + c * 4096, &op->tmB, bar, n0 + c * 32, k0);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    int cursor = 0;
+    uint32_t it = 0, tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tcount) {
+      Tile tc;
+      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      const uint32_t as = tcount & 1u;
+      const uint32_t aph = (tcount >> 1) & 1u;
+      int okl = 1;
+      if (lane == 0)
+        okl = wait_bar(smem_u32(&ctrl->tmem_empty[as]), aph ^ 1u, ctrl, p, SITE_TMEM_EMPTY, op->op_index, as);
+      ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+
+      const uint32_t d_tmem = tmem_base + as * MAX_BN;
+      const uint32_t idesc = op->idesc;
+      // K-major: 8-row groups 1024 B apart, 128B swizzle; k-step = 32 B inside the row.
+      // MN-major: 32-column chunks 4096 B apart (LBO), 4-row k-groups 512 B apart (SBO),
+      //           128B swizzle on 32-byte atoms; k-step = 8 rows = 1024 B.
+      const uint64_t hiA = op->a_mn ? smem_desc_hi(4096, 512, 1) : smem_desc_hi(16, 1024, 2);
+      const uint64_t hiB = op->b_mn ? smem_desc_hi(4096, 512, 1) : smem_desc_hi(16, 1024, 2);
+      const uint32_t stepA = op->a_mn ? 1024u : 32u;
+      const uint32_t stepB = op->b_mn ? 1024u : 32u;
+
+      for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
+        const int s = it % NST;
+        const uint32_t ph = (it / NST) & 1u;
+        okl = 1;
+        if (lane == 0) {
+          const uint32_t bar = X3 ? smem_u32(&ctrl->ready[s]) : smem_u32(&ctrl->full[s]);
+          okl = wait_bar(bar, ph, ctrl, p, X3 ? SITE_SMEM_READY : SITE_SMEM_FULL, op->op_index, s);
+        }
+        ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = ring + s * STAGE_STRIDE;
+          const uint32_t b_addr = a_addr + A_TILE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint32_t acc = (kb > tc.kb0 || ks > 0) ? 1u : 0u;
+            const uint64_t da = smem_desc(hiA, a_addr + ks * stepA);
+            const uint64_t db = smem_desc(hiB, b_addr + ks * stepB);
+            if (X3) {
+              const uint64_t da_lo = smem_desc(hiA, a_addr + LO_OFFSET + ks * stepA);
+              const uint64_t db_lo = smem_desc(hiB, b_addr + LO_OFFSET + ks * stepB);
+              mma_tf32(d_tmem, da_lo, db, idesc, acc);  // small terms first
+              mma_tf32(d_tmem, da, db_lo, idesc, 1u);
+              mma_tf32(d_tmem, da, db, idesc, 1u);
+            } else {
+              mma_tf32(d_tmem, da, db, idesc, acc);
+            }
+          }
+          mma_commit(smem_u32(&ctrl->empty[s]));  // frees the stage once these MMAs have read it
+        }
+        __syncwarp();
+      }
+      if (!ok) break;
+      if (lane == 0) mma_commit(smem_u32(&ctrl->tmem_full[as]));
+      __syncwarp();
+    }
+  } else if (warp < EPI_WARP0) {
+    // =============================== operand transform ===============================
+    const int x = tid - XFORM_WARP0 * 32;  // 0..127
+    int cursor = 0;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      Tile tc;
+      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      const int bn = op->bn;
+      const bool do_colsum = (op->colsum != nullptr) && tc.m_tile == 0 && op->b_mn;
+      // column-sum mapping: `groups` float4 column groups, `parts` threads share a group and
+      // split the 32 k-rows of a block between them.
+      const int groups = bn >> 2;
+      const int parts = 128 / groups;
+      const int rows_per_part = 32 / parts;
+      const int grp = x / parts, part = x % parts;
+      const int chunk = grp >> 3, q16 = grp & 7;
+      float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int stage_f4 = (A_TILE_BYTES + bn * BK * 4) >> 4;
+
+      for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
+        const int s = it % NST;
+        const uint32_t ph = (it / NST) & 1u;
+        int okl = 1;
+        if (lane == 0)
+          okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
+        ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+        if (!ok) break;
+        uint8_t *stage = ring_ptr + s * STAGE_STRIDE;
+        // An MN-major B block is walked by (column group, k-row) so that the thread that sums a
+        // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
+        // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
+        const bool walk_b = op->b_mn && (X3 || do_colsum);
+        if (walk_b) {
+          uint8_t *bchunk = stage + A_TILE_BYTES + chunk * 4096;
+#pragma unroll 4
+          for (int r = part * rows_per_part; r < (part + 1) * rows_per_part; ++r) {
+            const int phys32 = (q16 >> 1) ^ (r & 3);
+            float4 *ptr = reinterpret_cast<float4 *>(bchunk + r * 128 + phys32 * 32 + (q16 & 1) * 16);
+            const float4 v = *ptr;
+            csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w;
+            if (X3) {
+              float4 h, l;
+              h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
+              l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+              *ptr = h;
+              *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(ptr) + LO_OFFSET) = l;
+            }
+          }
+        }
+        if (X3) {
+          float4 *hi = reinterpret_cast<float4 *>(stage);
+          float4 *lo = reinterpret_cast<float4 *>(stage + LO_OFFSET);
+          const int lin_f4 = walk_b ? (A_TILE_BYTES >> 4) : stage_f4;  // A only, or A and a K-major B
+          for (int i = x; i < lin_f4; i += NUM_XFORM_WARPS * 32) {
+            const float4 v = hi[i];
+            float4 h, l;
+            h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
+            l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+            hi[i] = h;
+            lo[i] = l;
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if (X3) mbar_arrive(smem_u32(&ctrl->ready[s]));
+          mbar_arrive(smem_u32(&ctrl->empty[s]));
+        }
+      }
+      if (!ok) break;
+      if (do_colsum) {
+        for (int o = 1; o < parts; o <<= 1) {
+          csum.x += __shfl_xor_sync(0xffffffffu, csum.x, o);
+          csum.y += __shfl_xor_sync(0xffffffffu, csum.y, o);
+          csum.z += __shfl_xor_sync(0xffffffffu, csum.z, o);
+          csum.w += __shfl_xor_sync(0xffffffffu, csum.w, o);
+        }
+        if (part == 0) {
+          const int col = tc.n_tile * bn + grp * 4;
+          const float v[4] = {csum.x, csum.y, csum.z, csum.w};
+          for (int j = 0; j < 4; ++j) {
+            if (col + j < op->Nc) {
+              if (op->splits > 1) atomicAdd(op->colsum + col + j, v[j]);
+              else op->colsum[col + j] = v[j];
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // =============================== epilogue ===============================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int cursor = 0;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tcount) {
+      Tile tc;
+      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      const uint32_t as = tcount & 1u;
+      const uint32_t aph = (tcount >> 1) & 1u;
+      int okl = 1;
+      if (lane == 0)
+        okl = wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as);
+      ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+
+      const int bn = op->bn;
+      const int Mc = op->Mc, Nc = op->Nc;
+      const long long ldc = op->ldc;
+      const int row = tc.m_tile * BM + q * 32 + lane;
+      const int n0 = tc.n_tile * bn;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * MAX_BN;
+      const bool det_split = (op->splits > 1) && !op->atomic_out;
+      const bool add_bias = (op->bias != nullptr) && (tc.split == 0 || det_split);
+      const bool dual = (op->flags & GPT2L_EPI_GELU_DUAL) && op->C2 != nullptr;
+      const int out_tile = tc.m_tile * op->tiles_n + tc.n_tile;
+      float *ws_tile = nullptr;
+      if (det_split)
+        ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
+                  (size_t)(q * 32 + lane) * bn;
+
+      for (int c = 0; c < bn / 32; ++c) {
+        const int nb = n0 + c * 32;
+        if (nb >= Nc) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (det_split) {
+          float4 *dst = reinterpret_cast<float4 *>(ws_tile + c * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          continue;
+        }
+        if (row >= Mc) continue;
+        float *dst = op->C + (long long)row * ldc + nb;
+        const bool full = (nb + 32 <= Nc);
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            if (add_bias) {
+              const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + nb) + j);
+              v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+            }
+            if (op->atomic_out) {
+              red_add_v4(dst + 4 * j, v.x, v.y, v.z, v.w);
+            } else {
+              reinterpret_cast<float4 *>(dst)[j] = v;
+              if (dual) {
+                float4 g = make_float4(gelu_tanh(v.x), gelu_tanh(v.y), gelu_tanh(v.z), gelu_tanh(v.w));
+                reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + nb)[j] = g;
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (nb + j < Nc) {
+              float v = __uint_as_float(r[j]);
+              if (add_bias) v += __ldg(op->bias + nb + j);
+              if (op->atomic_out) {
+                atomicAdd(dst + j, v);
+              } else {
+                dst[j] = v;
+                if (dual) op->C2[(long long)row * ldc + nb + j] = gelu_tanh(v);
+              }
+            }
+          }
+        }
+      }
+      // the accumulator is in registers / memory now: hand the TMEM buffer back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[as]));
+
+      if (det_split) {
+        // Deterministic split-K: every split parks its partial rows in the workspace; the
+        // warp that arrives last for this (output tile, lane quarter) adds the partials in
+        // split order and writes C. No ordering between splits is ever waited for.
+        __threadfence();
+        __syncwarp();
+        unsigned old = 0;
+        unsigned *sem = op->ws_sem + (size_t)out_tile * 4 + q;
+        if (lane == 0) old = atom_acq_rel_add(sem, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == (unsigned)(op->splits - 1)) {
+          __threadfence();
+          if (lane == 0) *sem = 0;  // ready for the next launch
+          const size_t split_stride = (size_t)op->tiles_m * op->tiles_n * (size_t)(BM * bn);
+          const float *p0 = op->ws + (size_t)out_tile * (size_t)(BM * bn) + (size_t)(q * 32 + lane) * bn;
+          if (row < Mc) {
+            for (int c4 = 0; c4 < bn / 4; ++c4) {
+              const int col = n0 + c4 * 4;
+              if (col >= Nc) break;
+              // L2 reads: the partials were written by other SMs during this launch
+              float4 acc = __ldcg(reinterpret_cast<const float4 *>(p0 + c4 * 4));
+              for (int sp = 1; sp < op->splits; ++sp) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + sp * split_stride + c4 * 4));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+              }
+              float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+              float *dst = op->C + (long long)row * ldc + col;
+              if (col + 4 <= Nc) {
+                if (add_bias) {
+                  const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + col));
+                  vals[0] += bv.x; vals[1] += bv.y; vals[2] += bv.z; vals[3] += bv.w;
+                }
+                *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+                if (dual)
+                  *reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + col) =
+                      make_float4(gelu_tanh(vals[0]), gelu_tanh(vals[1]), gelu_tanh(vals[2]), gelu_tanh(vals[3]));
+              } else {
+                for (int j = 0; j < 4; ++j)
+                  if (col + j < Nc) {
+                    float v = vals[j] + (add_bias ? __ldg(op->bias + col + j) : 0.f);
+                    dst[j] = v;
+                    if (dual) op->C2[(long long)row * ldc + col + j] = gelu_tanh(v);
+                  }
+              }
+            }
+          }
+        }
+      }
+
+      // ---- publish: everything this warp stored is visible before the counters move
+      if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          if (op->pub_rb_base >= 0) red_release_add(p.counters + op->pub_rb_base + tc.m_tile, 1u);
+          if (op->pub_op_ctr >= 0) red_release_add(p.counters + op->pub_op_ctr, 1u);
+        }
+      }
+    }
+  }
+
+  // =============================== teardown ===============================
+  if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
+    // give copies and MMAs that are still in flight time to land before smem/TMEM go away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n); }
+long long launch_count_value() { return g_launches.load(); }
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else (void)cudaGetLastError();
+  }
+  return fn;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool tma_eligible(const GemmDesc &d) {
+  // row strides of every tensor involved are K or N floats; TMA needs 16-byte multiples
+  if ((d.K & 3) || (d.N & 3)) return false;
+  if (!aligned16(d.out) || !aligned16(d.a) || !aligned16(d.b)) return false;
+  if (d.bias && !aligned16(d.bias)) return false;
+  if (d.opts.out2 && !aligned16(d.opts.out2)) return false;
+  return true;
+}
+
+// 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch = inner.
+static int encode_map(CUtensorMap *map, const float *base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                      uint32_t box_outer, bool mn_major) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return GPT2L_ERR_CUDA;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * sizeof(float)};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Picks the tile width and the number of reduction splits: the pair that needs the fewest
+// (waves x per-tile work), where a tile's cost follows the bytes it pulls per k-block.
+static void choose_tiling(int Mc, int Nc, int kb_total, int num_sms, int forced_splits, int *bn_out,
+                          int *splits_out) {
+  const int tiles_m = ceil_div(Mc, BM);
+  double best = 1e300;
+  int best_bn = 128, best_s = 1;
+  const int cand[3] = {256, 128, 64};
+  for (int ci = 0; ci < 3; ++ci) {
+    const int bn = cand[ci];
+    if (bn > 64 && bn / 2 >= Nc) continue;  // tile twice as wide as the matrix
+    const int tiles = tiles_m * ceil_div(Nc, bn);
+    const int smax = forced_splits > 0 ? forced_splits : (kb_total < 32 ? kb_total : 32);
+    const int smin = forced_splits > 0 ? forced_splits : 1;
+    for (int s = smin; s <= smax; ++s) {
+      if (s > kb_total) break;
+      const int per = ceil_div(kb_total, s);
+      if (forced_splits == 0 && s > 1 && (s - 1) * per >= kb_total) continue;  // an empty split
+      const double waves = (double)ceil_div(tiles * s, num_sms);
+      // + 6 k-blocks of fixed per-tile overhead (pipeline fill, epilogue); splits pay an
+      // extra pass over the output
+      const double cost = waves * (per + 6.0 + (s > 1 ? 4.0 : 0.0)) * (double)(BM + bn);
+      if (cost < best - 1e-9) {
+        best = cost;
+        best_bn = bn;
+        best_s = s;
+      }
+    }
+  }
+  *bn_out = best_bn;
+  *splits_out = best_s;
+}
+
+// Host-only part of build_op: shapes, majorness, tiling, descriptor bits. No CUDA calls.
+int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
+  memset(op, 0, sizeof(*op));
+  if (d.M <= 0 || d.K <= 0 || d.N <= 0) return GPT2L_ERR_BAD_ARG;
+  switch (d.kind) {
+    case GPT2L_OP_FORWARD:  // out[M][N] = in[M][K] . w[K][N]
+      op->Mc = d.M; op->Nc = d.N; op->Kc = d.K; op->a_mn = 0; op->b_mn = 1;
+      op->bias = d.bias;
+      break;
+    case GPT2L_OP_BACKWARD_INPUT:  // g_in[M][K] = g_out[M][N] . w[K][N]^T
+      op->Mc = d.M; op->Nc = d.K; op->Kc = d.N; op->a_mn = 0; op->b_mn = 0;
+      break;
+    case GPT2L_OP_BACKWARD_WEIGHT:  // g_w[K][N] = in[M][K]^T . g_out[M][N]
+      op->Mc = d.K; op->Nc = d.N; op->Kc = d.M; op->a_mn = 1; op->b_mn = 1;
+      op->colsum = d.out_bias;
+      break;
+    default:
+      return GPT2L_ERR_BAD_ARG;
+  }
+  if (d.opts.mode != GPT2L_MODE_TF32 && d.opts.mode != GPT2L_MODE_TF32X3) return GPT2L_ERR_BAD_ARG;
+  if (d.opts.split_k < 0) return GPT2L_ERR_BAD_ARG;
+  op->C = d.out;
+  op->ldc = op->Nc;
+  op->mode = d.opts.mode;
+  op->flags = (d.kind == GPT2L_OP_FORWARD) ? d.opts.flags : 0u;
+  op->C2 = (op->flags & GPT2L_EPI_GELU_DUAL) ? d.opts.out2 : nullptr;
+  if ((op->flags & GPT2L_EPI_GELU_DUAL) && !op->C2) return GPT2L_ERR_BAD_ARG;
+  op->kb_total = ceil_div(op->Kc, BK);
+  int bn, splits;
+  int forced = d.opts.split_k;
+  if (forced > op->kb_total) forced = op->kb_total;
+  choose_tiling(op->Mc, op->Nc, op->kb_total, num_sms > 0 ? num_sms : 148, forced, &bn, &splits);
+  op->bn = bn;
+  op->kb_per_split = ceil_div(op->kb_total, splits);
+  op->splits = ceil_div(op->kb_total, op->kb_per_split);  // no empty trailing split
+  op->tiles_m = ceil_div(op->Mc, BM);
+  op->tiles_n = ceil_div(op->Nc, bn);
+  op->n_tiles = op->tiles_m * op->tiles_n * op->splits;
+  op->atomic_out = (op->splits > 1 && !d.opts.deterministic && !op->C2) ? 1 : 0;
+  op->idesc = make_idesc_tf32(BM, bn, op->a_mn, op->b_mn);
+  for (int w = 0; w < MAX_WAITS; ++w) { op->wait_ctr[w] = -1; op->wait_kind[w] = 0; op->wait_expected[w] = 0; }
+  op->pub_rb_base = -1;
+  op->pub_op_ctr = -1;
+  return GPT2L_OK;
+}
+
+int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
+  if (!d.out || !d.a || !d.b) return GPT2L_ERR_BAD_ARG;
+  int e = plan_op(d, num_sms, op);
+  if (e) return e;
+  uint64_t a_inner, a_outer, b_inner, b_outer;
+  switch (d.kind) {
+    case GPT2L_OP_FORWARD: a_inner = d.K; a_outer = d.M; b_inner = d.N; b_outer = d.K; break;
+    case GPT2L_OP_BACKWARD_INPUT: a_inner = d.N; a_outer = d.M; b_inner = d.N; b_outer = d.K; break;
+    default: a_inner = d.K; a_outer = d.M; b_inner = d.N; b_outer = d.M; break;
+  }
+  e = encode_map(&op->tmA, d.a, a_inner, a_outer, 32, op->a_mn ? 32 : BM, op->a_mn);
+  if (e) return e;
+  return encode_map(&op->tmB, d.b, b_inner, b_outer, 32, op->b_mn ? 32 : op->bn, op->b_mn);
+}
+
+size_t op_workspace_bytes(const GemmOp &op) {
+  if (op.splits <= 1 || op.atomic_out) return 0;
+  return (size_t)op.n_tiles * BM * op.bn * sizeof(float);
+}
+
+int set_kernel_attributes() {
+  cudaError_t e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return GPT2L_ERR_CUDA;
+  e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           SMEM_BYTES);
+  return e == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+static long long default_wait_limit_ns() { return 4000000000ll; }  // 4 s
+
+int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
+  op.tile_base = 0;
+  op.op_index = 0;
+  LaunchParams p;
+  p.ops = nullptr;
+  p.n_ops = 1;
+  p.total_tiles = op.n_tiles;
+  p.status = ctx->d_status;
+  p.counters = nullptr;
+  p.wait_limit_ns = default_wait_limit_ns();
+  const int grid = op.n_tiles < ctx->num_sms ? op.n_tiles : ctx->num_sms;
+  if (op.mode == GPT2L_MODE_TF32X3)
+    gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
+  else
+    gpt2_linear_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid, bool any_3x,
+                Status *d_status, unsigned *d_counters, long long wait_limit_ns, cudaStream_t stream) {
+  (void)ctx;
+  static GemmOp dummy;  // the by-value slot is unused when a list is given
+  LaunchParams p;
+  p.ops = d_ops;
+  p.n_ops = n_ops;
+  p.total_tiles = total_tiles;
+  p.status = d_status;
+  p.counters = d_counters;
+  p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
+  if (any_3x)
+    gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);
+  else
+    gpt2_linear_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+}  // namespace g2l

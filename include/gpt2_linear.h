@@ -1,0 +1,195 @@
+/*
+ * gpt2_linear.h — C ABI of the B200 (sm_100a) linear-layer GEMM path.
+ *
+ * Every entry point replaces one interface of vnnm404/gpt2.cu and keeps its argument
+ * order and meaning.  All tensors are fp32, row-major and contiguous; every linear weight
+ * is W[K][N] (input_dim x output_dim, the HF Conv1D layout), y = x.W + b.  K and N always
+ * describe the FORWARD weight, also for the two backward calls, so the reduction runs over
+ * K (forward), N (backward_input) or M = B*S (backward_weight) — the reference's convention
+ * (src/train.cu:404-405).
+ *
+ * Conventions
+ *   - return 0 on success; negative = argument / environment error found on the host before
+ *     anything was launched; positive = device status word (bounded wait ran out).
+ *     Nothing here calls exit() or prints from device code.
+ *   - work is enqueued on the caller's stream; the *_host variants synchronise that stream.
+ *   - pointers are device pointers unless the function name ends in _host.
+ *   - outputs are fully overwritten (the reference's semantics: mlp.h:305-333, 634-650,
+ *     952-995); bias / g_bias may be NULL.
+ *   - there is no CPU fallback: without a CUDA device every compute entry returns
+ *     GPT2L_ERR_NO_DEVICE.
+ */
+#ifndef GPT2_LINEAR_H
+#define GPT2_LINEAR_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* CUDA stream handle (cudaStream_t) passed as an opaque pointer so that C callers and
+ * ctypes need no CUDA headers. NULL = the default stream. */
+typedef void *gpt2l_stream_t;
+
+/* ---- error codes (negative: host side) ---- */
+#define GPT2L_OK 0
+#define GPT2L_ERR_NO_DEVICE (-1)   /* no CUDA device / wrong architecture (needs sm_100)   */
+#define GPT2L_ERR_BAD_ARG (-2)     /* NULL operand, non-positive dimension, bad option     */
+#define GPT2L_ERR_CUDA (-3)        /* a CUDA runtime / driver call failed                  */
+#define GPT2L_ERR_NOT_INIT (-4)    /* gpt2_linear_init() has not run on this device        */
+#define GPT2L_ERR_TOO_LARGE (-5)   /* size beyond a documented fixed limit                 */
+#define GPT2L_ERR_SCHEDULE (-6)    /* megakernel schedule is malformed (see validate)      */
+/* positive device status: bit 0 = a bounded wait expired (dependency counter, mbarrier or
+ * split-K turnstile); the op index and counter are in gpt2_linear_last_status(). */
+#define GPT2L_DEV_TIMEOUT 1
+
+/* ---- options ---- */
+enum gpt2l_mode {
+  GPT2L_MODE_TF32 = 0,   /* one tcgen05.mma.kind::tf32 per product                          */
+  GPT2L_MODE_TF32X3 = 1  /* operands split hi+lo, three MMAs per product (fp32-faithful)    */
+};
+
+/* epilogue flags */
+#define GPT2L_EPI_GELU_DUAL 1u /* forward only: also store gelu(out) (tanh form) to opts->out2 */
+
+typedef struct gpt2_linear_opts {
+  int mode;          /* enum gpt2l_mode                                                     */
+  unsigned flags;    /* GPT2L_EPI_*                                                         */
+  int split_k;       /* backward_weight: number of M-splits; 0 = choose from the SM count   */
+  int deterministic; /* backward_weight with split_k>1: combine partials in a fixed order   */
+  float *out2;       /* second output for GPT2L_EPI_GELU_DUAL, [B*S][N]                     */
+  int force_simt;    /* 1 = run the CUDA-core fallback kernel even where TMA is possible    */
+} gpt2_linear_opts;
+
+/* One-time set-up for the current device: checks the architecture, raises the dynamic
+ * shared-memory limit of the kernels, allocates the status word, the split-K workspace
+ * and (for the *_host entry points) nothing else — staging buffers grow on demand.
+ * Must run before the first compute call on that device. Idempotent. */
+int gpt2_linear_init(int device);
+/* Releases what init allocated on every device. */
+void gpt2_linear_shutdown(void);
+/* Library version, for the binding's sanity check. */
+int gpt2_linear_version(void);
+/* Number of kernel launches this library issued since init (all entry points). */
+long long gpt2_linear_launch_count(void);
+/* Last device status record of the current device: {status, op, counter, seen, expected,
+ * where}. Returns the status word. out may be NULL. */
+int gpt2_linear_last_status(int out[6]);
+
+/*
+ * out[M][N] = in[M][K] . w[K][N] + b[N]        (M = B*S; b may be NULL)
+ * Replaces mlp_forward<32> (include/gpt2/layers/mlp.h:336-353; call sites
+ * src/train.cu:356,360,365,369,376 and megakernel cases 3,5,8,10,13 in src/mk.cu).
+ */
+int gpt2_linear_forward(float *out, const float *in, const float *w, const float *b,
+                        int B, int S, int K, int N,
+                        const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+
+/*
+ * g_in[M][K] = g_out[M][N] . w[K][N]^T          (overwrites g_in)
+ * Replaces mlp_backward_input<32> (mlp.h:653-670; src/train.cu:404,424,429,436,441;
+ * megakernel cases 17,21,24,28,31).
+ */
+int gpt2_linear_backward_input(float *g_in, const float *g_out, const float *w,
+                               int B, int S, int K, int N,
+                               const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+
+/*
+ * g_w[K][N] = in[M][K]^T . g_out[M][N]          (overwrites g_w)
+ * g_b[N]    = sum_m g_out[m][n]                 (overwrites g_b; g_b may be NULL)
+ * Replaces mlp_backward_weight<32> (mlp.h:998-1017, bias-grad at :970-995;
+ * src/train.cu:405,425,430,437,442; megakernel cases 18,22,25,29,32).
+ */
+int gpt2_linear_backward_weight(float *g_w, float *g_b, const float *g_out, const float *in,
+                                int B, int S, int K, int N,
+                                const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+
+/*
+ * The same three operations with HOST buffers: inputs are copied to the device, the
+ * kernel runs, outputs are copied back, the stream is synchronised. This is the call a
+ * host-side plugin user makes when their tensors live in host memory; staging buffers are
+ * kept and reused between calls. Pinned host memory makes the copies asynchronous.
+ */
+int gpt2_linear_forward_host(float *out, const float *in, const float *w, const float *b,
+                             int B, int S, int K, int N,
+                             const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+int gpt2_linear_backward_input_host(float *g_in, const float *g_out, const float *w,
+                                    int B, int S, int K, int N,
+                                    const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+int gpt2_linear_backward_weight_host(float *g_w, float *g_b, const float *g_out,
+                                     const float *in, int B, int S, int K, int N,
+                                     const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Megakernel side: one persistent launch that runs a list of GEMM ops whose tiles are
+ * ordered by dependency counters (the role of schedule_instructions / megakernel / bar[]
+ * in src/mk.cu:281-942, 974-1028, 1124-1131, 1821-1824 and include/gpt2/mk.h:14-34).
+ *
+ * Differences from the reference's contract, all deliberate:
+ *   - counters are per (op, 128-row block) as well as per op, so a consumer tile starts as
+ *     soon as the row block it reads is complete, not when the whole previous op is;
+ *   - every wait is bounded; on expiry the launch ends and returns GPT2L_DEV_TIMEOUT;
+ *   - tiles are handed to CTAs in one global order (tile t runs on CTA t mod grid), which
+ *     with backward-pointing dependencies cannot deadlock while all CTAs are resident.
+ * ------------------------------------------------------------------------------------ */
+
+enum gpt2l_op_kind {
+  GPT2L_OP_FORWARD = 0,
+  GPT2L_OP_BACKWARD_INPUT = 1,
+  GPT2L_OP_BACKWARD_WEIGHT = 2
+};
+
+#define GPT2L_MAX_DEPS 2
+/* what a dependency waits for */
+#define GPT2L_DEP_NONE 0
+#define GPT2L_DEP_ROWBLOCK 1 /* the producer's 128-row block with the same index as mine */
+#define GPT2L_DEP_WHOLE_OP 2 /* every tile of the producer                               */
+
+typedef struct gpt2l_dep {
+  int producer; /* index of an EARLIER op in the list                                     */
+  int kind;     /* GPT2L_DEP_*                                                             */
+} gpt2l_dep;
+
+/* One GEMM of the schedule, in the argument vocabulary of the three calls above. */
+typedef struct gpt2l_op {
+  int kind;            /* enum gpt2l_op_kind                                               */
+  int layer;           /* carried through to profiling records; not interpreted            */
+  int B, S, K, N;
+  float *out;          /* forward: out; backward_input: g_in; backward_weight: g_w         */
+  float *out_bias;     /* backward_weight: g_b or NULL; others: unused                     */
+  const float *a;      /* forward: in; backward_input: g_out; backward_weight: in          */
+  const float *b;      /* forward: w;  backward_input: w;     backward_weight: g_out       */
+  const float *bias;   /* forward: b or NULL                                               */
+  gpt2_linear_opts opts;
+  gpt2l_dep deps[GPT2L_MAX_DEPS];
+} gpt2l_op;
+
+typedef struct gpt2l_schedule gpt2l_schedule; /* opaque; owns device copies */
+
+/* Builds the device-side schedule (tensor maps, tile ranges, counters) for n_ops ops.
+ * Returns NULL and sets *err on failure. The op list is copied. */
+gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err);
+void gpt2_schedule_destroy(gpt2l_schedule *s);
+/* Host-only replay of the schedule with `grid` CTAs taking tiles round-robin: returns 0 if
+ * every wait is satisfied under the in-order execution model, GPT2L_ERR_SCHEDULE otherwise.
+ * Needs no GPU (used by the CPU tests). */
+int gpt2_schedule_validate(const gpt2l_op *ops, int n_ops, int grid);
+/* Host-only: fills counts[0]=total tiles, [1]=number of counters, [2]=grid the launch
+ * would use on a device with `num_sms` SMs. */
+int gpt2_schedule_describe(const gpt2l_op *ops, int n_ops, int num_sms, int counts[3]);
+/* Zeroes the counters and launches the persistent kernel once on `stream`. */
+int gpt2_megakernel_run(gpt2l_schedule *s, gpt2l_stream_t stream);
+/* After the stream has been synchronised: returns the device status of the last run. */
+int gpt2_megakernel_status(gpt2l_schedule *s);
+/* Test hook for the bounded-wait path: overrides the expected count of one dependency of
+ * one op in the device copy (host-side fault injection; no device fault is provoked) and
+ * the wait limit in milliseconds (0 keeps the default). */
+int gpt2_schedule_debug_set_expected(gpt2l_schedule *s, int op, int dep, int expected,
+                                     int wait_limit_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPT2_LINEAR_H */

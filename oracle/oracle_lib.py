@@ -1,0 +1,145 @@
+"""TEST INFRASTRUCTURE — ctypes loader of the CPU restatement (liboracle_linear.so) and of the
+reference's own CUDA kernels (_ref/libref_mlp.so). Imported only by tests/, by
+__graft_entry__.smoke() and by bench.py's CPU-baseline legs; the product never imports it."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "liboracle_linear.so")
+REF_SO = os.path.join(HERE, "_ref", "libref_mlp.so")
+
+
+def build(reference_root="/root/reference"):
+    """make the CPU oracle; make the reference-kernel library too when the reference tree exists."""
+    subprocess.run(["make", "-C", HERE], check=True, capture_output=True)
+    if os.path.exists(os.path.join(reference_root, "include", "gpt2", "layers", "mlp.h")):
+        subprocess.run(["make", "-C", HERE, "ref", f"REF={reference_root}"], check=True, capture_output=True)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        L = ctypes.CDLL(ORACLE_SO)
+        F = ctypes.POINTER(ctypes.c_float)
+        D = ctypes.POINTER(ctypes.c_double)
+        I = ctypes.c_int
+        L.oracle_linear_forward_f32.argtypes = [F, F, F, F, I, I, I, I]
+        L.oracle_linear_forward_f64.argtypes = [D, F, F, F, I, I, I, I]
+        L.oracle_linear_backward_input_f32.argtypes = [F, F, F, I, I, I, I]
+        L.oracle_linear_backward_input_f64.argtypes = [D, F, F, I, I, I, I]
+        L.oracle_linear_backward_weight_f32.argtypes = [F, F, F, F, I, I, I, I]
+        L.oracle_linear_backward_weight_f64.argtypes = [D, D, F, F, I, I, I, I]
+        L.oracle_gelu_f32.argtypes = [F, F, ctypes.c_long]
+        L.oracle_set_threads.argtypes = [I]
+        L.oracle_get_threads.restype = I
+        _lib = L
+    return _lib
+
+
+def _f(a):
+    return None if a is None else a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def _d(a):
+    return None if a is None else a.ctypes.data_as(ctypes.POINTER(ctypes.c_double))
+
+
+def _c(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def set_threads(n):
+    lib().oracle_set_threads(n)
+
+
+def get_threads():
+    return lib().oracle_get_threads()
+
+
+def forward(x, w, b=None, f64=False):
+    """x [M,K], w [K,N], b [N] or None -> y [M,N] (float32 reference order, or float64 truth)"""
+    x, w, b = _c(x), _c(w), _c(b)
+    M, K = x.shape
+    N = w.shape[1]
+    if f64:
+        out = np.empty((M, N), np.float64)
+        rc = lib().oracle_linear_forward_f64(_d(out), _f(x), _f(w), _f(b), M, 1, K, N)
+    else:
+        out = np.empty((M, N), np.float32)
+        rc = lib().oracle_linear_forward_f32(_f(out), _f(x), _f(w), _f(b), M, 1, K, N)
+    assert rc == 0
+    return out
+
+
+def backward_input(dy, w, f64=False):
+    """dy [M,N], w [K,N] -> dx [M,K]"""
+    dy, w = _c(dy), _c(w)
+    M, N = dy.shape
+    K = w.shape[0]
+    if f64:
+        out = np.empty((M, K), np.float64)
+        rc = lib().oracle_linear_backward_input_f64(_d(out), _f(dy), _f(w), M, 1, K, N)
+    else:
+        out = np.empty((M, K), np.float32)
+        rc = lib().oracle_linear_backward_input_f32(_f(out), _f(dy), _f(w), M, 1, K, N)
+    assert rc == 0
+    return out
+
+
+def backward_weight(dy, x, want_bias=True, f64=False):
+    """dy [M,N], x [M,K] -> (dw [K,N], db [N] or None)"""
+    dy, x = _c(dy), _c(x)
+    M, N = dy.shape
+    K = x.shape[1]
+    if f64:
+        dw = np.empty((K, N), np.float64)
+        db = np.empty((N,), np.float64) if want_bias else None
+        rc = lib().oracle_linear_backward_weight_f64(_d(dw), _d(db), _f(dy), _f(x), M, 1, K, N)
+    else:
+        dw = np.empty((K, N), np.float32)
+        db = np.empty((N,), np.float32) if want_bias else None
+        rc = lib().oracle_linear_backward_weight_f32(_f(dw), _f(db), _f(dy), _f(x), M, 1, K, N)
+    assert rc == 0
+    return dw, db
+
+
+def gelu(x):
+    x = _c(x)
+    out = np.empty_like(x)
+    lib().oracle_gelu_f32(_f(out), _f(x), x.size)
+    return out
+
+
+def max_rel_err(got, truth):
+    """max_i |got_i - truth_i| / max_i |truth_i| — the error metric of the parity thresholds"""
+    truth = np.asarray(truth, np.float64)
+    got = np.asarray(got, np.float64)
+    denom = np.max(np.abs(truth))
+    if denom == 0:
+        return float(np.max(np.abs(got)))
+    return float(np.max(np.abs(got - truth)) / denom)
+
+
+# ---- the reference's own CUDA kernels (GPU box only) ----
+_ref = None
+
+
+def ref_lib():
+    """Returns the library of reference kernels, or None when it was not built."""
+    global _ref
+    if _ref is None and os.path.exists(REF_SO):
+        L = ctypes.CDLL(REF_SO)
+        P, I = ctypes.c_void_p, ctypes.c_int
+        L.ref_mlp_forward.argtypes = [P, P, P, P, I, I, I, I, P]
+        L.ref_mlp_backward_input.argtypes = [P, P, P, I, I, I, I, P]
+        L.ref_mlp_backward_weight.argtypes = [P, P, P, P, I, I, I, I, P]
+        _ref = L
+    return _ref

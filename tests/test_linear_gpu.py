@@ -1,0 +1,203 @@
+"""GPU parity tests: the three linear-layer calls through the C ABI against the CPU oracle
+(float64 truth), on the same seeded inputs.
+
+Tolerances are the ones the specification of this path states: max relative error
+(max|y - y_ref| / max|y_ref|) <= 1e-2 in TF32 mode and <= 2e-3 in 3xTF32 mode.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import LAYERS, golden
+
+pytestmark = pytest.mark.gpu
+
+TOL = {0: 1e-2, 1: 2e-3}
+# what the modes actually deliver on N(0,1) x N(0,0.02) data (checked, so regressions show)
+TIGHT = {0: 2e-3, 1: 2e-5}
+
+
+def dev(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_all(g, x, w, b, dy, mode, want_bias=True, **okw):
+    """Runs forward / backward_input / backward_weight on the device; returns numpy outputs."""
+    M, K = x.shape
+    N = w.shape[1]
+    xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
+    y = torch.full((M, N), float("nan"), device="cuda")
+    dx = torch.full((M, K), float("nan"), device="cuda")
+    dw = torch.full((K, N), float("nan"), device="cuda")
+    db = torch.full((N,), float("nan"), device="cuda") if want_bias else None
+    o = g.make_opts(mode=mode, **okw)
+    g.check("forward", g.forward(y, xd, wd, bd, 1, M, K, N, o))
+    g.check("backward_input", g.backward_input(dx, dyd, wd, 1, M, K, N, o))
+    g.check("backward_weight", g.backward_weight(dw, db, dyd, xd, 1, M, K, N, o))
+    torch.cuda.synchronize()
+    st, rec = g.last_status()
+    assert st == 0, f"device status record {rec}"
+    return y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy(), None if db is None else db.cpu().numpy()
+
+
+def check_all(orc, outs, x, w, b, dy, tol):
+    y, dx, dw, db = outs
+    errs = {
+        "y": orc.max_rel_err(y, orc.forward(x, w, b, f64=True)),
+        "dx": orc.max_rel_err(dx, orc.backward_input(dy, w, f64=True)),
+    }
+    dw_t, db_t = orc.backward_weight(dy, x, want_bias=db is not None, f64=True)
+    errs["dw"] = orc.max_rel_err(dw, dw_t)
+    if db is not None:
+        errs["db"] = orc.max_rel_err(db, db_t)
+    for k, v in errs.items():
+        assert np.isfinite(v) and v <= tol, (k, v, errs)
+    return errs
+
+
+def seeded(M, K, N, seed=0):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    w = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    dy = (rng.standard_normal((M, N)) * 0.01).astype(np.float32)
+    return x, w, b, dy
+
+
+# shapes: aligned multiples of the tile, ragged in every dimension (still 16-byte strides),
+# tiny, one k-block, many k-blocks, and the B=4,T=64 GPT-2 small layer shapes
+SHAPES = [
+    (128, 32, 64), (128, 128, 256), (256, 768, 768), (384, 96, 320),
+    (4, 4, 4), (1, 8, 12), (129, 36, 68), (200, 100, 52), (130, 260, 516),
+    (256, 768, 2304), (256, 3072, 768), (256, 768, 3072),
+]
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("M,K,N", SHAPES)
+def test_parity_against_oracle(gpu, orc, M, K, N, mode):
+    x, w, b, dy = seeded(M, K, N, seed=M + K + N)
+    outs = run_all(gpu, x, w, b, dy, mode)
+    check_all(orc, outs, x, w, b, dy, TIGHT[mode])
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("fx", ["llm_tiny_aligned.npz", "llm_tiny_ragged.npz"])
+@pytest.mark.parametrize("layer", LAYERS)
+def test_parity_against_reference_model_fixtures(gpu, orc, fx, layer, mode):
+    """Same inputs the reference's PyTorch model saw; outputs compared with what it produced.
+    The ragged fixture's lm_head (vocabulary 101) exercises the CUDA-core kernel for shapes
+    TMA cannot address."""
+    z = golden(fx)
+    x, w, y, dy, dx, dw = (z[f"{layer}.{k}"] for k in ("x", "w", "y", "dy", "dx", "dw"))
+    b = z[f"{layer}.b"] if f"{layer}.b" in z else None
+    got = run_all(gpu, x, w, b, dy, mode, want_bias=b is not None)
+    assert orc.max_rel_err(got[0], y) <= TOL[mode]
+    assert orc.max_rel_err(got[1], dx) <= TOL[mode]
+    assert orc.max_rel_err(got[2], dw) <= TOL[mode]
+    if b is not None:
+        assert orc.max_rel_err(got[3], z[f"{layer}.db"]) <= TOL[mode]
+
+
+def test_null_bias_and_null_bias_grad(gpu, orc):
+    x, w, b, dy = seeded(256, 64, 128, seed=3)
+    y, dx, dw, db = run_all(gpu, x, w, None, dy, 0, want_bias=False)
+    assert db is None
+    assert orc.max_rel_err(y, orc.forward(x, w, None, f64=True)) <= TIGHT[0]
+
+
+def test_unaligned_shapes_use_cuda_core_kernel(gpu, orc):
+    """K or N not a multiple of 4 floats: no TMA; results are fp32-exact-ish."""
+    for (M, K, N) in [(70, 33, 50), (64, 64, 50257 % 1000), (5, 7, 9)]:
+        x, w, b, dy = seeded(M, K, N, seed=K)
+        outs = run_all(gpu, x, w, b, dy, 0)
+        check_all(orc, outs, x, w, b, dy, 1e-5)
+
+
+def test_force_simt_matches(gpu, orc):
+    x, w, b, dy = seeded(256, 128, 192, seed=9)
+    outs = run_all(gpu, x, w, b, dy, 0, force_simt=1)
+    check_all(orc, outs, x, w, b, dy, 1e-5)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("det", [0, 1])
+@pytest.mark.parametrize("splits", [2, 5])
+def test_split_k_weight_gradient(gpu, orc, splits, det, mode):
+    x, w, b, dy = seeded(1024, 128, 256, seed=splits)
+    outs = run_all(gpu, x, w, b, dy, mode, split_k=splits, deterministic=det)
+    check_all(orc, outs, x, w, b, dy, TIGHT[mode])
+
+
+def test_deterministic_split_is_bitwise_repeatable(gpu):
+    x, w, b, dy = seeded(2048, 128, 256, seed=21)
+    a = run_all(gpu, x, w, b, dy, 0, split_k=4, deterministic=1)
+    for _ in range(3):
+        c = run_all(gpu, x, w, b, dy, 0, split_k=4, deterministic=1)
+        assert np.array_equal(a[2], c[2]) and np.array_equal(a[3], c[3])
+
+
+def test_small_m_long_reduction_picks_splits(gpu, orc):
+    """lm_head-like backward_input at tiny M: few tiles, long reduction -> automatic split."""
+    x, w, b, dy = seeded(64, 128, 8192, seed=4)
+    outs = run_all(gpu, x, w, b, dy, 0)
+    check_all(orc, outs, x, w, b, dy, TIGHT[0])
+
+
+def test_gelu_dual_store(gpu, orc):
+    x, w, b, dy = seeded(300, 64, 256, seed=6)
+    M, K = x.shape
+    N = w.shape[1]
+    y = torch.empty((M, N), device="cuda")
+    y2 = torch.empty((M, N), device="cuda")
+    o = gpu.make_opts(mode=1, flags=gpu.EPI_GELU_DUAL, out2=y2.data_ptr())
+    gpu.check("forward", gpu.forward(y, dev(x), dev(w), dev(b), 1, M, K, N, o))
+    torch.cuda.synchronize()
+    pre = y.cpu().numpy()
+    assert orc.max_rel_err(pre, orc.forward(x, w, b, f64=True)) <= TIGHT[1]
+    assert np.allclose(y2.cpu().numpy(), orc.gelu(pre), atol=2e-6)
+
+
+def test_outputs_are_overwritten_not_accumulated(gpu, orc):
+    x, w, b, dy = seeded(256, 64, 128, seed=8)
+    first = run_all(gpu, x, w, b, dy, 1)
+    second = run_all(gpu, x, w, b, dy, 1)  # buffers pre-filled with NaN inside run_all
+    for a, c in zip(first, second):
+        assert np.array_equal(a, c)
+
+
+def test_host_buffer_entry_points(gpu, orc):
+    x, w, b, dy = seeded(512, 96, 160, seed=12)
+    M, K = x.shape
+    N = w.shape[1]
+    y = np.empty((M, N), np.float32)
+    dx = np.empty((M, K), np.float32)
+    dw = np.empty((K, N), np.float32)
+    db = np.empty((N,), np.float32)
+    o = gpu.make_opts(mode=1)
+    assert gpu.forward(y, x, w, b, 1, M, K, N, o, host=True) == 0
+    assert gpu.backward_input(dx, dy, w, 1, M, K, N, o, host=True) == 0
+    assert gpu.backward_weight(dw, db, dy, x, 1, M, K, N, o, host=True) == 0
+    check_all(orc, (y, dx, dw, db), x, w, b, dy, TIGHT[1])
+
+
+def test_linearity_at_full_size(gpu):
+    """Size-independent property at the benchmark's QKV shape (M = 8192): the forward is linear
+    in x, so f(x1) + f(x2) - f(0) == f(x1 + x2) up to TF32 rounding; 3xTF32 makes it tight."""
+    M, K, N = 8192, 768, 2304
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    x1 = torch.randn((M, K), device="cuda", generator=gen)
+    x2 = torch.randn((M, K), device="cuda", generator=gen)
+    w = torch.randn((K, N), device="cuda", generator=gen) * 0.02
+    b = torch.randn((N,), device="cuda", generator=gen) * 0.02
+    o = gpu.make_opts(mode=1)
+    outs = []
+    for xin in (x1, x2, x1 + x2, torch.zeros_like(x1)):
+        y = torch.empty((M, N), device="cuda")
+        gpu.check("forward", gpu.forward(y, xin, w, b, 8, 1024, K, N, o))
+        outs.append(y)
+    torch.cuda.synchronize()
+    lhs = outs[0] + outs[1] - outs[3]
+    rel = (lhs - outs[2]).abs().max().item() / outs[2].abs().max().item()
+    assert rel <= 1e-5, rel
+    assert torch.equal(outs[3], b.expand(M, N))  # x = 0 leaves exactly the bias
