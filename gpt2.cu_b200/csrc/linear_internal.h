@@ -71,6 +71,7 @@ struct alignas(64) GemmOp {
   long long ldc;
   int Mc, Nc, Kc;
   int a_mn, b_mn;       // 1 = MN-major
+  int a_3d, b_3d;       // MN-major operand fetched with one chunked 3-D copy per k-block
   int bn;               // 64 / 128 / 256
   int tiles_m, tiles_n, splits, kb_total, kb_per_split;
   int tile_base;        // global index of this op's first tile

@@ -242,12 +242,16 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
           const int k0 = kb * BK;
           if (!a_mn) {
             tma_load_2d(a_dst, &op->tmA, bar, k0, m0);
+          } else if (op->a_3d) {
+            tma_load_3d(a_dst, &op->tmA, bar, 0, k0, m0 >> 5);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + c * 4096, &op->tmA, bar, m0 + c * 32, k0);
           }
           if (!b_mn) {
             tma_load_2d(b_dst, &op->tmB, bar, k0, n0);
+          } else if (op->b_3d) {
+            tma_load_3d(b_dst, &op->tmB, bar, 0, k0, n0 >> 5);
           } else {
             for (int c = 0; c < bn / 32; ++c) tma_load_2d(b_dst + c * 4096, &op->tmB, bar, n0 + c * 32, k0);
           }
@@ -622,6 +626,22 @@ static int encode_map(CUtensorMap *map, const float *base, uint64_t inner, uint6
   return r == CUDA_SUCCESS ? GPT2L_OK : GPT2L_ERR_CUDA;
 }
 
+// MN-major operand whose contiguous extent is a multiple of 32: viewed as [inner/32][outer][32]
+// so that ONE copy lands every 32-column chunk of a tile (chunk c at offset c * 4096 bytes).
+static int encode_map_chunked(CUtensorMap *map, const float *base, uint64_t inner, uint64_t outer,
+                              uint32_t chunks) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return GPT2L_ERR_CUDA;
+  cuuint64_t dims[3] = {32, outer, inner / 32};
+  cuuint64_t strides[2] = {inner * sizeof(float), 32 * sizeof(float)};
+  cuuint32_t box[3] = {32, 32, chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Picks the tile width and the number of reduction splits: the pair that needs the fewest
@@ -713,8 +733,12 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
     case GPT2L_OP_BACKWARD_INPUT: a_inner = d.N; a_outer = d.M; b_inner = d.N; b_outer = d.K; break;
     default: a_inner = d.K; a_outer = d.M; b_inner = d.N; b_outer = d.M; break;
   }
-  e = encode_map(&op->tmA, d.a, a_inner, a_outer, 32, op->a_mn ? 32 : BM, op->a_mn);
+  op->a_3d = (op->a_mn && a_inner % 32 == 0) ? 1 : 0;
+  op->b_3d = (op->b_mn && b_inner % 32 == 0) ? 1 : 0;
+  if (op->a_3d) e = encode_map_chunked(&op->tmA, d.a, a_inner, a_outer, BM / 32);
+  else e = encode_map(&op->tmA, d.a, a_inner, a_outer, 32, op->a_mn ? 32 : BM, op->a_mn);
   if (e) return e;
+  if (op->b_3d) return encode_map_chunked(&op->tmB, d.b, b_inner, b_outer, op->bn / 32);
   return encode_map(&op->tmB, d.b, b_inner, b_outer, 32, op->b_mn ? 32 : op->bn, op->b_mn);
 }
 

@@ -190,6 +190,8 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
     GemmOp &g = s->plan.ops[i];
     g.tmA = full.tmA;
     g.tmB = full.tmB;
+    g.a_3d = full.a_3d;
+    g.b_3d = full.b_3d;
     ws_bytes += op_workspace_bytes(g);
     if (g.splits > 1 && !g.atomic_out) sem_count += (size_t)g.tiles_m * g.tiles_n * 4;
   }

@@ -1,0 +1,75 @@
+"""Data-parallel gradient exchange for the linear-layer path.
+
+The GEMM rows (B*T) are independent across sequences, so N GPUs each run the same GEMM set on
+their own batch and only the weight/bias gradients cross the links: one averaged all-reduce
+per bucket (NCCL over NVLink on GPUs, gloo in the CPU tests). Buckets are handed over in the
+order the backward pass finishes them, each on a side stream behind an event, so that the
+exchange of bucket i runs under the backward_weight GEMMs of bucket i+1.
+
+The reference is single-GPU (no collective anywhere in vnnm404/gpt2.cu); its flat gradient
+buffer g_model.params_memory (include/gpt2/gpt2.h:70) is what these buckets slice.
+"""
+import torch
+import torch.distributed as dist
+
+
+def plan_buckets(named_sizes, bucket_bytes):
+    """Groups (name, numel) pairs, kept in the given order, into buckets of at most
+    `bucket_bytes` (fp32); a tensor larger than the limit gets a bucket of its own.
+    Returns a list of lists of names."""
+    buckets, cur, cur_bytes = [], [], 0
+    for name, numel in named_sizes:
+        nbytes = 4 * int(numel)
+        if cur and cur_bytes + nbytes > bucket_bytes:
+            buckets.append(cur)
+            cur, cur_bytes = [], 0
+        cur.append(name)
+        cur_bytes += nbytes
+    if cur:
+        buckets.append(cur)
+    return buckets
+
+
+class GradientExchange:
+    """Averages gradient tensors across the ranks of `group`, overlapped with compute.
+
+    exchange(tensors) is called right after the kernels that produce `tensors` were enqueued on
+    the current stream; finish() makes the current stream wait for every exchange issued so far.
+    With world_size 1 both are no-ops (nothing to exchange)."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.comm_stream = None
+        self.pending = []
+        self.calls = 0
+
+    def exchange(self, tensors):
+        if self.world == 1:
+            return
+        tensors = [t for t in tensors if t is not None]
+        if not tensors:
+            return
+        self.calls += 1
+        if tensors[0].is_cuda:
+            if self.comm_stream is None:
+                self.comm_stream = torch.cuda.Stream()
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                for t in tensors:
+                    dist.all_reduce(t, op=dist.ReduceOp.AVG, group=self.group)
+                done = torch.cuda.Event()
+                done.record()
+            self.pending.append(done)
+        else:
+            # gloo has no AVG: sum, then scale
+            for t in tensors:
+                dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+                t.div_(self.world)
+
+    def finish(self):
+        for ev in self.pending:
+            torch.cuda.current_stream().wait_event(ev)
+        self.pending = []
