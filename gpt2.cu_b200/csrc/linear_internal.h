@@ -29,7 +29,9 @@ constexpr int XFORM_WARP0 = 2;
 constexpr int NUM_XFORM_WARPS = 4;
 constexpr int NUM_EPI_WARPS = 4;
 constexpr int SMEM_CTRL_BYTES = 512;  // mbarriers + tmem pointer + abort flag
-constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + RING_BYTES + SMEM_CTRL_BYTES;
+constexpr int EPI_BUF_BYTES = 32 * 32 * 4;                       // one 32 x 32 fp32 store box
+constexpr int EPI_BYTES = NUM_EPI_WARPS * 2 * EPI_BUF_BYTES;    // two boxes per epilogue warp
+constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + RING_BYTES + EPI_BYTES + SMEM_CTRL_BYTES;
 
 constexpr int MAX_WAITS = GPT2L_MAX_DEPS;
 
@@ -61,6 +63,8 @@ struct Status {
 struct alignas(64) GemmOp {
   CUtensorMap tmA;  // box {32, 128} (K-major) or {32, 32} (MN-major)
   CUtensorMap tmB;  // box {32, bn}  (K-major) or {32, 32} (MN-major)
+  CUtensorMap tmC;  // output, box {32, 32}: epilogue stores / split-K reduce-adds
+  CUtensorMap tmC2; // second output of the GELU dual store
   float *C;
   float *C2;            // gelu(C) when flags & GPT2L_EPI_GELU_DUAL
   const float *bias;    // [Nc] or null

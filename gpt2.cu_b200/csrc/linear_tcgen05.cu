@@ -168,7 +168,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t ring = (raw + 1023u) & ~1023u;
   uint8_t *ring_ptr = smem_raw + (ring - raw);
-  Ctrl *ctrl = reinterpret_cast<Ctrl *>(ring_ptr + RING_BYTES);
+  Ctrl *ctrl = reinterpret_cast<Ctrl *>(ring_ptr + RING_BYTES + EPI_BYTES);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -417,6 +417,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
   } else {
     // =============================== epilogue ===============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t epi_base = ring + RING_BYTES + (uint32_t)(warp - EPI_WARP0) * 2u * EPI_BUF_BYTES;
+    uint32_t epi_cc = 0;  // boxes this warp has handed to the copy engine so far
     int cursor = 0;
     uint32_t tcount = 0;
     bool ok = true;
@@ -447,56 +449,61 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
                   (size_t)(q * 32 + lane) * bn;
 
+      if (!det_split) {
+        // ---- staged path: registers -> swizzled 32x32 box in shared memory -> TMA store (or
+        // TMA reduce-add for split-K partials). The copy engine clips rows/columns outside C.
+        const int row0 = tc.m_tile * BM + q * 32;
+        for (int c = 0; c < bn / 32; ++c) {
+          const int nb = n0 + c * 32;
+          if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (add_bias && nb + 4 * j < Nc) bv = __ldg(reinterpret_cast<const float4 *>(op->bias + nb) + j);
+            v[4 * j + 0] = __uint_as_float(r[4 * j + 0]) + bv.x;
+            v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + bv.y;
+            v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
+            v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
+          }
+          for (int pass = 0; pass < (dual ? 2 : 1); ++pass, ++epi_cc) {
+            const uint32_t sbuf = epi_base + (epi_cc & 1u) * EPI_BUF_BYTES;
+            if (epi_cc >= 2) {
+              if (lane == 0) bulk_wait_read<1>();  // the box written two chunks ago has been read
+              __syncwarp();
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t a = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
+              if (pass == 0) st_shared_v4(a, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              else st_shared_v4(a, gelu_tanh(v[4 * j]), gelu_tanh(v[4 * j + 1]), gelu_tanh(v[4 * j + 2]),
+                                gelu_tanh(v[4 * j + 3]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (op->atomic_out) tma_reduce_add_2d(&op->tmC, sbuf, nb, row0);
+              else tma_store_2d(pass == 0 ? &op->tmC : &op->tmC2, sbuf, nb, row0);
+              bulk_commit();
+            }
+          }
+        }
+      } else
       for (int c = 0; c < bn / 32; ++c) {
         const int nb = n0 + c * 32;
         if (nb >= Nc) break;  // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (det_split) {
+        {
           float4 *dst = reinterpret_cast<float4 *>(ws_tile + c * 32);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-          continue;
-        }
-        if (row >= Mc) continue;
-        float *dst = op->C + (long long)row * ldc + nb;
-        const bool full = (nb + 32 <= Nc);
-        if (full) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-            if (add_bias) {
-              const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + nb) + j);
-              v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-            }
-            if (op->atomic_out) {
-              red_add_v4(dst + 4 * j, v.x, v.y, v.z, v.w);
-            } else {
-              reinterpret_cast<float4 *>(dst)[j] = v;
-              if (dual) {
-                float4 g = make_float4(gelu_tanh(v.x), gelu_tanh(v.y), gelu_tanh(v.z), gelu_tanh(v.w));
-                reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + nb)[j] = g;
-              }
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (nb + j < Nc) {
-              float v = __uint_as_float(r[j]);
-              if (add_bias) v += __ldg(op->bias + nb + j);
-              if (op->atomic_out) {
-                atomicAdd(dst + j, v);
-              } else {
-                dst[j] = v;
-                if (dual) op->C2[(long long)row * ldc + nb + j] = gelu_tanh(v);
-              }
-            }
-          }
         }
       }
       // the accumulator is in registers / memory now: hand the TMEM buffer back
@@ -555,6 +562,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
 
       // ---- publish: everything this warp stored is visible before the counters move
       if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
+        if (lane == 0) bulk_wait_all();  // the copy engine's writes of this tile are complete
         __threadfence();
         __syncwarp();
         if (lane == 0) {
@@ -564,6 +572,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       }
     }
   }
+
+  if (warp >= EPI_WARP0 && lane == 0) bulk_wait_all();  // shared memory stays valid until the stores have read it
 
   // =============================== teardown ===============================
   if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
@@ -738,8 +748,13 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   if (op->a_3d) e = encode_map_chunked(&op->tmA, d.a, a_inner, a_outer, BM / 32);
   else e = encode_map(&op->tmA, d.a, a_inner, a_outer, 32, op->a_mn ? 32 : BM, op->a_mn);
   if (e) return e;
-  if (op->b_3d) return encode_map_chunked(&op->tmB, d.b, b_inner, b_outer, op->bn / 32);
-  return encode_map(&op->tmB, d.b, b_inner, b_outer, 32, op->b_mn ? 32 : op->bn, op->b_mn);
+  if (op->b_3d) e = encode_map_chunked(&op->tmB, d.b, b_inner, b_outer, op->bn / 32);
+  else e = encode_map(&op->tmB, d.b, b_inner, b_outer, 32, op->b_mn ? 32 : op->bn, op->b_mn);
+  if (e) return e;
+  e = encode_map(&op->tmC, op->C, (uint64_t)op->Nc, (uint64_t)op->Mc, 32, 32, false);
+  if (e) return e;
+  if (op->C2) e = encode_map(&op->tmC2, op->C2, (uint64_t)op->Nc, (uint64_t)op->Mc, 32, 32, false);
+  return e;
 }
 
 size_t op_workspace_bytes(const GemmOp &op) {

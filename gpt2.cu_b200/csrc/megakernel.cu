@@ -190,6 +190,8 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
     GemmOp &g = s->plan.ops[i];
     g.tmA = full.tmA;
     g.tmB = full.tmB;
+    g.tmC = full.tmC;
+    g.tmC2 = full.tmC2;
     g.a_3d = full.a_3d;
     g.b_3d = full.b_3d;
     ws_bytes += op_workspace_bytes(g);

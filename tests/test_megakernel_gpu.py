@@ -85,7 +85,7 @@ def test_whole_gemm_set_in_one_launch(gpu):
     M = B * S
     o = gpu.make_opts(mode=0, deterministic=1)
     gen = torch.Generator(device="cuda").manual_seed(3)
-    ops, outs, refs = [], [], []
+    ops, outs, refs, keep = [], [], [], []
     for (K, N) in [(C, 3 * C), (C, C), (C, 4 * C), (4 * C, C), (C, V)]:
         x = torch.randn((M, K), device="cuda", generator=gen)
         w = torch.randn((K, N), device="cuda", generator=gen) * 0.02
@@ -96,6 +96,7 @@ def test_whole_gemm_set_in_one_launch(gpu):
                 gpu.make_op(gpu.OP_BACKWARD_INPUT, B, S, K, N, dx, dy, w, opts=o),
                 gpu.make_op(gpu.OP_BACKWARD_WEIGHT, B, S, K, N, dw, x, dy, out_bias=db, opts=o)]
         outs.append((y, dx, dw, db))
+        keep.append((x, w, b, dy))  # the schedule holds raw pointers: the operands must stay allocated
         refs.append((x @ w + b, dy @ w.t(), x.t() @ dy, dy.sum(0)))
     torch.backends.cuda.matmul.allow_tf32 = False
     sched = gpu.Schedule(ops)
