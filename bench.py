@@ -258,16 +258,22 @@ def run_ours(args):
     mode = g.MODE_TF32X3 if args.mode == "tf32x3" else g.MODE_TF32
     opts = g.make_opts(mode=mode)
 
+    rows = args.rows
+    seq = SEQ if rows % SEQ == 0 else rows
+    batch = rows // seq
+    only = set(args.only.split(",")) if args.only else None
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     bufs = []
     for name, K, N in LAYERS:
+        if only and not any(o.startswith(name + ".") for o in only):
+            continue
         d = {
-            "x": torch.randn((M_ROWS, K), device="cuda", generator=gen),
+            "x": torch.randn((rows, K), device="cuda", generator=gen),
             "w": torch.randn((K, N), device="cuda", generator=gen) * 0.02,
             "b": None if name == "lm_head" else torch.randn((N,), device="cuda", generator=gen) * 0.02,
-            "dy": torch.randn((M_ROWS, N), device="cuda", generator=gen) * 0.01,
-            "y": torch.empty((M_ROWS, N), device="cuda"),
-            "dx": torch.empty((M_ROWS, K), device="cuda"),
+            "dy": torch.randn((rows, N), device="cuda", generator=gen) * 0.01,
+            "y": torch.empty((rows, N), device="cuda"),
+            "dx": torch.empty((rows, K), device="cuda"),
             "dw": torch.empty((K, N), device="cuda"),
             "db": None if name == "lm_head" else torch.empty((N,), device="cuda"),
         }
@@ -279,11 +285,14 @@ def run_ours(args):
     def one_step(timed_events=None):
         for name, K, N, d in bufs:
             calls = (
-                lambda: g.forward(d["y"], d["x"], d["w"], d["b"], BATCH, SEQ, K, N, opts, stream),
-                lambda: g.backward_input(d["dx"], d["dy"], d["w"], BATCH, SEQ, K, N, opts, stream),
-                lambda: g.backward_weight(d["dw"], d["db"], d["dy"], d["x"], BATCH, SEQ, K, N, opts, stream),
+                ("fwd", lambda: g.forward(d["y"], d["x"], d["w"], d["b"], batch, seq, K, N, opts, stream)),
+                ("dgrad", lambda: g.backward_input(d["dx"], d["dy"], d["w"], batch, seq, K, N, opts, stream)),
+                ("wgrad", lambda: g.backward_weight(d["dw"], d["db"], d["dy"], d["x"], batch, seq, K, N, opts,
+                                                    stream)),
             )
-            for fn in calls:
+            for kind, fn in calls:
+                if only and f"{name}.{kind}" not in only:
+                    continue
                 if timed_events is not None:
                     s = torch.cuda.Event(enable_timing=True)
                     e = torch.cuda.Event(enable_timing=True)
@@ -330,7 +339,21 @@ def run_ours(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         elapsed_ms, kernel_ms = tt.tolist()
     ms_per_step = elapsed_ms / args.steps
-    value = step_flops() * world / (ms_per_step * 1e-3) / 1e12
+    if only:
+        flops_step = sum(2.0 * rows * K * N for n_, K, N in LAYERS for k_ in KINDS if f"{n_}.{k_}" in only)
+    else:
+        flops_step = step_flops(rows)
+    value = flops_step * world / (ms_per_step * 1e-3) / 1e12
+    if only or args.no_e2e or rows != M_ROWS:
+        # reduced run (profiling aid): kernel-only numbers, no end-to-end / CPU legs
+        if rank == 0:
+            print(json.dumps({"partial": True, "only": sorted(only) if only else None, "rows": rows,
+                              "value": value, "unit": "TFLOP/s", "ms_per_step": ms_per_step,
+                              "kernel_ms_per_step": kernel_ms / args.steps, "gpu_launches": int(launches),
+                              "clocks": clocks}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
 
     # ---- end to end through the host-buffer entry points (rank-local, all ranks in parallel)
     e2e = measure_e2e(g, torch, opts, stream, world, barrier, dist if world > 1 else None,
@@ -344,14 +367,14 @@ def run_ours(args):
     peaks = load_peaks()
     peak_tf32 = peaks["bf16_sustained"] / 2.0
     n_launch = len(ev_pairs)
-    achieved = step_flops() * args.steps / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else None
+    achieved = flops_step * args.steps / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else None
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak_tf32, "unit": "TFLOP/s",
         "frac": (achieved / peak_tf32) if achieved else None,
         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
         "kernel": "gpt2_linear_tcgen05_kernel", "launches_timed": n_launch,
         "avg_launch_ms": kernel_ms / n_launch if n_launch else None,
-        "flops_per_launch": step_flops() / 15.0,
+        "flops_per_launch": flops_step / 15.0,
         "peak_source": f"MEASURED_PEAKS.json bf16 sustained {peaks['bf16_sustained']} TF/s / 2 (TF32 rate), of "
                        f"{peaks['source']}; burst figure would be {peaks['bf16_burst'] / 2.0}",
     }
@@ -428,6 +451,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="tf32", choices=["tf32", "tf32x3"])
+    ap.add_argument("--rows", type=int, default=M_ROWS, help="rows per GPU (profiling aid; default is the workload)")
+    ap.add_argument("--only", default="", help="comma list like lm_head.fwd,qkv.wgrad (profiling aid)")
+    ap.add_argument("--no-e2e", dest="no_e2e", action="store_true", help="kernel-only run (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

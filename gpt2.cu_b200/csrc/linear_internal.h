@@ -78,6 +78,7 @@ struct alignas(64) GemmOp {
   int a_3d, b_3d;       // MN-major operand fetched with one chunked 3-D copy per k-block
   int bn;               // 64 / 128 / 256
   int tiles_m, tiles_n, splits, kb_total, kb_per_split;
+  int band_m;           // rasterisation: tile rows per band (see decode_local)
   int tile_base;        // global index of this op's first tile
   int n_tiles;          // tiles_m * tiles_n * splits
   int mode;             // gpt2l_mode
@@ -100,6 +101,7 @@ struct LaunchParams {
   Status *status;
   unsigned *counters;
   long long wait_limit_ns;
+  int xform_active;  // 0: no op needs the transform warps (TF32 mode, no fused bias gradient)
 };
 
 // host-side description used to build a GemmOp
@@ -140,11 +142,26 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op);
 // The host-only part of build_op (no tensor maps, no CUDA calls): shapes, tiling, descriptor bits.
 int plan_op(const GemmDesc &d, int num_sms, GemmOp *op);
 long long launch_count_value();
+// tile index inside an op -> (tile row, tile column, split); shared by the kernel and the host replay
+__host__ __device__ __forceinline__ void decode_local(int local, int tiles_m, int tiles_n, int band_m,
+                                                      int &m_tile, int &n_tile, int &split) {
+  const int per_split = tiles_m * tiles_n;
+  split = local / per_split;
+  const int l = local - split * per_split;
+  const int band_size = band_m * tiles_n;
+  const int band = l / band_size;
+  const int rem = l - band * band_size;
+  const int left = tiles_m - band * band_m;
+  const int gb = left < band_m ? left : band_m;
+  n_tile = rem / gb;
+  m_tile = band * band_m + (rem - n_tile * gb);
+}
+
 // bytes of deterministic split-K workspace the op needs (0 if none)
 size_t op_workspace_bytes(const GemmOp &op);
 int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream);
 int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid,
-                bool any_3x, Status *d_status, unsigned *d_counters, long long wait_limit_ns,
+                bool any_3x, bool any_colsum, Status *d_status, unsigned *d_counters, long long wait_limit_ns,
                 cudaStream_t stream);
 int set_kernel_attributes();
 void count_launch(int n = 1);

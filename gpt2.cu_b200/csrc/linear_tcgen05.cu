@@ -62,17 +62,16 @@ struct Tile {
 };
 
 // Advances `cursor` to the op that owns global tile `t` and decodes the tile.
-// Order inside an op: n fastest, then m, then split — tiles that run at the same time share
-// the same k-range of both operands in L2.
+// Order inside an op: splits outermost (tiles that run together share a k-range); inside a
+// split the output tiles are walked in bands of `band_m` tile rows, row index fastest inside a
+// band. The ~148 tiles in flight then cover band_m rows x a few columns of tiles: the A rows of
+// the band stay in L2 for the whole sweep and every B column block is fetched from HBM once
+// per band instead of once per tile row.
 __device__ __forceinline__ const GemmOp *decode_tile(const GemmOp *ops, int n_ops, int t, int &cursor,
                                                      Tile &tc) {
   while (cursor + 1 < n_ops && t >= ops[cursor].tile_base + ops[cursor].n_tiles) ++cursor;
   const GemmOp *op = ops + cursor;
-  int local = t - op->tile_base;
-  tc.n_tile = local % op->tiles_n;
-  int rest = local / op->tiles_n;
-  tc.m_tile = rest % op->tiles_m;
-  tc.split = rest / op->tiles_m;
+  decode_local(t - op->tile_base, op->tiles_m, op->tiles_n, op->band_m, tc.m_tile, tc.n_tile, tc.split);
   tc.kb0 = tc.split * op->kb_per_split;
   int kb1 = tc.kb0 + op->kb_per_split;
   tc.kb1 = kb1 < op->kb_total ? kb1 : op->kb_total;
@@ -93,12 +92,16 @@ __device__ __noinline__ void raise_timeout(Ctrl *ctrl, const LaunchParams &p, in
 }
 
 // true = the phase completed; false = abort (ours or another CTA's) or the limit ran out.
+// `backoff_ns` > 0 parks the polling lane between probes (waits that last microseconds and are not
+// on the critical path: epilogue, producer), so that spinning does not eat the issue slots the
+// MMA and epilogue warps need.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl *ctrl, const LaunchParams &p,
-                                         int site, int op, int idx) {
+                                         int site, int op, int idx, unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   for (;;) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 127u) == 0) {
       if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
@@ -177,7 +180,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
   if (tid == 0) {
     for (int s = 0; s < STAGES_1X; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), 1);
-      mbar_init(smem_u32(&ctrl->empty[s]), 1 + NUM_XFORM_WARPS);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1 + (p.xform_active ? NUM_XFORM_WARPS : 0));
       mbar_init(smem_u32(&ctrl->ready[s]), NUM_XFORM_WARPS);
     }
     for (int a = 0; a < NUM_ACC; ++a) {
@@ -231,7 +234,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         const uint32_t ph = (it / NST) & 1u;
         int okl = 1;
         if (lane == 0)
-          okl = wait_bar(smem_u32(&ctrl->empty[s]), ph ^ 1u, ctrl, p, SITE_SMEM_EMPTY, op->op_index, s);
+          okl = wait_bar(smem_u32(&ctrl->empty[s]), ph ^ 1u, ctrl, p, SITE_SMEM_EMPTY, op->op_index, s, 32);
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
         if (!ok) break;
         if (lane == 0) {
@@ -271,7 +274,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const uint32_t aph = (tcount >> 1) & 1u;
       int okl = 1;
       if (lane == 0)
-        okl = wait_bar(smem_u32(&ctrl->tmem_empty[as]), aph ^ 1u, ctrl, p, SITE_TMEM_EMPTY, op->op_index, as);
+        okl = wait_bar(smem_u32(&ctrl->tmem_empty[as]), aph ^ 1u, ctrl, p, SITE_TMEM_EMPTY, op->op_index, as, 32);
       ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -325,6 +328,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     }
   } else if (warp < EPI_WARP0) {
     // =============================== operand transform ===============================
+    // (these warps leave at once when no op of the launch needs a split or a column sum)
+    if (p.xform_active) {
     const int x = tid - XFORM_WARP0 * 32;  // 0..127
     int cursor = 0;
     uint32_t it = 0;
@@ -349,7 +354,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         const uint32_t ph = (it / NST) & 1u;
         int okl = 1;
         if (lane == 0)
-          okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
+          okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s, X3 ? 0 : 64);
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
         if (!ok) break;
         uint8_t *stage = ring_ptr + s * STAGE_STRIDE;
@@ -414,6 +419,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         }
       }
     }
+    }
   } else {
     // =============================== epilogue ===============================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -429,7 +435,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const uint32_t aph = (tcount >> 1) & 1u;
       int okl = 1;
       if (lane == 0)
-        okl = wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as);
+        okl = wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128);
       ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -725,6 +731,15 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   op->tiles_m = ceil_div(op->Mc, BM);
   op->tiles_n = ceil_div(op->Nc, bn);
   op->n_tiles = op->tiles_m * op->tiles_n * op->splits;
+  {
+    // band height: as many tile rows as keep the band's A rows (of one split) within ~48 MB of L2
+    const double a_bytes_per_tile_row = (double)BM * (double)op->kb_per_split * BK * 4.0;
+    int g = (int)(48.0 * 1024 * 1024 / a_bytes_per_tile_row);
+    if (g < 1) g = 1;
+    if (g > op->tiles_m) g = op->tiles_m;
+    const int bands = ceil_div(op->tiles_m, g);
+    op->band_m = ceil_div(op->tiles_m, bands);  // balanced bands
+  }
   op->atomic_out = (op->splits > 1 && !d.opts.deterministic && !op->C2) ? 1 : 0;
   op->idesc = make_idesc_tf32(BM, bn, op->a_mn, op->b_mn);
   for (int w = 0; w < MAX_WAITS; ++w) { op->wait_ctr[w] = -1; op->wait_kind[w] = 0; op->wait_expected[w] = 0; }
@@ -783,6 +798,7 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.status = ctx->d_status;
   p.counters = nullptr;
   p.wait_limit_ns = default_wait_limit_ns();
+  p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
   const int grid = op.n_tiles < ctx->num_sms ? op.n_tiles : ctx->num_sms;
   if (op.mode == GPT2L_MODE_TF32X3)
     gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
@@ -792,7 +808,7 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }
 
-int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid, bool any_3x,
+int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid, bool any_3x, bool any_colsum,
                 Status *d_status, unsigned *d_counters, long long wait_limit_ns, cudaStream_t stream) {
   (void)ctx;
   static GemmOp dummy;  // the by-value slot is unused when a list is given
@@ -803,6 +819,7 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
   p.status = d_status;
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
+  p.xform_active = (any_3x || any_colsum) ? 1 : 0;
   if (any_3x)
     gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);
   else

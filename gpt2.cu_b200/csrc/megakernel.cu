@@ -22,6 +22,7 @@ struct Plan {
   int total_tiles = 0;
   int n_counters = 0;
   bool any_3x = false;
+  bool any_colsum = false;
 };
 
 static GemmDesc desc_from(const gpt2l_op &o) {
@@ -59,6 +60,7 @@ static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
     g.pub_op_ctr = ctr + g.tiles_m;
     ctr += g.tiles_m + 1;
     if (g.mode == GPT2L_MODE_TF32X3) plan->any_3x = true;
+    if (g.colsum) plan->any_colsum = true;
   }
   for (int i = 0; i < n_ops; ++i) {
     GemmOp &g = plan->ops[i];
@@ -104,8 +106,8 @@ static int replay(const Plan &plan, int grid) {
         int &cur = cursor[c];
         while (cur + 1 < (int)plan.ops.size() && t >= plan.ops[cur].tile_base + plan.ops[cur].n_tiles) ++cur;
         const GemmOp &g = plan.ops[cur];
-        const int local = t - g.tile_base;
-        const int m_tile = (local / g.tiles_n) % g.tiles_m;
+        int m_tile, n_tile, split;
+        decode_local(t - g.tile_base, g.tiles_m, g.tiles_n, g.band_m, m_tile, n_tile, split);
         bool ready = true;
         for (int w = 0; w < MAX_WAITS; ++w) {
           if (g.wait_ctr[w] < 0) continue;
@@ -253,7 +255,7 @@ int gpt2_megakernel_run(gpt2l_schedule *s, gpt2l_stream_t stream) {
         return GPT2L_ERR_CUDA;
     }
   }
-  return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x,
+  return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x, s->plan.any_colsum,
                      s->d_status, s->d_counters, s->wait_limit_ns, st);
 }
 
