@@ -43,6 +43,7 @@ EXPORTS = [
     "gpt2_linear_last_status",
     "gpt2_linear_forward", "gpt2_linear_backward_input", "gpt2_linear_backward_weight",
     "gpt2_linear_forward_host", "gpt2_linear_backward_input_host", "gpt2_linear_backward_weight_host",
+    "gpt2_linear_backward_weight_noalloc",
     "gpt2_schedule_create", "gpt2_schedule_destroy", "gpt2_schedule_validate", "gpt2_schedule_describe",
     "gpt2_megakernel_run", "gpt2_megakernel_status", "gpt2_schedule_debug_set_expected",
 ]
@@ -111,7 +112,8 @@ def _load():
         f = getattr(lib, name)
         f.argtypes = [P, P, P, I, I, I, I, OP, V]
         f.restype = I
-    for name in ("gpt2_linear_backward_weight", "gpt2_linear_backward_weight_host"):
+    for name in ("gpt2_linear_backward_weight", "gpt2_linear_backward_weight_host",
+                 "gpt2_linear_backward_weight_noalloc"):
         f = getattr(lib, name)
         f.argtypes = [P, P, P, P, I, I, I, I, OP, V]
         f.restype = I
@@ -173,6 +175,13 @@ def backward_input(g_in, g_out, w, B, S, K, N, opts=None, stream=None, host=Fals
 def backward_weight(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=None, host=False):
     fn = lib.gpt2_linear_backward_weight_host if host else lib.gpt2_linear_backward_weight
     return fn(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def backward_weight_noalloc(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=None):
+    """gpt2_linear_backward_weight_noalloc: deterministic split-K weight gradient whose workspace is a
+    fixed array in the library image (for callers that must not allocate device memory)."""
+    return lib.gpt2_linear_backward_weight_noalloc(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N,
+                                                   ctypes.byref(opts) if opts else None, stream)
 
 
 def last_status():

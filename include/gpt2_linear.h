@@ -122,6 +122,37 @@ int gpt2_linear_backward_weight_host(float *g_w, float *g_b, const float *g_out,
                                      const float *in, int B, int S, int K, int N,
                                      const gpt2_linear_opts *opts, gpt2l_stream_t stream);
 
+/*
+ * Weight gradient for callers that may not allocate device memory. (No counterpart in the
+ * reference, which allocates everything up front and has no split-K.)
+ *
+ * Computes exactly what gpt2_linear_backward_weight computes with opts->deterministic = 1 — the
+ * reduction over M split into chunks whose partial tiles are combined in a fixed order — but keeps
+ * the partial tiles in a fixed array inside the library image instead of a cudaMalloc'ed
+ * workspace. Use it from code that runs after a server has given the whole GPU to its own memory
+ * pool, from loops that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply,
+ * or wherever a driver allocation at call time is simply forbidden. It does not need
+ * gpt2_linear_init() and calls no cudaMalloc, cudaFree or other allocating routine, ever.
+ *
+ * Limits and rules:
+ *   - the partial tiles (splits x ceil(K/128) x ceil(N/bn) tiles of 128 x bn floats) must fit in
+ *     GPT2L_NOALLOC_MAX_WORKSPACE_BYTES. A split count forced through opts->split_k that does not
+ *     fit returns GPT2L_ERR_TOO_LARGE; an automatic one is lowered until it fits (a single split
+ *     needs no workspace, so large weight matrices still run, just without the split);
+ *   - at most 4096 output tiles when splitting (else GPT2L_ERR_TOO_LARGE);
+ *   - the first call on each device resolves the array's device address and configures the
+ *     kernels; make that first call outside of any stream capture;
+ *   - the array is shared by every call on the device and keeps the previous call's contents;
+ *     each call re-zeroes the part that must start at zero, on the caller's stream. Two calls whose
+ *     kernels overlap on the GPU (different streams, or different threads) race on it: serialise
+ *     them. Every GPU that loads the library holds the array until the process exits;
+ *   - opts->flags and opts->out2 are ignored; opts->mode and opts->split_k are honoured.
+ */
+#define GPT2L_NOALLOC_MAX_WORKSPACE_BYTES (32u << 20)
+int gpt2_linear_backward_weight_noalloc(float *g_w, float *g_b, const float *g_out, const float *in,
+                                        int B, int S, int K, int N,
+                                        const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+
 /* ------------------------------------------------------------------------------------
  * Megakernel side: one persistent launch that runs a list of GEMM ops whose tiles are
  * ordered by dependency counters (the role of schedule_instructions / megakernel / bar[]
