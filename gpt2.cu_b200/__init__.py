@@ -58,6 +58,7 @@ class Opts(ctypes.Structure):
         ("deterministic", ctypes.c_int),
         ("out2", ctypes.c_void_p),
         ("force_simt", ctypes.c_int),
+        ("cta_pair", ctypes.c_int),
     ]
 
 
@@ -147,8 +148,8 @@ def init(device=0):
     check("gpt2_linear_init", lib.gpt2_linear_init(device))
 
 
-def make_opts(mode=MODE_TF32, flags=0, split_k=0, deterministic=0, out2=None, force_simt=0):
-    return Opts(mode, flags, split_k, deterministic, out2, force_simt)
+def make_opts(mode=MODE_TF32, flags=0, split_k=0, deterministic=0, out2=None, force_simt=0, cta_pair=0):
+    return Opts(mode, flags, split_k, deterministic, out2, force_simt, cta_pair)
 
 
 def _p(t):

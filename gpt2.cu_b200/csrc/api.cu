@@ -132,8 +132,11 @@ int gpt2_linear_init(int device) {
   if (!get_encode_fn()) return GPT2L_ERR_CUDA;
   int e = set_kernel_attributes();
   if (e) return e;
+  e = pair_set_kernel_attributes();
+  if (e) return e;
   c.device = device;
   c.num_sms = prop.multiProcessorCount;
+  c.max_pairs = pair_max_pairs(c.num_sms);
   if (cudaMalloc(reinterpret_cast<void **>(&c.d_status), sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;
   cudaMemset(c.d_status, 0, sizeof(Status));
   if (cudaMallocHost(reinterpret_cast<void **>(&c.h_status), sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;

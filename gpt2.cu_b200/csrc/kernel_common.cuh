@@ -1,0 +1,127 @@
+// Device-side helpers shared by the one-CTA and the CTA-pair GEMM kernels: the shared-memory
+// control block, tile decoding, and the bounded waits.
+#pragma once
+
+#include "linear_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace g2l {
+
+using namespace ptx;
+
+constexpr int MAX_STAGES = 6;
+
+// ------------------------------------------------------------------------------------
+// shared-memory control block
+// ------------------------------------------------------------------------------------
+struct Ctrl {
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
+  uint64_t ready[MAX_STAGES];
+  uint64_t tmem_full[NUM_ACC];
+  uint64_t tmem_empty[NUM_ACC];
+  uint32_t tmem_base;
+  int abort;
+};
+static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
+
+struct Tile {
+  int m_tile, n_tile, split;
+  int kb0, kb1;
+};
+
+// Advances `cursor` to the op that owns global tile `t` and decodes the tile.
+// Order inside an op: splits outermost (tiles that run together share a k-range); inside a
+// split the output tiles are walked in bands of `band_m` tile rows, row index fastest inside a
+// band. The ~148 tiles in flight then cover band_m rows x a few columns of tiles: the A rows of
+// the band stay in L2 for the whole sweep and every B column block is fetched from HBM once
+// per band instead of once per tile row.
+__device__ __forceinline__ const GemmOp *decode_tile(const GemmOp *ops, int n_ops, int t, int &cursor,
+                                                     Tile &tc) {
+  while (cursor + 1 < n_ops && t >= ops[cursor].tile_base + ops[cursor].n_tiles) ++cursor;
+  const GemmOp *op = ops + cursor;
+  decode_local(t - op->tile_base, op->tiles_dec, op->tiles_n, op->band_m, tc.m_tile, tc.n_tile, tc.split);
+  tc.kb0 = tc.split * op->kb_per_split;
+  int kb1 = tc.kb0 + op->kb_per_split;
+  tc.kb1 = kb1 < op->kb_total ? kb1 : op->kb_total;
+  return op;
+}
+
+static __device__ __noinline__ void raise_timeout(Ctrl *ctrl, const LaunchParams &p, int site, int op, int idx,
+                                           int seen, int expected) {
+  *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+  if (atomicCAS(&p.status->status, 0, GPT2L_DEV_TIMEOUT) == 0) {
+    p.status->op = op;
+    p.status->counter = idx;
+    p.status->seen = seen;
+    p.status->expected = expected;
+    p.status->where = site;
+    __threadfence();
+  }
+}
+
+// true = the phase completed; false = abort (ours or another CTA's) or the limit ran out.
+// `backoff_ns` > 0 parks the polling lane between probes (waits that last microseconds and are not
+// on the critical path: epilogue, producer), so that spinning does not eat the issue slots the
+// MMA and epilogue warps need.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl *ctrl, const LaunchParams &p,
+                                         int site, int op, int idx, unsigned backoff_ns = 0) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (backoff_ns) __nanosleep(backoff_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 127u) == 0) {
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
+      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
+        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+        return false;
+      }
+      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
+        raise_timeout(ctrl, p, site, op, idx, -1, (int)parity);
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded acquire-poll on a dependency counter.
+__device__ __forceinline__ bool wait_counter(const unsigned *ctr, unsigned expected, Ctrl *ctrl,
+                                             const LaunchParams &p, int op, int idx) {
+  unsigned v = ld_acquire(ctr);
+  if (v >= expected) return true;
+  const long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    __nanosleep(64);
+    v = ld_acquire(ctr);
+    if (v >= expected) return true;
+    if ((++spins & 15u) == 0) {
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
+      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
+        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+        return false;
+      }
+      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
+        raise_timeout(ctrl, p, SITE_DEP_COUNTER, op, idx, (int)v, (int)expected);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;  // sqrt(2/pi)
+  float u = k * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+
+}  // namespace g2l

@@ -79,6 +79,8 @@ struct alignas(64) GemmOp {
   int bn;               // 64 / 128 / 256
   int tiles_m, tiles_n, splits, kb_total, kb_per_split;
   int band_m;           // rasterisation: tile rows per band (see decode_local)
+  int pair;             // 1: tiles are 256 rows, computed by a CTA pair (cta_group::2)
+  int tiles_dec;        // tile rows in scheduling units: tiles_m, or ceil(tiles_m / 2) for pairs
   int tile_base;        // global index of this op's first tile
   int n_tiles;          // tiles_m * tiles_n * splits
   int mode;             // gpt2l_mode
@@ -120,6 +122,7 @@ struct DeviceCtx {
   bool ready = false;
   int device = -1;
   int num_sms = 0;
+  int max_pairs = 0;                // resident CTA pairs (cluster size 2)
   Status *d_status = nullptr;       // device
   Status *h_status = nullptr;       // pinned host mirror
   float *ws = nullptr;              // split-K workspace
@@ -160,8 +163,12 @@ __host__ __device__ __forceinline__ void decode_local(int local, int tiles_m, in
 // bytes of deterministic split-K workspace the op needs (0 if none)
 size_t op_workspace_bytes(const GemmOp &op);
 int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream);
+// --- linear_tcgen05_pair.cu (CTA-pair kernel) ---
+int pair_set_kernel_attributes();
+int pair_max_pairs(int num_sms);  // how many CTA pairs can be resident at once
+int pair_launch(const GemmOp *op_by_value, const LaunchParams &p, int n_pairs, bool x3, cudaStream_t stream);
 int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid,
-                bool any_3x, bool any_colsum, Status *d_status, unsigned *d_counters, long long wait_limit_ns,
+                bool any_3x, bool any_colsum, bool pair, Status *d_status, unsigned *d_counters, long long wait_limit_ns,
                 cudaStream_t stream);
 int set_kernel_attributes();
 void count_launch(int n = 1);

@@ -37,122 +37,11 @@
 
 #include "linear_internal.h"
 #include "ptx_sm100.cuh"
+#include "kernel_common.cuh"
 
 namespace g2l {
 
 using namespace ptx;
-
-// ------------------------------------------------------------------------------------
-// shared-memory control block
-// ------------------------------------------------------------------------------------
-struct Ctrl {
-  uint64_t full[STAGES_1X];
-  uint64_t empty[STAGES_1X];
-  uint64_t ready[STAGES_1X];
-  uint64_t tmem_full[NUM_ACC];
-  uint64_t tmem_empty[NUM_ACC];
-  uint32_t tmem_base;
-  int abort;
-};
-static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
-
-struct Tile {
-  int m_tile, n_tile, split;
-  int kb0, kb1;
-};
-
-// Advances `cursor` to the op that owns global tile `t` and decodes the tile.
-// Order inside an op: splits outermost (tiles that run together share a k-range); inside a
-// split the output tiles are walked in bands of `band_m` tile rows, row index fastest inside a
-// band. The ~148 tiles in flight then cover band_m rows x a few columns of tiles: the A rows of
-// the band stay in L2 for the whole sweep and every B column block is fetched from HBM once
-// per band instead of once per tile row.
-__device__ __forceinline__ const GemmOp *decode_tile(const GemmOp *ops, int n_ops, int t, int &cursor,
-                                                     Tile &tc) {
-  while (cursor + 1 < n_ops && t >= ops[cursor].tile_base + ops[cursor].n_tiles) ++cursor;
-  const GemmOp *op = ops + cursor;
-  decode_local(t - op->tile_base, op->tiles_m, op->tiles_n, op->band_m, tc.m_tile, tc.n_tile, tc.split);
-  tc.kb0 = tc.split * op->kb_per_split;
-  int kb1 = tc.kb0 + op->kb_per_split;
-  tc.kb1 = kb1 < op->kb_total ? kb1 : op->kb_total;
-  return op;
-}
-
-__device__ __noinline__ void raise_timeout(Ctrl *ctrl, const LaunchParams &p, int site, int op, int idx,
-                                           int seen, int expected) {
-  *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
-  if (atomicCAS(&p.status->status, 0, GPT2L_DEV_TIMEOUT) == 0) {
-    p.status->op = op;
-    p.status->counter = idx;
-    p.status->seen = seen;
-    p.status->expected = expected;
-    p.status->where = site;
-    __threadfence();
-  }
-}
-
-// true = the phase completed; false = abort (ours or another CTA's) or the limit ran out.
-// `backoff_ns` > 0 parks the polling lane between probes (waits that last microseconds and are not
-// on the critical path: epilogue, producer), so that spinning does not eat the issue slots the
-// MMA and epilogue warps need.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl *ctrl, const LaunchParams &p,
-                                         int site, int op, int idx, unsigned backoff_ns = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    if (backoff_ns) __nanosleep(backoff_ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 127u) == 0) {
-      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
-      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
-        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
-        return false;
-      }
-      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
-        raise_timeout(ctrl, p, site, op, idx, -1, (int)parity);
-        return false;
-      }
-    }
-  }
-}
-
-// Bounded acquire-poll on a dependency counter.
-__device__ __forceinline__ bool wait_counter(const unsigned *ctr, unsigned expected, Ctrl *ctrl,
-                                             const LaunchParams &p, int op, int idx) {
-  unsigned v = ld_acquire(ctr);
-  if (v >= expected) return true;
-  const long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    __nanosleep(64);
-    v = ld_acquire(ctr);
-    if (v >= expected) return true;
-    if ((++spins & 15u) == 0) {
-      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
-      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
-        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
-        return false;
-      }
-      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
-        raise_timeout(ctrl, p, SITE_DEP_COUNTER, op, idx, (int)v, (int)expected);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float k = 0.7978845608028654f;  // sqrt(2/pi)
-  float u = k * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
-}
-
-__device__ __forceinline__ float tf32_round(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
 
 // ------------------------------------------------------------------------------------
 // the kernel
@@ -662,14 +551,18 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Picks the tile width and the number of reduction splits: the pair that needs the fewest
 // (waves x per-tile work), where a tile's cost follows the bytes it pulls per k-block.
-static void choose_tiling(int Mc, int Nc, int kb_total, int num_sms, int forced_splits, int *bn_out,
+static void choose_tiling(int Mc, int Nc, int kb_total, int num_sms, int forced_splits, bool pair, int *bn_out,
                           int *splits_out) {
-  const int tiles_m = ceil_div(Mc, BM);
+  // scheduling units: SMs with 128-row tiles, or CTA pairs with 256-row tiles
+  const int tile_rows = pair ? 2 * BM : BM;
+  if (pair) num_sms = num_sms / 2 > 0 ? num_sms / 2 : 1;
+  const int tiles_m = ceil_div(Mc, tile_rows);
   double best = 1e300;
   int best_bn = 128, best_s = 1;
   const int cand[3] = {256, 128, 64};
   for (int ci = 0; ci < 3; ++ci) {
     const int bn = cand[ci];
+    if (pair && bn < 128) continue;         // each CTA of a pair holds bn / 2 >= 64 columns of B
     if (bn > 64 && bn / 2 >= Nc) continue;  // tile twice as wide as the matrix
     const int tiles = tiles_m * ceil_div(Nc, bn);
     const int smax = forced_splits > 0 ? forced_splits : (kb_total < 32 ? kb_total : 32);
@@ -681,7 +574,7 @@ static void choose_tiling(int Mc, int Nc, int kb_total, int num_sms, int forced_
       const double waves = (double)ceil_div(tiles * s, num_sms);
       // + 6 k-blocks of fixed per-tile overhead (pipeline fill, epilogue); splits pay an
       // extra pass over the output
-      const double cost = waves * (per + 6.0 + (s > 1 ? 4.0 : 0.0)) * (double)(BM + bn);
+      const double cost = waves * (per + 6.0 + (s > 1 ? 4.0 : 0.0)) * (double)(tile_rows + bn);
       if (cost < best - 1e-9) {
         best = cost;
         best_bn = bn;
@@ -713,7 +606,7 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
       return GPT2L_ERR_BAD_ARG;
   }
   if (d.opts.mode != GPT2L_MODE_TF32 && d.opts.mode != GPT2L_MODE_TF32X3) return GPT2L_ERR_BAD_ARG;
-  if (d.opts.split_k < 0) return GPT2L_ERR_BAD_ARG;
+  if (d.opts.split_k < 0 || d.opts.cta_pair < 0 || d.opts.cta_pair > 2) return GPT2L_ERR_BAD_ARG;
   op->C = d.out;
   op->ldc = op->Nc;
   op->mode = d.opts.mode;
@@ -724,24 +617,28 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   int bn, splits;
   int forced = d.opts.split_k;
   if (forced > op->kb_total) forced = op->kb_total;
-  choose_tiling(op->Mc, op->Nc, op->kb_total, num_sms > 0 ? num_sms : 148, forced, &bn, &splits);
+  // CTA pairs (256-row tiles, B split between the two CTAs) cut operand traffic per flop by a
+  // third; they need more than one 128-row block of output to be worth it
+  op->pair = (d.opts.cta_pair == 2 || (d.opts.cta_pair == 0 && op->Mc > BM)) ? 1 : 0;
+  choose_tiling(op->Mc, op->Nc, op->kb_total, num_sms > 0 ? num_sms : 148, forced, op->pair != 0, &bn, &splits);
   op->bn = bn;
   op->kb_per_split = ceil_div(op->kb_total, splits);
   op->splits = ceil_div(op->kb_total, op->kb_per_split);  // no empty trailing split
   op->tiles_m = ceil_div(op->Mc, BM);
   op->tiles_n = ceil_div(op->Nc, bn);
-  op->n_tiles = op->tiles_m * op->tiles_n * op->splits;
+  op->tiles_dec = op->pair ? ceil_div(op->tiles_m, 2) : op->tiles_m;
+  op->n_tiles = op->tiles_dec * op->tiles_n * op->splits;
   {
     // band height: as many tile rows as keep the band's A rows (of one split) within ~48 MB of L2
-    const double a_bytes_per_tile_row = (double)BM * (double)op->kb_per_split * BK * 4.0;
+    const double a_bytes_per_tile_row = (double)(op->pair ? 2 * BM : BM) * (double)op->kb_per_split * BK * 4.0;
     int g = (int)(48.0 * 1024 * 1024 / a_bytes_per_tile_row);
     if (g < 1) g = 1;
-    if (g > op->tiles_m) g = op->tiles_m;
-    const int bands = ceil_div(op->tiles_m, g);
-    op->band_m = ceil_div(op->tiles_m, bands);  // balanced bands
+    if (g > op->tiles_dec) g = op->tiles_dec;
+    const int bands = ceil_div(op->tiles_dec, g);
+    op->band_m = ceil_div(op->tiles_dec, bands);  // balanced bands
   }
   op->atomic_out = (op->splits > 1 && !d.opts.deterministic && !op->C2) ? 1 : 0;
-  op->idesc = make_idesc_tf32(BM, bn, op->a_mn, op->b_mn);
+  op->idesc = make_idesc_tf32(op->pair ? 2 * BM : BM, bn, op->a_mn, op->b_mn);
   for (int w = 0; w < MAX_WAITS; ++w) { op->wait_ctr[w] = -1; op->wait_kind[w] = 0; op->wait_expected[w] = 0; }
   op->pub_rb_base = -1;
   op->pub_op_ctr = -1;
@@ -763,8 +660,9 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   if (op->a_3d) e = encode_map_chunked(&op->tmA, d.a, a_inner, a_outer, BM / 32);
   else e = encode_map(&op->tmA, d.a, a_inner, a_outer, 32, op->a_mn ? 32 : BM, op->a_mn);
   if (e) return e;
-  if (op->b_3d) e = encode_map_chunked(&op->tmB, d.b, b_inner, b_outer, op->bn / 32);
-  else e = encode_map(&op->tmB, d.b, b_inner, b_outer, 32, op->b_mn ? 32 : op->bn, op->b_mn);
+  const int bn_cta = op->pair ? op->bn / 2 : op->bn;  // B columns one CTA stages
+  if (op->b_3d) e = encode_map_chunked(&op->tmB, d.b, b_inner, b_outer, bn_cta / 32);
+  else e = encode_map(&op->tmB, d.b, b_inner, b_outer, 32, op->b_mn ? 32 : bn_cta, op->b_mn);
   if (e) return e;
   e = encode_map(&op->tmC, op->C, (uint64_t)op->Nc, (uint64_t)op->Mc, 32, 32, false);
   if (e) return e;
@@ -774,7 +672,7 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
 
 size_t op_workspace_bytes(const GemmOp &op) {
   if (op.splits <= 1 || op.atomic_out) return 0;
-  return (size_t)op.n_tiles * BM * op.bn * sizeof(float);
+  return (size_t)op.tiles_m * op.tiles_n * op.splits * BM * op.bn * sizeof(float);
 }
 
 int set_kernel_attributes() {
@@ -799,6 +697,11 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.counters = nullptr;
   p.wait_limit_ns = default_wait_limit_ns();
   p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
+  if (op.pair) {
+    const int pairs = op.n_tiles < ctx->max_pairs ? op.n_tiles : ctx->max_pairs;
+    if (pairs <= 0) return GPT2L_ERR_CUDA;
+    return pair_launch(&op, p, pairs, op.mode == GPT2L_MODE_TF32X3, stream);
+  }
   const int grid = op.n_tiles < ctx->num_sms ? op.n_tiles : ctx->num_sms;
   if (op.mode == GPT2L_MODE_TF32X3)
     gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
@@ -809,7 +712,7 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
 }
 
 int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid, bool any_3x, bool any_colsum,
-                Status *d_status, unsigned *d_counters, long long wait_limit_ns, cudaStream_t stream) {
+                bool pair, Status *d_status, unsigned *d_counters, long long wait_limit_ns, cudaStream_t stream) {
   (void)ctx;
   static GemmOp dummy;  // the by-value slot is unused when a list is given
   LaunchParams p;
@@ -820,6 +723,7 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
   p.xform_active = (any_3x || any_colsum) ? 1 : 0;
+  if (pair) return pair_launch(nullptr, p, grid, any_3x, stream);
   if (any_3x)
     gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);
   else

@@ -23,6 +23,7 @@ struct Plan {
   int n_counters = 0;
   bool any_3x = false;
   bool any_colsum = false;
+  bool pair = false;  // every op runs on CTA pairs (256-row tiles)
 };
 
 static GemmDesc desc_from(const gpt2l_op &o) {
@@ -45,8 +46,18 @@ static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
   if (!ops || n_ops <= 0) return GPT2L_ERR_BAD_ARG;
   plan->ops.resize(n_ops);
   int tile_base = 0, ctr = 0;
+  // one kernel runs the whole list, so all ops use the same CTA arrangement: pairs when every op
+  // has more than one 128-row block of output and none asks for single CTAs
+  bool pair = true;
   for (int i = 0; i < n_ops; ++i) {
     GemmDesc d = desc_from(ops[i]);
+    const int rows = d.kind == GPT2L_OP_BACKWARD_WEIGHT ? d.K : d.M;
+    if (rows <= BM || d.opts.cta_pair == 1) pair = false;
+  }
+  plan->pair = pair;
+  for (int i = 0; i < n_ops; ++i) {
+    GemmDesc d = desc_from(ops[i]);
+    d.opts.cta_pair = pair ? 2 : 1;
     // bias gradient inside a schedule is always the fused column sum
     int e = plan_op(d, num_sms, &plan->ops[i]);
     if (e) return e;
@@ -78,7 +89,7 @@ static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
       } else if (dep.kind == GPT2L_DEP_WHOLE_OP) {
         g.wait_ctr[w] = pr.pub_op_ctr;
         g.wait_kind[w] = GPT2L_DEP_WHOLE_OP;
-        g.wait_expected[w] = (int)(ARRIVALS_PER_TILE * pr.n_tiles);
+        g.wait_expected[w] = (int)(ARRIVALS_PER_TILE * pr.tiles_m * pr.tiles_n * pr.splits);
       } else {
         return GPT2L_ERR_SCHEDULE;
       }
@@ -106,18 +117,28 @@ static int replay(const Plan &plan, int grid) {
         int &cur = cursor[c];
         while (cur + 1 < (int)plan.ops.size() && t >= plan.ops[cur].tile_base + plan.ops[cur].n_tiles) ++cur;
         const GemmOp &g = plan.ops[cur];
-        int m_tile, n_tile, split;
-        decode_local(t - g.tile_base, g.tiles_m, g.tiles_n, g.band_m, m_tile, n_tile, split);
+        int m_dec, n_tile, split;
+        decode_local(t - g.tile_base, g.tiles_dec, g.tiles_n, g.band_m, m_dec, n_tile, split);
+        // a pair tile covers two 128-row blocks, one per CTA
+        const int halves = g.pair ? 2 : 1;
         bool ready = true;
-        for (int w = 0; w < MAX_WAITS; ++w) {
-          if (g.wait_ctr[w] < 0) continue;
-          const int idx = g.wait_ctr[w] + (g.wait_kind[w] == GPT2L_DEP_ROWBLOCK ? m_tile : 0);
-          if (idx < 0 || idx >= plan.n_counters) return GPT2L_ERR_SCHEDULE;
-          if (counters[idx] < g.wait_expected[w]) ready = false;
+        for (int h = 0; h < halves; ++h) {
+          const int m_tile = g.pair ? 2 * m_dec + h : m_dec;
+          if (m_tile >= g.tiles_m) continue;
+          for (int w = 0; w < MAX_WAITS; ++w) {
+            if (g.wait_ctr[w] < 0) continue;
+            const int idx = g.wait_ctr[w] + (g.wait_kind[w] == GPT2L_DEP_ROWBLOCK ? m_tile : 0);
+            if (idx < 0 || idx >= plan.n_counters) return GPT2L_ERR_SCHEDULE;
+            if (counters[idx] < g.wait_expected[w]) ready = false;
+          }
         }
         if (!ready) break;
-        counters[g.pub_rb_base + m_tile] += ARRIVALS_PER_TILE;
-        counters[g.pub_op_ctr] += ARRIVALS_PER_TILE;
+        for (int h = 0; h < halves; ++h) {
+          const int m_tile = g.pair ? 2 * m_dec + h : m_dec;
+          if (m_tile >= g.tiles_m) continue;
+          counters[g.pub_rb_base + m_tile] += ARRIVALS_PER_TILE;
+          counters[g.pub_op_ctr] += ARRIVALS_PER_TILE;
+        }
         next[c] += grid;
         --remaining;
         progress = true;
@@ -151,8 +172,9 @@ int gpt2_schedule_validate(const gpt2l_op *ops, int n_ops, int grid) {
   Plan plan;
   int e = make_plan(ops, n_ops, grid, &plan);
   if (e) return e;
-  const int g = grid < plan.total_tiles ? grid : plan.total_tiles;
-  return replay(plan, g);
+  int units = plan.pair ? (grid / 2 > 0 ? grid / 2 : 1) : grid;  // CTAs, or CTA pairs
+  if (units > plan.total_tiles) units = plan.total_tiles;
+  return replay(plan, units);
 }
 
 int gpt2_schedule_describe(const gpt2l_op *ops, int n_ops, int num_sms, int counts[3]) {
@@ -162,7 +184,8 @@ int gpt2_schedule_describe(const gpt2l_op *ops, int n_ops, int num_sms, int coun
   if (counts) {
     counts[0] = plan.total_tiles;
     counts[1] = plan.n_counters;
-    counts[2] = num_sms < plan.total_tiles ? num_sms : plan.total_tiles;
+    const int units = plan.pair ? (num_sms / 2 > 0 ? num_sms / 2 : 1) : num_sms;
+    counts[2] = units < plan.total_tiles ? units : plan.total_tiles;  // CTAs, or CTA pairs
   }
   return GPT2L_OK;
 }
@@ -178,13 +201,18 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
   e = make_plan(ops, n_ops, ctx->num_sms, &s->plan);
   if (e) { *err = e; delete s; return nullptr; }
   s->user_ops.assign(ops, ops + n_ops);
-  s->grid = ctx->num_sms < s->plan.total_tiles ? ctx->num_sms : s->plan.total_tiles;
+  {
+    const int units = s->plan.pair ? ctx->max_pairs : ctx->num_sms;  // CTA pairs or CTAs
+    s->grid = units < s->plan.total_tiles ? units : s->plan.total_tiles;
+    if (s->grid <= 0) { *err = GPT2L_ERR_CUDA; delete s; return nullptr; }
+  }
   e = replay(s->plan, s->grid);
   if (e) { *err = e; delete s; return nullptr; }
   // tensor maps + workspace
   size_t ws_bytes = 0, sem_count = 0;
   for (int i = 0; i < n_ops; ++i) {
     GemmDesc d = desc_from(ops[i]);
+    d.opts.cta_pair = s->plan.pair ? 2 : 1;
     if (!d.out || !d.a || !d.b || !tma_eligible(d)) { *err = GPT2L_ERR_BAD_ARG; delete s; return nullptr; }
     GemmOp full;
     e = build_op(d, ctx->num_sms, &full);
@@ -255,7 +283,7 @@ int gpt2_megakernel_run(gpt2l_schedule *s, gpt2l_stream_t stream) {
         return GPT2L_ERR_CUDA;
     }
   }
-  return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x, s->plan.any_colsum,
+  return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x, s->plan.any_colsum, s->plan.pair,
                      s->d_status, s->d_counters, s->wait_limit_ns, st);
 }
 

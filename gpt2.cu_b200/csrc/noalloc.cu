@@ -36,6 +36,7 @@ struct PerDevice {
   bool ready = false;
   unsigned char *base = nullptr;  // device address of g_noalloc_scratch on this device
   int num_sms = 0;
+  int max_pairs = 0;
 };
 constexpr int NA_MAX_DEVICES = 16;
 PerDevice g_dev[NA_MAX_DEVICES];
@@ -62,6 +63,9 @@ int setup_current_device(PerDevice **out) {
     if (!get_encode_fn()) return GPT2L_ERR_CUDA;
     int e = set_kernel_attributes();
     if (e) return e;
+    e = pair_set_kernel_attributes();
+    if (e) return e;
+    d.max_pairs = pair_max_pairs(sms);
     void *ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) {
       (void)cudaGetLastError();
@@ -136,6 +140,7 @@ extern "C" int gpt2_linear_backward_weight_noalloc(float *g_w, float *g_b, const
   DeviceCtx ctx;  // a view for the shared launcher; nothing in it is owned or allocated
   ctx.ready = true;
   ctx.num_sms = dev->num_sms;
+  ctx.max_pairs = dev->max_pairs;
   ctx.d_status = status;
   err = launch_single(&ctx, op, st);
   if (err) return err;

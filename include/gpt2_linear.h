@@ -61,6 +61,7 @@ typedef struct gpt2_linear_opts {
   int deterministic; /* backward_weight with split_k>1: combine partials in a fixed order   */
   float *out2;       /* second output for GPT2L_EPI_GELU_DUAL, [B*S][N]                     */
   int force_simt;    /* 1 = run the CUDA-core fallback kernel even where TMA is possible    */
+  int cta_pair;      /* 0 = choose; 1 = one CTA per 128-row tile; 2 = CTA pairs, 256-row tiles */
 } gpt2_linear_opts;
 
 /* One-time set-up for the current device: checks the architecture, raises the dynamic

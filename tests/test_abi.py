@@ -74,9 +74,17 @@ def test_schedule_describe_counts(g):
     ops = mlp_chain(g, B=2, S=256, C=64)
     code, (tiles, counters, grid) = g.describe_schedule(ops, 148)
     assert code == g.OK
-    # M = 512 -> 4 row blocks for the three M-row ops, K-row blocks for the weight gradient
+    # M = 512 -> 4 row blocks for the four M-row ops, K = 256 -> 2 row blocks for the weight gradient
     assert counters == (4 + 1) * 4 + (2 + 1)
-    assert tiles >= 4 + 4 + 4 + 1 + 4 and grid == min(148, tiles)
+    # every op has more than 128 output rows, so the list runs on CTA pairs (256-row tiles):
+    # at least 2 + 2 + 2 + 1 + 2 tiles, one pair each on 148 / 2 pairs
+    assert tiles >= 9 and grid == min(74, tiles)
+    # the same list forced onto single CTAs (128-row tiles)
+    for op in ops:
+        op.opts.cta_pair = 1
+    code, (tiles1, counters1, grid1) = g.describe_schedule(ops, 148)
+    assert code == g.OK and counters1 == counters
+    assert tiles1 >= 4 + 4 + 4 + 2 + 4 and grid1 == min(148, tiles1)
 
 
 def test_schedule_rejects_forward_pointing_dependency(g):

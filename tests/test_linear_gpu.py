@@ -73,11 +73,12 @@ SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("pair", [1, 2])  # 1: one CTA per 128-row tile; 2: CTA pairs, 256-row tiles
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("M,K,N", SHAPES)
-def test_parity_against_oracle(gpu, orc, M, K, N, mode):
+def test_parity_against_oracle(gpu, orc, M, K, N, mode, pair):
     x, w, b, dy = seeded(M, K, N, seed=M + K + N)
-    outs = run_all(gpu, x, w, b, dy, mode)
+    outs = run_all(gpu, x, w, b, dy, mode, cta_pair=pair)
     check_all(orc, outs, x, w, b, dy, TIGHT[mode])
 
 
@@ -120,12 +121,13 @@ def test_force_simt_matches(gpu, orc):
     check_all(orc, outs, x, w, b, dy, 1e-5)
 
 
+@pytest.mark.parametrize("pair", [1, 2])
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("det", [0, 1])
 @pytest.mark.parametrize("splits", [2, 5])
-def test_split_k_weight_gradient(gpu, orc, splits, det, mode):
-    x, w, b, dy = seeded(1024, 128, 256, seed=splits)
-    outs = run_all(gpu, x, w, b, dy, mode, split_k=splits, deterministic=det)
+def test_split_k_weight_gradient(gpu, orc, splits, det, mode, pair):
+    x, w, b, dy = seeded(1024, 384, 256, seed=splits)
+    outs = run_all(gpu, x, w, b, dy, mode, split_k=splits, deterministic=det, cta_pair=pair)
     check_all(orc, outs, x, w, b, dy, TIGHT[mode])
 
 
@@ -144,13 +146,14 @@ def test_small_m_long_reduction_picks_splits(gpu, orc):
     check_all(orc, outs, x, w, b, dy, TIGHT[0])
 
 
-def test_gelu_dual_store(gpu, orc):
+@pytest.mark.parametrize("pair", [1, 2])
+def test_gelu_dual_store(gpu, orc, pair):
     x, w, b, dy = seeded(300, 64, 256, seed=6)
     M, K = x.shape
     N = w.shape[1]
     y = torch.empty((M, N), device="cuda")
     y2 = torch.empty((M, N), device="cuda")
-    o = gpu.make_opts(mode=1, flags=gpu.EPI_GELU_DUAL, out2=y2.data_ptr())
+    o = gpu.make_opts(mode=1, flags=gpu.EPI_GELU_DUAL, out2=y2.data_ptr(), cta_pair=pair)
     gpu.check("forward", gpu.forward(y, dev(x), dev(w), dev(b), 1, M, K, N, o))
     torch.cuda.synchronize()
     pre = y.cpu().numpy()

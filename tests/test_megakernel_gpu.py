@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def mlp_block(g, B, S, C, mode, seed=0, det=1):
+def mlp_block(g, B, S, C, mode, seed=0, det=1, pair=0):
     """x -> h = x.W1+b1 -> y = h.W2+b2, then the backward of both GEMMs (no GELU: a linear
     chain keeps every intermediate checkable by GEMMs alone)."""
     M = B * S
@@ -26,7 +26,7 @@ def mlp_block(g, B, S, C, mode, seed=0, det=1):
     for name, shape in (("h", (M, 4 * C)), ("y", (M, C)), ("dh", (M, 4 * C)), ("dw2", (4 * C, C)),
                         ("db2", (C,)), ("dx", (M, C)), ("dw1", (C, 4 * C)), ("db1", (4 * C,))):
         t[name] = torch.full(shape, float("nan"), device="cuda")
-    o = g.make_opts(mode=mode, deterministic=det)
+    o = g.make_opts(mode=mode, deterministic=det, cta_pair=pair)
     ops = [
         g.make_op(g.OP_FORWARD, B, S, C, 4 * C, t["h"], t["x"], t["w1"], bias=t["b1"], opts=o),
         g.make_op(g.OP_FORWARD, B, S, 4 * C, C, t["y"], t["h"], t["w2"], bias=t["b2"], opts=o,
@@ -54,10 +54,11 @@ def separate_calls(g, t, B, S, C, o):
     return r
 
 
+@pytest.mark.parametrize("pair", [0, 1])  # 0: the scheduler chooses (CTA pairs where every op allows); 1: single CTAs
 @pytest.mark.parametrize("mode", [0, 1])
-@pytest.mark.parametrize("B,S,C", [(2, 256, 64), (4, 1024, 256), (3, 100, 96)])
-def test_dependent_chain_in_one_launch(gpu, orc, B, S, C, mode):
-    t, ops, o = mlp_block(gpu, B, S, C, mode, seed=C)
+@pytest.mark.parametrize("B,S,C", [(2, 256, 64), (4, 1024, 256), (3, 100, 96), (1, 300, 160)])
+def test_dependent_chain_in_one_launch(gpu, orc, B, S, C, mode, pair):
+    t, ops, o = mlp_block(gpu, B, S, C, mode, seed=C, pair=pair)
     sched = gpu.Schedule(ops)
     launches0 = gpu.lib.gpt2_linear_launch_count()
     for _ in range(3):  # counters are re-armed on every run
