@@ -124,4 +124,32 @@ __device__ __forceinline__ float tf32_round(float x) {
 }
 
 
+
+// Epilogue store of one 32-row x 32-column chunk held as "thread = row, 32 consecutive columns"
+// (the tcgen05.ld 32x32b layout). Written straight from registers each thread would touch 32
+// different 128-byte lines per instruction; instead the chunk goes through a swizzled 4 KiB box in
+// shared memory and comes back as "instruction = 4 rows x 128 bytes", so that every global store (or
+// split-K reduction) instruction covers four whole lines. Only the warp's own lanes are involved:
+// __syncwarp is the only synchronisation, and no asynchronous-proxy fence is needed.
+__device__ __forceinline__ void store_chunk(const float (&v)[32], uint32_t sbuf, float *C, long long ldc,
+                                            int row0, int nb, int Mc, int Nc, int lane, bool atomic) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    st_shared_v4(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  __syncwarp();
+  const int rr = lane >> 3, cc = lane & 7;
+  const int col = nb + cc * 4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rl = 4 * i + rr;
+    const float4 x = ld_shared_v4(sbuf + rl * 128 + ((cc ^ (rl & 7)) << 4));
+    const int grow = row0 + rl;
+    if (grow < Mc && col < Nc) {
+      float *dst = C + (long long)grow * ldc + col;
+      if (atomic) red_add_v4(dst, x.x, x.y, x.z, x.w);
+      else *reinterpret_cast<float4 *>(dst) = x;
+    }
+  }
+}
+
 }  // namespace g2l

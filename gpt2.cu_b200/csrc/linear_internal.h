@@ -104,6 +104,7 @@ struct LaunchParams {
   unsigned *counters;
   long long wait_limit_ns;
   int xform_active;  // 0: no op needs the transform warps (TF32 mode, no fused bias gradient)
+  int debug;         // timing experiments only (env GPT2L_DEBUG): 1 no TMA store, 2 no staging either, 4 no tcgen05.ld
 };
 
 // host-side description used to build a GemmOp

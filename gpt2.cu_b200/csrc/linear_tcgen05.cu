@@ -31,6 +31,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -153,12 +154,23 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
+    // The next tile is decoded while the current one is being issued: at a tile boundary the
+    // tensor pipe holds less than a k-block of queued work, so nothing slow may sit there.
     int cursor = 0;
     uint32_t it = 0, tcount = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tcount) {
-      Tile tc;
-      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+    int t = blockIdx.x;
+    Tile tc;
+    const GemmOp *op = nullptr;
+    bool have = t < p.total_tiles;
+    if (have) op = decode_tile(ops, n_ops, t, cursor, tc);
+    while (have && ok) {
+      const int t_next = t + (int)gridDim.x;
+      const bool have_next = t_next < p.total_tiles;
+      Tile tc_next = tc;
+      const GemmOp *op_next = op;
+      if (have_next) op_next = decode_tile(ops, n_ops, t_next, cursor, tc_next);
+
       const uint32_t as = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
       int okl = 1;
@@ -214,6 +226,11 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       if (!ok) break;
       if (lane == 0) mma_commit(smem_u32(&ctrl->tmem_full[as]));
       __syncwarp();
+      t = t_next;
+      tc = tc_next;
+      op = op_next;
+      have = have_next;
+      ++tcount;
     }
   } else if (warp < EPI_WARP0) {
     // =============================== operand transform ===============================
@@ -345,8 +362,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
                   (size_t)(q * 32 + lane) * bn;
 
       if (!det_split) {
-        // ---- staged path: registers -> swizzled 32x32 box in shared memory -> TMA store (or
-        // TMA reduce-add for split-K partials). The copy engine clips rows/columns outside C.
+        // ---- registers -> swizzled 32x32 box in shared memory -> coalesced stores (or vector
+        // reductions for split-K partials); see store_chunk
         const int row0 = tc.m_tile * BM + q * 32;
         for (int c = 0; c < bn / 32; ++c) {
           const int nb = n0 + c * 32;
@@ -366,24 +383,11 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
           }
           for (int pass = 0; pass < (dual ? 2 : 1); ++pass, ++epi_cc) {
             const uint32_t sbuf = epi_base + (epi_cc & 1u) * EPI_BUF_BYTES;
-            if (epi_cc >= 2) {
-              if (lane == 0) bulk_wait_read<1>();  // the box written two chunks ago has been read
-              __syncwarp();
-            }
+            if (pass == 1) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t a = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
-              if (pass == 0) st_shared_v4(a, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              else st_shared_v4(a, gelu_tanh(v[4 * j]), gelu_tanh(v[4 * j + 1]), gelu_tanh(v[4 * j + 2]),
-                                gelu_tanh(v[4 * j + 3]));
+              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (op->atomic_out) tma_reduce_add_2d(&op->tmC, sbuf, nb, row0);
-              else tma_store_2d(pass == 0 ? &op->tmC : &op->tmC2, sbuf, nb, row0);
-              bulk_commit();
-            }
+            store_chunk(v, sbuf, pass == 0 ? op->C : op->C2, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0);
           }
         }
       } else
@@ -457,7 +461,6 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
 
       // ---- publish: everything this warp stored is visible before the counters move
       if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
-        if (lane == 0) bulk_wait_all();  // the copy engine's writes of this tile are complete
         __threadfence();
         __syncwarp();
         if (lane == 0) {
@@ -467,8 +470,6 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       }
     }
   }
-
-  if (warp >= EPI_WARP0 && lane == 0) bulk_wait_all();  // shared memory stays valid until the stores have read it
 
   // =============================== teardown ===============================
   if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
@@ -618,8 +619,9 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   int forced = d.opts.split_k;
   if (forced > op->kb_total) forced = op->kb_total;
   // CTA pairs (256-row tiles, B split between the two CTAs) cut operand traffic per flop by a
-  // third; they need more than one 128-row block of output to be worth it
-  op->pair = (d.opts.cta_pair == 2 || (d.opts.cta_pair == 0 && op->Mc > BM)) ? 1 : 0;
+  // third, but measured no faster than single CTAs on these shapes (both reach the same ~480 ns
+  // per 128x256x32 k-block) and quantise worse on 74 pairs: they run only on request
+  op->pair = (d.opts.cta_pair == 2) ? 1 : 0;
   choose_tiling(op->Mc, op->Nc, op->kb_total, num_sms > 0 ? num_sms : 148, forced, op->pair != 0, &bn, &splits);
   op->bn = bn;
   op->kb_per_split = ceil_div(op->kb_total, splits);
@@ -685,6 +687,11 @@ int set_kernel_attributes() {
 }
 
 static long long default_wait_limit_ns() { return 4000000000ll; }  // 4 s
+int debug_flags() {
+  static int v = -1;
+  if (v < 0) { const char *e = getenv("GPT2L_DEBUG"); v = e ? atoi(e) : 0; }
+  return v;
+}
 
 int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   op.tile_base = 0;
@@ -697,6 +704,7 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.counters = nullptr;
   p.wait_limit_ns = default_wait_limit_ns();
   p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
+  p.debug = debug_flags();
   if (op.pair) {
     const int pairs = op.n_tiles < ctx->max_pairs ? op.n_tiles : ctx->max_pairs;
     if (pairs <= 0) return GPT2L_ERR_CUDA;
@@ -723,6 +731,7 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
   p.xform_active = (any_3x || any_colsum) ? 1 : 0;
+  p.debug = debug_flags();
   if (pair) return pair_launch(nullptr, p, grid, any_3x, stream);
   if (any_3x)
     gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);

@@ -267,7 +267,7 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
           int okl = 1;
           if (lane == 0) {
             okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
-            if (okl) mbar_arrive_cluster(mapa_cluster(smem_u32(&ctrl->ready[s]), 0));
+            if (okl) mbar_arrive_cluster_relaxed(mapa_cluster(smem_u32(&ctrl->ready[s]), 0));
           }
           ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
           if (!ok) break;
@@ -407,8 +407,14 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
           const int nb = n0 + c * 32;
           if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
           uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
+          if (!(p.debug & 4)) {
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
+          if (p.debug & 2) continue;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -421,24 +427,11 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
           }
           for (int pass = 0; pass < (dual ? 2 : 1); ++pass, ++epi_cc) {
             const uint32_t sbuf = epi_base + (epi_cc & 1u) * EPI_BUF_BYTES;
-            if (epi_cc >= 2) {
-              if (lane == 0) bulk_wait_read<1>();
-              __syncwarp();
-            }
+            if (pass == 1) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t a = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
-              if (pass == 0) st_shared_v4(a, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              else st_shared_v4(a, gelu_tanh(v[4 * j]), gelu_tanh(v[4 * j + 1]), gelu_tanh(v[4 * j + 2]),
-                                gelu_tanh(v[4 * j + 3]));
+              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
             }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (op->atomic_out) tma_reduce_add_2d(&op->tmC, sbuf, nb, row0);
-              else tma_store_2d(pass == 0 ? &op->tmC : &op->tmC2, sbuf, nb, row0);
-              bulk_commit();
-            }
+            store_chunk(v, sbuf, pass == 0 ? op->C : op->C2, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0);
           }
         }
       } else if (live) {
@@ -506,7 +499,6 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
       }
 
       if (live && (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0)) {
-        if (lane == 0) bulk_wait_all();
         __threadfence();
         __syncwarp();
         if (lane == 0) {
@@ -516,8 +508,6 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
       }
     }
   }
-
-  if (warp >= EPI_WARP0 && lane == 0) bulk_wait_all();
 
   // =============================== teardown ===============================
   if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {

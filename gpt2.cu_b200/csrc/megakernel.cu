@@ -46,14 +46,11 @@ static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
   if (!ops || n_ops <= 0) return GPT2L_ERR_BAD_ARG;
   plan->ops.resize(n_ops);
   int tile_base = 0, ctr = 0;
-  // one kernel runs the whole list, so all ops use the same CTA arrangement: pairs when every op
-  // has more than one 128-row block of output and none asks for single CTAs
+  // one kernel runs the whole list, so all ops use the same CTA arrangement: pairs only when
+  // every op asks for them (cta_pair == 2)
   bool pair = true;
-  for (int i = 0; i < n_ops; ++i) {
-    GemmDesc d = desc_from(ops[i]);
-    const int rows = d.kind == GPT2L_OP_BACKWARD_WEIGHT ? d.K : d.M;
-    if (rows <= BM || d.opts.cta_pair == 1) pair = false;
-  }
+  for (int i = 0; i < n_ops; ++i)
+    if (ops[i].opts.cta_pair != 2) pair = false;
   plan->pair = pair;
   for (int i = 0; i < n_ops; ++i) {
     GemmDesc d = desc_from(ops[i]);

@@ -76,15 +76,15 @@ def test_schedule_describe_counts(g):
     assert code == g.OK
     # M = 512 -> 4 row blocks for the four M-row ops, K = 256 -> 2 row blocks for the weight gradient
     assert counters == (4 + 1) * 4 + (2 + 1)
-    # every op has more than 128 output rows, so the list runs on CTA pairs (256-row tiles):
-    # at least 2 + 2 + 2 + 1 + 2 tiles, one pair each on 148 / 2 pairs
-    assert tiles >= 9 and grid == min(74, tiles)
-    # the same list forced onto single CTAs (128-row tiles)
+    # default: single CTAs, 128-row tiles
+    assert tiles >= 4 + 4 + 4 + 2 + 4 and grid == min(148, tiles)
+    # the same list on CTA pairs (256-row tiles): at least 2 + 2 + 2 + 1 + 2 tiles on 148 / 2 pairs
     for op in ops:
-        op.opts.cta_pair = 1
-    code, (tiles1, counters1, grid1) = g.describe_schedule(ops, 148)
-    assert code == g.OK and counters1 == counters
-    assert tiles1 >= 4 + 4 + 4 + 2 + 4 and grid1 == min(148, tiles1)
+        op.opts.cta_pair = 2
+    code, (tiles2, counters2, grid2) = g.describe_schedule(ops, 148)
+    assert code == g.OK and counters2 == counters
+    assert 9 <= tiles2 < tiles and grid2 == min(74, tiles2)
+    assert g.validate_schedule(ops, 148) == g.OK
 
 
 def test_schedule_rejects_forward_pointing_dependency(g):

@@ -54,7 +54,7 @@ def separate_calls(g, t, B, S, C, o):
     return r
 
 
-@pytest.mark.parametrize("pair", [0, 1])  # 0: the scheduler chooses (CTA pairs where every op allows); 1: single CTAs
+@pytest.mark.parametrize("pair", [0, 2])  # 0: single CTAs (default); 2: CTA pairs, 256-row tiles
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("B,S,C", [(2, 256, 64), (4, 1024, 256), (3, 100, 96), (1, 300, 160)])
 def test_dependent_chain_in_one_launch(gpu, orc, B, S, C, mode, pair):
