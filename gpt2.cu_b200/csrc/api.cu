@@ -67,8 +67,31 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   GemmDesc dd = d;
   dd.out_bias = fused_bias;
   GemmOp op;
+  // Wide weight gradients (lm_head: N = 50304 against K = 768): the tensor core reads an MN-major A
+  // operand about 20 % slower than a K-major one, and here A = in^T is tiny next to the GEMM. So
+  // `in` is transposed once into scratch (2 * M * K * 4 bytes of traffic, ~1 % of the GEMM's time) and
+  // the product runs in the forward form g_w[K][N] = inT[K][M] . g_out[M][N] with a K-major A.
+  bool transposed_a = false;
+  if (d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.N >= 8192 && d.N >= 8 * d.K && (d.M & 3) == 0 && d.M > 1) {
+    {
+      std::lock_guard<std::mutex> lk(g_mu);
+      err = ensure_bytes(&ctx->xt, &ctx->xt_bytes, (size_t)d.M * d.K * sizeof(float));
+    }
+    if (err) return err;
+    err = launch_transpose(ctx->xt, d.a, d.M, d.K, st);
+    if (err) return err;
+    dd.kind = GPT2L_OP_FORWARD;
+    dd.M = d.K;  // output rows
+    dd.K = d.M;  // reduction
+    dd.a = ctx->xt;
+    dd.b = d.b;
+    dd.bias = nullptr;
+    dd.opts.flags = 0;
+    transposed_a = true;
+  }
   err = build_op(dd, ctx->num_sms, &op);
   if (err) return err;
+  if (transposed_a) op.colsum = fused_bias;  // the B operand is still g_out: its column sums are g_b
   if (op.splits > 1) {
     if (op.atomic_out) {
       if (cudaMemsetAsync(op.C, 0, (size_t)op.Mc * op.Nc * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
@@ -161,6 +184,7 @@ void gpt2_linear_shutdown(void) {
     cudaFreeHost(c.h_status);
     cudaFree(c.ws_sem);
     if (c.ws) cudaFree(c.ws);
+    if (c.xt) cudaFree(c.xt);
     for (int i = 0; i < 4; ++i)
       if (c.stage[i]) cudaFree(c.stage[i]);
     c = DeviceCtx();

@@ -1,0 +1,518 @@
+// The non-GEMM layers of the GPT-2 training step (embedding, layernorm, attention, GELU backward,
+// residual, softmax + cross-entropy, AdamW), written for the model driver in model.cu. They keep the
+// reference's tensor layouts (src/layers/*.cu of vnnm404/gpt2.cu: activations [B*T][C], qkv
+// [B*T][3C] with q | k | v side by side, wte stored [C][V]) but not its kernels: attention is
+// flash-style (no [B,NH,T,T] tensors; only the log-sum-exp per row is kept for the backward pass),
+// softmax and cross-entropy are one pass that leaves dlogits in place of the logits, and layernorm
+// works a row per warp. All fp32 CUDA-core code; the GEMMs around them are the tcgen05 path.
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "layers.h"
+#include "linear_internal.h"
+
+namespace g2l {
+
+static inline int cdiv(long long a, int b) { return (int)((a + b - 1) / b); }
+
+// ------------------------------------------------------------------------------------
+// embedding: out[m][c] = wte[c][tok[m]] + wpe[t][c]     (reference: embedding.cu:11-27; wte is [C][V])
+// ------------------------------------------------------------------------------------
+__global__ void embedding_forward_kernel(float *out, const int *tokens, const float *wte, const float *wpe, int M,
+                                         int T, int C, int Vp) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * C) return;
+  const int m = (int)(i / C), c = (int)(i % C);
+  const int tok = tokens[m], t = m % T;
+  out[i] = wte[(long long)c * Vp + tok] + wpe[(long long)t * C + c];
+}
+
+// g_wte[c][tok] += g[m][c]; g_wpe[t][c] += g[m][c]. (The reference indexes g_wte as [V][C] here,
+// embedding.cu:93, which does not match its own forward; the PyTorch model is the semantics kept.)
+__global__ void embedding_backward_kernel(float *g_wte, float *g_wpe, const float *g, const int *tokens, int M, int T,
+                                          int C, int Vp) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * C) return;
+  const int m = (int)(i / C), c = (int)(i % C);
+  const int tok = tokens[m], t = m % T;
+  const float v = g[i];
+  atomicAdd(g_wte + (long long)c * Vp + tok, v);
+  atomicAdd(g_wpe + (long long)t * C + c, v);
+}
+
+// ------------------------------------------------------------------------------------
+// layernorm, one warp per row (eps 1e-5 as layernorm.cu:54-116)
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+layernorm_forward_kernel(float *out, float *mean, float *rstd, const float *in, const float *w, const float *b,
+                         int M, int C) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float *x = in + (long long)row * C;
+  float s = 0.f;
+  for (int c = lane; c < C; c += 32) s += x[c];
+  const float mu = warp_sum(s) / C;
+  float v = 0.f;
+  for (int c = lane; c < C; c += 32) { const float d = x[c] - mu; v += d * d; }
+  const float rs = rsqrtf(warp_sum(v) / C + 1e-5f);
+  float *o = out + (long long)row * C;
+  for (int c = lane; c < C; c += 32) o[c] = (x[c] - mu) * rs * w[c] + b[c];
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
+// g_in[row] += layernorm backward of g_out[row]; g_w / g_b accumulate over rows. Each block handles
+// `rows_per_block` rows, keeps per-column partial sums in registers (thread = column slot) and adds
+// them to g_w / g_b once at the end.
+__global__ void __launch_bounds__(256)
+layernorm_backward_kernel(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
+                          const float *mean, const float *rstd, int M, int C, int rows_per_block) {
+  extern __shared__ float sm[];  // [2][C] column sums of this block
+  float *sw = sm, *sb = sm + C;
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) sm[c] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  for (int row = r0 + warp; row < r1; row += nwarps) {
+    const float *x = in + (long long)row * C;
+    const float *go = g_out + (long long)row * C;
+    const float mu = mean[row], rs = rstd[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane; c < C; c += 32) {
+      const float nh = (x[c] - mu) * rs;
+      const float dn = go[c] * w[c];
+      s1 += dn;
+      s2 += dn * nh;
+    }
+    s1 = warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+    float *gi = g_in + (long long)row * C;
+    for (int c = lane; c < C; c += 32) {
+      const float nh = (x[c] - mu) * rs;
+      const float dn = go[c] * w[c];
+      gi[c] += (dn - s1 - nh * s2) * rs;
+      atomicAdd(sw + c, go[c] * nh);
+      atomicAdd(sb + c, go[c]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    atomicAdd(g_w + c, sw[c]);
+    atomicAdd(g_b + c, sb[c]);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// elementwise
+// ------------------------------------------------------------------------------------
+__global__ void add_kernel(float *out, const float *a, const float *b, long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    const float4 x = *reinterpret_cast<const float4 *>(a + i), y = *reinterpret_cast<const float4 *>(b + i);
+    *reinterpret_cast<float4 *>(out + i) = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  } else {
+    for (long long j = i; j < n; ++j) out[j] = a[j] + b[j];
+  }
+}
+
+__device__ __forceinline__ float gelu_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float cube = 0.044715f * x * x * x;
+  const float th = tanhf(k * (x + cube));
+  const float sech2 = 1.f - th * th;
+  return 0.5f * (1.f + th) + x * 0.5f * sech2 * k * (1.f + 3.f * 0.044715f * x * x);
+}
+// g[i] = g[i] * gelu'(pre[i])     (gelu.cu:49-63 computes the same derivative, accumulating)
+__global__ void gelu_backward_kernel(float *g, const float *pre, long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    float4 gv = *reinterpret_cast<float4 *>(g + i);
+    const float4 p = *reinterpret_cast<const float4 *>(pre + i);
+    gv.x *= gelu_grad(p.x); gv.y *= gelu_grad(p.y); gv.z *= gelu_grad(p.z); gv.w *= gelu_grad(p.w);
+    *reinterpret_cast<float4 *>(g + i) = gv;
+  } else {
+    for (long long j = i; j < n; ++j) g[j] *= gelu_grad(pre[j]);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// softmax + cross-entropy, one block per row: loss[row] = -log softmax(logits[row])[target], and the
+// logits row is overwritten with dlogits = (p - onehot) * scale (pad columns V..Vp-1 get 0).
+// (reference: softmax.cu, cross_entropy.cu:24-93; scale = 1 / (B*T).)
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+softmax_xent_kernel(float *logits, float *losses, const int *targets, int V, int Vp, float scale) {
+  __shared__ float red[32];
+  float *row = logits + (long long)blockIdx.x * Vp;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  float mx = -INFINITY;
+  for (int c = tid; c < V; c += blockDim.x) mx = fmaxf(mx, row[c]);
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int i = 1; i < nw; ++i) mx = fmaxf(mx, red[i]);
+  __syncthreads();
+  float s = 0.f;
+  for (int c = tid; c < V; c += blockDim.x) s += expf(row[c] - mx);
+  s = warp_sum(s);
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  s = 0.f;
+  for (int i = 0; i < nw; ++i) s += red[i];
+  const int tgt = targets[blockIdx.x];
+  const float inv = 1.f / s;
+  if (tid == 0) losses[blockIdx.x] = -(row[tgt] - mx - logf(s));
+  __syncthreads();
+  for (int c = tid; c < Vp; c += blockDim.x) {
+    float g = 0.f;
+    if (c < V) g = (expf(row[c] - mx) * inv - (c == tgt ? 1.f : 0.f)) * scale;
+    row[c] = g;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// causal self-attention, flash style, head size 64. qkv[m][3C] = q | k | v, head h at columns h*64.
+// forward: out[m][h*64 + d], lse[b][h][t] = log sum_j exp(q_t.k_j / 8)
+// One thread per query row, 128 rows per block; keys / values stream through shared memory in
+// blocks of 32 and are read as broadcasts.
+// ------------------------------------------------------------------------------------
+constexpr int HS = 64;
+constexpr int ATT_ROWS = 128;
+constexpr int ATT_KB = 32;
+
+__global__ void __launch_bounds__(ATT_ROWS)
+attention_forward_kernel(float *out, float *lse, const float *qkv, int T, int C, int NH) {
+  __shared__ float4 sk[ATT_KB][HS / 4];
+  __shared__ float4 sv[ATT_KB][HS / 4];
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * ATT_ROWS;
+  const int t = q0 + threadIdx.x;
+  const bool live = t < T;
+  const float scale = 0.125f;  // 1 / sqrt(64)
+  const long long base = (long long)b * T * 3 * C;
+  float q[HS], acc[HS];
+  if (live) {
+    const float4 *qp = reinterpret_cast<const float4 *>(qkv + base + (long long)t * 3 * C + h * HS);
+#pragma unroll
+    for (int d = 0; d < HS / 4; ++d) {
+      const float4 v = qp[d];
+      q[4 * d] = v.x * scale; q[4 * d + 1] = v.y * scale; q[4 * d + 2] = v.z * scale; q[4 * d + 3] = v.w * scale;
+    }
+  }
+#pragma unroll
+  for (int d = 0; d < HS; ++d) acc[d] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  const int kend = min(T, q0 + ATT_ROWS);  // causal: no key beyond the block's last query
+  for (int k0 = 0; k0 < kend; k0 += ATT_KB) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < ATT_KB * (HS / 4); i += ATT_ROWS) {
+      const int j = i / (HS / 4), d = i % (HS / 4);
+      const int kt = k0 + j;
+      float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+      if (kt < T) {
+        const float *rowp = qkv + base + (long long)kt * 3 * C + h * HS;
+        kk = reinterpret_cast<const float4 *>(rowp + C)[d];
+        vv = reinterpret_cast<const float4 *>(rowp + 2 * C)[d];
+      }
+      sk[j][d] = kk;
+      sv[j][d] = vv;
+    }
+    __syncthreads();
+    if (!live) continue;
+    const int jmax = min(ATT_KB, t - k0 + 1);  // keys k0 .. t
+    for (int j = 0; j < jmax; ++j) {
+      float s = 0.f;
+#pragma unroll
+      for (int d = 0; d < HS / 4; ++d) {
+        const float4 kk = sk[j][d];
+        s += q[4 * d] * kk.x + q[4 * d + 1] * kk.y + q[4 * d + 2] * kk.z + q[4 * d + 3] * kk.w;
+      }
+      const float mn = fmaxf(m, s);
+      const float corr = __expf(m - mn), p = __expf(s - mn);
+      l = l * corr + p;
+#pragma unroll
+      for (int d = 0; d < HS / 4; ++d) {
+        const float4 vv = sv[j][d];
+        acc[4 * d] = acc[4 * d] * corr + p * vv.x;
+        acc[4 * d + 1] = acc[4 * d + 1] * corr + p * vv.y;
+        acc[4 * d + 2] = acc[4 * d + 2] * corr + p * vv.z;
+        acc[4 * d + 3] = acc[4 * d + 3] * corr + p * vv.w;
+      }
+      m = mn;
+    }
+  }
+  if (live) {
+    const float inv = 1.f / l;
+    float4 *op = reinterpret_cast<float4 *>(out + ((long long)b * T + t) * C + h * HS);
+#pragma unroll
+    for (int d = 0; d < HS / 4; ++d)
+      op[d] = make_float4(acc[4 * d] * inv, acc[4 * d + 1] * inv, acc[4 * d + 2] * inv, acc[4 * d + 3] * inv);
+    lse[((long long)b * NH + h) * T + t] = m + logf(l);
+  }
+}
+
+// delta[b][h][t] = sum_d dout[m][h*64+d] * out[m][h*64+d]
+__global__ void attention_delta_kernel(float *delta, const float *dout, const float *out, int T, int C, int NH,
+                                       long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over B*NH*T
+  if (i >= total) return;
+  const int t = (int)(i % T);
+  const int h = (int)((i / T) % NH);
+  const int b = (int)(i / ((long long)T * NH));
+  const float4 *a = reinterpret_cast<const float4 *>(dout + ((long long)b * T + t) * C + h * HS);
+  const float4 *o = reinterpret_cast<const float4 *>(out + ((long long)b * T + t) * C + h * HS);
+  float s = 0.f;
+#pragma unroll
+  for (int d = 0; d < HS / 4; ++d) {
+    const float4 x = a[d], y = o[d];
+    s += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
+  }
+  delta[i] = s;
+}
+
+// dq: one thread per query row, streaming keys/values (same structure as the forward pass).
+// dS_ij = p_ij (dO_i.V_j - delta_i), dQ_i = sum_j dS_ij K_j / 8
+__global__ void __launch_bounds__(ATT_ROWS)
+attention_backward_dq_kernel(float *dqkv, const float *dout, const float *qkv, const float *lse, const float *delta,
+                             int T, int C, int NH) {
+  __shared__ float4 sk[ATT_KB][HS / 4];
+  __shared__ float4 sv[ATT_KB][HS / 4];
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * ATT_ROWS;
+  const int t = q0 + threadIdx.x;
+  const bool live = t < T;
+  const float scale = 0.125f;
+  const long long base = (long long)b * T * 3 * C;
+  float q[HS], go[HS], acc[HS];
+  float L = 0.f, D = 0.f;
+  if (live) {
+    const float4 *qp = reinterpret_cast<const float4 *>(qkv + base + (long long)t * 3 * C + h * HS);
+    const float4 *gp = reinterpret_cast<const float4 *>(dout + ((long long)b * T + t) * C + h * HS);
+#pragma unroll
+    for (int d = 0; d < HS / 4; ++d) {
+      const float4 v = qp[d], g = gp[d];
+      q[4 * d] = v.x * scale; q[4 * d + 1] = v.y * scale; q[4 * d + 2] = v.z * scale; q[4 * d + 3] = v.w * scale;
+      go[4 * d] = g.x; go[4 * d + 1] = g.y; go[4 * d + 2] = g.z; go[4 * d + 3] = g.w;
+    }
+    L = lse[((long long)b * NH + h) * T + t];
+    D = delta[((long long)b * NH + h) * T + t];
+  }
+#pragma unroll
+  for (int d = 0; d < HS; ++d) acc[d] = 0.f;
+  const int kend = min(T, q0 + ATT_ROWS);
+  for (int k0 = 0; k0 < kend; k0 += ATT_KB) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < ATT_KB * (HS / 4); i += ATT_ROWS) {
+      const int j = i / (HS / 4), d = i % (HS / 4);
+      const int kt = k0 + j;
+      float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+      if (kt < T) {
+        const float *rowp = qkv + base + (long long)kt * 3 * C + h * HS;
+        kk = reinterpret_cast<const float4 *>(rowp + C)[d];
+        vv = reinterpret_cast<const float4 *>(rowp + 2 * C)[d];
+      }
+      sk[j][d] = kk;
+      sv[j][d] = vv;
+    }
+    __syncthreads();
+    if (!live) continue;
+    const int jmax = min(ATT_KB, t - k0 + 1);
+    for (int j = 0; j < jmax; ++j) {
+      float s = 0.f, dp = 0.f;
+#pragma unroll
+      for (int d = 0; d < HS / 4; ++d) {
+        const float4 kk = sk[j][d], vv = sv[j][d];
+        s += q[4 * d] * kk.x + q[4 * d + 1] * kk.y + q[4 * d + 2] * kk.z + q[4 * d + 3] * kk.w;
+        dp += go[4 * d] * vv.x + go[4 * d + 1] * vv.y + go[4 * d + 2] * vv.z + go[4 * d + 3] * vv.w;
+      }
+      const float ds = __expf(s - L) * (dp - D) * scale;
+#pragma unroll
+      for (int d = 0; d < HS / 4; ++d) {
+        const float4 kk = sk[j][d];
+        acc[4 * d] += ds * kk.x; acc[4 * d + 1] += ds * kk.y; acc[4 * d + 2] += ds * kk.z; acc[4 * d + 3] += ds * kk.w;
+      }
+    }
+  }
+  if (live) {
+    float4 *op = reinterpret_cast<float4 *>(dqkv + base + (long long)t * 3 * C + h * HS);
+#pragma unroll
+    for (int d = 0; d < HS / 4; ++d) op[d] = make_float4(acc[4 * d], acc[4 * d + 1], acc[4 * d + 2], acc[4 * d + 3]);
+  }
+}
+
+// dk, dv: TWO threads per key row (each owns half of the head dimension, the two dot products are
+// completed with one shuffle), streaming the queries at or after the key.
+// dV_j = sum_i p_ij dO_i;  dK_j = sum_i dS_ij Q_i / 8
+constexpr int HH = HS / 2;
+__global__ void __launch_bounds__(2 * ATT_ROWS)
+attention_backward_dkv_kernel(float *dqkv, const float *dout, const float *qkv, const float *lse, const float *delta,
+                              int T, int C, int NH) {
+  __shared__ float4 sq[ATT_KB][HS / 4];
+  __shared__ float4 sg[ATT_KB][HS / 4];
+  __shared__ float sl[ATT_KB], sd[ATT_KB];
+  const int b = blockIdx.z, h = blockIdx.y, k0 = blockIdx.x * ATT_ROWS;
+  const int j = k0 + (threadIdx.x >> 1);
+  const int half = threadIdx.x & 1;  // which 32 of the 64 head columns
+  const bool live = j < T;
+  const float scale = 0.125f;
+  const long long base = (long long)b * T * 3 * C;
+  float k[HH], v[HH], dk[HH], dv[HH];
+  if (live) {
+    const float *rowp = qkv + base + (long long)j * 3 * C + h * HS + half * HH;
+    const float4 *kp = reinterpret_cast<const float4 *>(rowp + C);
+    const float4 *vp = reinterpret_cast<const float4 *>(rowp + 2 * C);
+#pragma unroll
+    for (int d = 0; d < HH / 4; ++d) {
+      const float4 a = kp[d], c = vp[d];
+      k[4 * d] = a.x; k[4 * d + 1] = a.y; k[4 * d + 2] = a.z; k[4 * d + 3] = a.w;
+      v[4 * d] = c.x; v[4 * d + 1] = c.y; v[4 * d + 2] = c.z; v[4 * d + 3] = c.w;
+    }
+  } else {
+#pragma unroll
+    for (int d = 0; d < HH; ++d) { k[d] = 0.f; v[d] = 0.f; }
+  }
+#pragma unroll
+  for (int d = 0; d < HH; ++d) { dk[d] = 0.f; dv[d] = 0.f; }
+  for (int i0 = k0; i0 < T; i0 += ATT_KB) {  // queries from the block's first key on
+    __syncthreads();
+    for (int i = threadIdx.x; i < ATT_KB * (HS / 4); i += 2 * ATT_ROWS) {
+      const int r = i / (HS / 4), d = i % (HS / 4);
+      const int qt = i0 + r;
+      float4 qq = make_float4(0.f, 0.f, 0.f, 0.f), gg = qq;
+      if (qt < T) {
+        qq = reinterpret_cast<const float4 *>(qkv + base + (long long)qt * 3 * C + h * HS)[d];
+        gg = reinterpret_cast<const float4 *>(dout + ((long long)b * T + qt) * C + h * HS)[d];
+      }
+      sq[r][d] = qq;
+      sg[r][d] = gg;
+    }
+    if (threadIdx.x < ATT_KB) {
+      const int qt = i0 + threadIdx.x;
+      sl[threadIdx.x] = qt < T ? lse[((long long)b * NH + h) * T + qt] : 0.f;
+      sd[threadIdx.x] = qt < T ? delta[((long long)b * NH + h) * T + qt] : 0.f;
+    }
+    __syncthreads();
+    // both threads of a pair share j, hence the same trip count: the shuffles below stay converged
+    const int rmin = live ? max(0, j - i0) : ATT_KB;  // queries i >= j only
+    const int rmax = min(ATT_KB, T - i0);
+    for (int r = rmin; r < rmax; ++r) {
+      float s = 0.f, dp = 0.f;
+#pragma unroll
+      for (int d = 0; d < HH / 4; ++d) {
+        const float4 qq = sq[r][half * (HH / 4) + d], gg = sg[r][half * (HH / 4) + d];
+        s += k[4 * d] * qq.x + k[4 * d + 1] * qq.y + k[4 * d + 2] * qq.z + k[4 * d + 3] * qq.w;
+        dp += v[4 * d] * gg.x + v[4 * d + 1] * gg.y + v[4 * d + 2] * gg.z + v[4 * d + 3] * gg.w;
+      }
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      dp += __shfl_xor_sync(0xffffffffu, dp, 1);
+      const float p = __expf(s * scale - sl[r]);
+      const float ds = p * (dp - sd[r]) * scale;
+#pragma unroll
+      for (int d = 0; d < HH / 4; ++d) {
+        const float4 qq = sq[r][half * (HH / 4) + d], gg = sg[r][half * (HH / 4) + d];
+        dv[4 * d] += p * gg.x; dv[4 * d + 1] += p * gg.y; dv[4 * d + 2] += p * gg.z; dv[4 * d + 3] += p * gg.w;
+        dk[4 * d] += ds * qq.x; dk[4 * d + 1] += ds * qq.y; dk[4 * d + 2] += ds * qq.z; dk[4 * d + 3] += ds * qq.w;
+      }
+    }
+  }
+  if (live) {
+    float *rowp = dqkv + base + (long long)j * 3 * C + h * HS + half * HH;
+    float4 *kp = reinterpret_cast<float4 *>(rowp + C);
+    float4 *vp = reinterpret_cast<float4 *>(rowp + 2 * C);
+#pragma unroll
+    for (int d = 0; d < HH / 4; ++d) {
+      kp[d] = make_float4(dk[4 * d], dk[4 * d + 1], dk[4 * d + 2], dk[4 * d + 3]);
+      vp[d] = make_float4(dv[4 * d], dv[4 * d + 1], dv[4 * d + 2], dv[4 * d + 3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// AdamW over the flat parameter buffer; decay on every element, bias-corrected (adamw.cu:11-48)
+// ------------------------------------------------------------------------------------
+__global__ void adamw_kernel(float *p, float *m, float *v, const float *g, long long n, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float gi = g[i];
+  const float mi = b1 * m[i] + (1.f - b1) * gi;
+  const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  m[i] = mi;
+  v[i] = vi;
+  const float mh = mi / bc1, vh = vi / bc2;
+  p[i] -= lr * (mh / (sqrtf(vh) + eps) + wd * p[i]);
+}
+
+// ------------------------------------------------------------------------------------
+// launchers
+// ------------------------------------------------------------------------------------
+#define LAUNCH_OK() (count_launch(), cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA)
+
+int embedding_forward(float *out, const int *tokens, const float *wte, const float *wpe, int B, int T, int C, int Vp,
+                      cudaStream_t s) {
+  const long long n = (long long)B * T * C;
+  embedding_forward_kernel<<<cdiv(n, 256), 256, 0, s>>>(out, tokens, wte, wpe, B * T, T, C, Vp);
+  return LAUNCH_OK();
+}
+int embedding_backward(float *g_wte, float *g_wpe, const float *g, const int *tokens, int B, int T, int C, int Vp,
+                       cudaStream_t s) {
+  const long long n = (long long)B * T * C;
+  embedding_backward_kernel<<<cdiv(n, 256), 256, 0, s>>>(g_wte, g_wpe, g, tokens, B * T, T, C, Vp);
+  return LAUNCH_OK();
+}
+int layernorm_forward(float *out, float *mean, float *rstd, const float *in, const float *w, const float *b, int M,
+                      int C, cudaStream_t s) {
+  layernorm_forward_kernel<<<cdiv(M, 8), 256, 0, s>>>(out, mean, rstd, in, w, b, M, C);
+  return LAUNCH_OK();
+}
+int layernorm_backward(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
+                       const float *mean, const float *rstd, int M, int C, cudaStream_t s) {
+  const int rows_per_block = 64;
+  layernorm_backward_kernel<<<cdiv(M, rows_per_block), 256, 2 * C * sizeof(float), s>>>(
+      g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
+  return LAUNCH_OK();
+}
+int add_forward(float *out, const float *a, const float *b, long long n, cudaStream_t s) {
+  add_kernel<<<cdiv((n + 3) / 4, 256), 256, 0, s>>>(out, a, b, n);
+  return LAUNCH_OK();
+}
+int gelu_backward(float *g, const float *pre, long long n, cudaStream_t s) {
+  gelu_backward_kernel<<<cdiv((n + 3) / 4, 256), 256, 0, s>>>(g, pre, n);
+  return LAUNCH_OK();
+}
+int softmax_xent(float *logits, float *losses, const int *targets, int M, int V, int Vp, cudaStream_t s) {
+  softmax_xent_kernel<<<M, 512, 0, s>>>(logits, losses, targets, V, Vp, 1.f / (float)M);
+  return LAUNCH_OK();
+}
+int attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t s) {
+  if (C != NH * HS) return GPT2L_ERR_BAD_ARG;
+  dim3 grid(cdiv(T, ATT_ROWS), NH, B);
+  attention_forward_kernel<<<grid, ATT_ROWS, 0, s>>>(out, lse, qkv, T, C, NH);
+  return LAUNCH_OK();
+}
+int attention_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
+                       const float *lse, int B, int T, int C, int NH, cudaStream_t s) {
+  if (C != NH * HS) return GPT2L_ERR_BAD_ARG;
+  const long long total = (long long)B * NH * T;
+  attention_delta_kernel<<<cdiv(total, 256), 256, 0, s>>>(delta, dout, out, T, C, NH, total);
+  count_launch();
+  dim3 grid(cdiv(T, ATT_ROWS), NH, B);
+  attention_backward_dq_kernel<<<grid, ATT_ROWS, 0, s>>>(dqkv, dout, qkv, lse, delta, T, C, NH);
+  count_launch();
+  attention_backward_dkv_kernel<<<grid, 2 * ATT_ROWS, 0, s>>>(dqkv, dout, qkv, lse, delta, T, C, NH);
+  return LAUNCH_OK();
+}
+int adamw_update(float *p, float *m, float *v, const float *g, long long n, float lr, float b1, float b2, float eps,
+                 float wd, int t, cudaStream_t s) {
+  const float bc1 = 1.f - powf(b1, (float)t), bc2 = 1.f - powf(b2, (float)t);
+  adamw_kernel<<<cdiv(n, 256), 256, 0, s>>>(p, m, v, g, n, lr, b1, b2, eps, wd, bc1, bc2);
+  return LAUNCH_OK();
+}
+
+}  // namespace g2l

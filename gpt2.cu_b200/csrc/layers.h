@@ -1,0 +1,25 @@
+// Launchers of the non-GEMM layers (layers.cu). All take device pointers and a stream and return a
+// GPT2L_* code.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace g2l {
+
+int embedding_forward(float *out, const int *tokens, const float *wte, const float *wpe, int B, int T, int C, int Vp,
+                      cudaStream_t s);
+int embedding_backward(float *g_wte, float *g_wpe, const float *g, const int *tokens, int B, int T, int C, int Vp,
+                       cudaStream_t s);
+int layernorm_forward(float *out, float *mean, float *rstd, const float *in, const float *w, const float *b, int M,
+                      int C, cudaStream_t s);
+int layernorm_backward(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
+                       const float *mean, const float *rstd, int M, int C, cudaStream_t s);
+int add_forward(float *out, const float *a, const float *b, long long n, cudaStream_t s);
+int gelu_backward(float *g, const float *pre, long long n, cudaStream_t s);
+int softmax_xent(float *logits, float *losses, const int *targets, int M, int V, int Vp, cudaStream_t s);
+int attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t s);
+int attention_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
+                       const float *lse, int B, int T, int C, int NH, cudaStream_t s);
+int adamw_update(float *p, float *m, float *v, const float *g, long long n, float lr, float b1, float b2, float eps,
+                 float wd, int t, cudaStream_t s);
+
+}  // namespace g2l

@@ -104,7 +104,6 @@ struct LaunchParams {
   unsigned *counters;
   long long wait_limit_ns;
   int xform_active;  // 0: no op needs the transform warps (TF32 mode, no fused bias gradient)
-  int debug;         // timing experiments only (env GPT2L_DEBUG): 1 no TMA store, 2 no staging either, 4 no tcgen05.ld
 };
 
 // host-side description used to build a GemmOp
@@ -130,6 +129,8 @@ struct DeviceCtx {
   size_t ws_bytes = 0;
   unsigned *ws_sem = nullptr;
   size_t ws_sem_count = 0;
+  float *xt = nullptr;              // transposed activations for wide weight gradients
+  size_t xt_bytes = 0;
   // host-call staging
   float *stage[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t stage_bytes[4] = {0, 0, 0, 0};
@@ -177,6 +178,7 @@ void count_launch(int n = 1);
 // --- linear_simt.cu ---
 int launch_simt(const GemmDesc &d, cudaStream_t stream);
 int launch_colsum(float *out, const float *x, int rows, int cols, cudaStream_t stream);
+int launch_transpose(float *dst, const float *src, int rows, int cols, cudaStream_t stream);
 
 // --- driver entry point for tensor-map encoding ---
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,

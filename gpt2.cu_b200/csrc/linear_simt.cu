@@ -71,6 +71,30 @@ gpt2_linear_colsum_kernel(float *__restrict__ out, const float *__restrict__ x, 
   }
 }
 
+// dst[c][r] = src[r][c] for src[rows][cols]; 32 x 32 tiles through shared memory, both sides coalesced.
+__global__ void __launch_bounds__(256)
+gpt2_linear_transpose_kernel(float *__restrict__ dst, const float *__restrict__ src, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + tx;
+    tile[i][tx] = (r < rows && c < cols) ? src[(long long)r * cols + c] : 0.f;
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + tx;
+    if (c < cols && r < rows) dst[(long long)c * rows + r] = tile[tx][i];
+  }
+}
+
+int launch_transpose(float *dst, const float *src, int rows, int cols, cudaStream_t stream) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+  gpt2_linear_transpose_kernel<<<grid, 256, 0, stream>>>(dst, src, rows, cols);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
 int launch_simt(const GemmDesc &d, cudaStream_t stream) {
   int Mc, Nc, Kc;
   long long ai, ak, bk, bj;

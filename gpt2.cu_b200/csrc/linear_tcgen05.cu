@@ -687,11 +687,6 @@ int set_kernel_attributes() {
 }
 
 static long long default_wait_limit_ns() { return 4000000000ll; }  // 4 s
-int debug_flags() {
-  static int v = -1;
-  if (v < 0) { const char *e = getenv("GPT2L_DEBUG"); v = e ? atoi(e) : 0; }
-  return v;
-}
 
 int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   op.tile_base = 0;
@@ -704,7 +699,6 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.counters = nullptr;
   p.wait_limit_ns = default_wait_limit_ns();
   p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
-  p.debug = debug_flags();
   if (op.pair) {
     const int pairs = op.n_tiles < ctx->max_pairs ? op.n_tiles : ctx->max_pairs;
     if (pairs <= 0) return GPT2L_ERR_CUDA;
@@ -731,7 +725,6 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
   p.xform_active = (any_3x || any_colsum) ? 1 : 0;
-  p.debug = debug_flags();
   if (pair) return pair_launch(nullptr, p, grid, any_3x, stream);
   if (any_3x)
     gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);

@@ -407,14 +407,8 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
           const int nb = n0 + c * 32;
           if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
           uint32_t r[32];
-          if (!(p.debug & 4)) {
-            tmem_ld_32x32(taddr + c * 32, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0;
-          }
-          if (p.debug & 2) continue;
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
           float v[32];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {

@@ -100,6 +100,18 @@ def test_parity_against_reference_model_fixtures(gpu, orc, fx, layer, mode):
         assert orc.max_rel_err(got[3], z[f"{layer}.db"]) <= TOL[mode]
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("M,K,N", [(256, 64, 8192), (132, 36, 8196)])
+def test_wide_weight_gradient_uses_transposed_activations(gpu, orc, M, K, N, mode):
+    """N >= 8192 and N >= 8 K: backward_weight transposes `in` into scratch and runs with a K-major A
+    operand (the lm_head case); the bias gradient is still the fused column sum."""
+    x, w, b, dy = seeded(M, K, N, seed=N)
+    outs = run_all(gpu, x, w, b, dy, mode)
+    check_all(orc, outs, x, w, b, dy, TIGHT[mode])
+    outs = run_all(gpu, x, w, b, dy, mode, deterministic=1, split_k=3)
+    check_all(orc, outs, x, w, b, dy, TIGHT[mode])
+
+
 def test_null_bias_and_null_bias_grad(gpu, orc):
     x, w, b, dy = seeded(256, 64, 128, seed=3)
     y, dx, dw, db = run_all(gpu, x, w, None, dy, 0, want_bias=False)
