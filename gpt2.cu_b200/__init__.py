@@ -47,6 +47,13 @@ EXPORTS = [
     "gpt2_schedule_create", "gpt2_schedule_destroy", "gpt2_schedule_validate", "gpt2_schedule_describe",
     "gpt2_megakernel_run", "gpt2_megakernel_status", "gpt2_schedule_debug_set_expected",
 ]
+# every symbol include/gpt2_model.h declares
+MODEL_EXPORTS = [
+    "gpt2_model_create", "gpt2_model_destroy", "gpt2_model_num_params", "gpt2_model_params", "gpt2_model_grads",
+    "gpt2_model_param_offsets", "gpt2_model_set_params", "gpt2_model_get_params", "gpt2_model_get_grads",
+    "gpt2_model_forward", "gpt2_model_backward", "gpt2_model_update", "gpt2_model_mean_loss",
+    "gpt2_model_device_bytes",
+]
 
 
 class Opts(ctypes.Structure):
@@ -80,6 +87,14 @@ class Op(ctypes.Structure):
         ("bias", ctypes.c_void_p),
         ("opts", Opts),
         ("deps", Dep * MAX_DEPS),
+    ]
+
+
+class ModelConfig(ctypes.Structure):
+    """struct gpt2_model_config"""
+    _fields_ = [
+        ("vocab_size", ctypes.c_int), ("padded_vocab_size", ctypes.c_int), ("n_layer", ctypes.c_int),
+        ("n_head", ctypes.c_int), ("n_embd", ctypes.c_int), ("n_positions", ctypes.c_int),
     ]
 
 
@@ -132,6 +147,35 @@ def _load():
     lib.gpt2_megakernel_status.restype = I
     lib.gpt2_schedule_debug_set_expected.argtypes = [V, I, I, I, I]
     lib.gpt2_schedule_debug_set_expected.restype = I
+    # ---- gpt2_model.h ----
+    LL = ctypes.c_longlong
+    F = ctypes.c_float
+    lib.gpt2_model_create.argtypes = [ctypes.POINTER(ModelConfig), I, I, I, ctypes.POINTER(I)]
+    lib.gpt2_model_create.restype = V
+    lib.gpt2_model_destroy.argtypes = [V]
+    lib.gpt2_model_destroy.restype = None
+    lib.gpt2_model_num_params.argtypes = [V]
+    lib.gpt2_model_num_params.restype = LL
+    lib.gpt2_model_device_bytes.argtypes = [V]
+    lib.gpt2_model_device_bytes.restype = LL
+    lib.gpt2_model_params.argtypes = [V]
+    lib.gpt2_model_params.restype = V
+    lib.gpt2_model_grads.argtypes = [V]
+    lib.gpt2_model_grads.restype = V
+    lib.gpt2_model_param_offsets.argtypes = [V, ctypes.POINTER(LL), I]
+    lib.gpt2_model_param_offsets.restype = I
+    for name in ("gpt2_model_set_params", "gpt2_model_get_params", "gpt2_model_get_grads"):
+        f = getattr(lib, name)
+        f.argtypes = [V, P, LL]
+        f.restype = I
+    lib.gpt2_model_forward.argtypes = [V, P, P, V]
+    lib.gpt2_model_forward.restype = I
+    lib.gpt2_model_backward.argtypes = [V, V]
+    lib.gpt2_model_backward.restype = I
+    lib.gpt2_model_update.argtypes = [V, F, F, F, F, F, I, V]
+    lib.gpt2_model_update.restype = I
+    lib.gpt2_model_mean_loss.argtypes = [V, V]
+    lib.gpt2_model_mean_loss.restype = F
     return lib
 
 
@@ -245,3 +289,65 @@ def describe_schedule(ops, num_sms):
     counts = (ctypes.c_int * 3)()
     code = lib.gpt2_schedule_describe(arr, len(ops), num_sms, ctypes.byref(counts))
     return code, list(counts)
+
+
+class Model:
+    """Owns a gpt2_model (include/gpt2_model.h): GPT-2 training step around the GEMM path."""
+
+    def __init__(self, vocab_size, padded_vocab_size, n_layer, n_head, n_embd, n_positions, B, T, mode=MODE_TF32):
+        self.cfg = ModelConfig(vocab_size, padded_vocab_size, n_layer, n_head, n_embd, n_positions)
+        self.B, self.T = B, T
+        err = ctypes.c_int(0)
+        self.handle = lib.gpt2_model_create(ctypes.byref(self.cfg), B, T, mode, ctypes.byref(err))
+        if not self.handle:
+            raise LinearError("gpt2_model_create", err.value)
+        self.num_params = lib.gpt2_model_num_params(self.handle)
+
+    def offsets(self):
+        n = 4 + 12 * self.cfg.n_layer
+        arr = (ctypes.c_longlong * n)()
+        got = lib.gpt2_model_param_offsets(self.handle, arr, n)
+        if got != n:
+            raise LinearError("gpt2_model_param_offsets", got)
+        return list(arr)
+
+    def set_params(self, host):
+        check("gpt2_model_set_params", lib.gpt2_model_set_params(self.handle, _p(host), host.size))
+
+    def get_params(self, host):
+        check("gpt2_model_get_params", lib.gpt2_model_get_params(self.handle, _p(host), host.size))
+
+    def get_grads(self, host):
+        check("gpt2_model_get_grads", lib.gpt2_model_get_grads(self.handle, _p(host), host.size))
+
+    def params_ptr(self):
+        return lib.gpt2_model_params(self.handle)
+
+    def grads_ptr(self):
+        return lib.gpt2_model_grads(self.handle)
+
+    def forward(self, tokens, targets, stream=None):
+        return lib.gpt2_model_forward(self.handle, _p(tokens), _p(targets), stream)
+
+    def backward(self, stream=None):
+        return lib.gpt2_model_backward(self.handle, stream)
+
+    def update(self, lr, beta1, beta2, eps, weight_decay, t, stream=None):
+        return lib.gpt2_model_update(self.handle, lr, beta1, beta2, eps, weight_decay, t, stream)
+
+    def mean_loss(self, stream=None):
+        return lib.gpt2_model_mean_loss(self.handle, stream)
+
+    def device_bytes(self):
+        return lib.gpt2_model_device_bytes(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib.gpt2_model_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -398,7 +398,9 @@ attention_backward_dkv_kernel(float *dqkv, const float *dout, const float *qkv, 
       sd[threadIdx.x] = qt < T ? delta[((long long)b * NH + h) * T + qt] : 0.f;
     }
     __syncthreads();
-    // both threads of a pair share j, hence the same trip count: the shuffles below stay converged
+    // The two threads of a pair share j and therefore the trip count of this loop; other pairs of
+    // the warp run a different number of iterations, so the shuffles name only the pair's two lanes.
+    const unsigned pair_mask = 3u << (threadIdx.x & 30);
     const int rmin = live ? max(0, j - i0) : ATT_KB;  // queries i >= j only
     const int rmax = min(ATT_KB, T - i0);
     for (int r = rmin; r < rmax; ++r) {
@@ -409,8 +411,8 @@ attention_backward_dkv_kernel(float *dqkv, const float *dout, const float *qkv, 
         s += k[4 * d] * qq.x + k[4 * d + 1] * qq.y + k[4 * d + 2] * qq.z + k[4 * d + 3] * qq.w;
         dp += v[4 * d] * gg.x + v[4 * d + 1] * gg.y + v[4 * d + 2] * gg.z + v[4 * d + 3] * gg.w;
       }
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      dp += __shfl_xor_sync(0xffffffffu, dp, 1);
+      s += __shfl_xor_sync(pair_mask, s, 1);
+      dp += __shfl_xor_sync(pair_mask, dp, 1);
       const float p = __expf(s * scale - sl[r]);
       const float ds = p * (dp - sd[r]) * scale;
 #pragma unroll

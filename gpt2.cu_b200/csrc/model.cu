@@ -1,0 +1,294 @@
+// GPT-2 training step around the linear-layer GEMM path: buffers, forward, backward, AdamW.
+// C ABI in include/gpt2_model.h; the reference counterpart is src/train.cu + src/gpt2.cu of
+// vnnm404/gpt2.cu (same parameter order and tensor layouts, new kernels).
+#include <cuda_runtime.h>
+#include <math.h>
+#include <string.h>
+
+#include <vector>
+
+#include "gpt2_model.h"
+#include "layers.h"
+#include "linear_internal.h"
+
+using namespace g2l;
+
+namespace {
+
+struct LayerParams {  // offsets into the flat parameter / gradient buffers
+  long long ln1_w, ln1_b, qkv_w, qkv_b, proj_w, proj_b, ln2_w, ln2_b, fc_w, fc_b, fcproj_w, fcproj_b;
+};
+
+struct LayerActs {  // device pointers into the activation buffer
+  float *ln1, *ln1_mean, *ln1_rstd, *qkv, *atty, *lse, *res2, *ln2, *ln2_mean, *ln2_rstd, *fc, *fc_gelu, *res3;
+};
+
+}  // namespace
+
+struct gpt2_model {
+  gpt2_model_config cfg;
+  int B = 0, T = 0, mode = 0;
+  long long n_params = 0;
+  long long off_wte = 0, off_wpe = 0, off_lnf_w = 0, off_lnf_b = 0;
+  std::vector<LayerParams> lp;
+  std::vector<long long> tensor_offsets;
+  float *params = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr;
+  float *acts = nullptr;
+  long long acts_floats = 0;
+  float *encoded = nullptr, *lnf = nullptr, *lnf_mean = nullptr, *lnf_rstd = nullptr, *logits = nullptr,
+        *losses = nullptr;
+  float *tmp_c = nullptr;    // [M][C]   GEMM output before a residual add / small gradient scratch
+  float *dresid = nullptr;   // [M][C]   gradient of the residual stream
+  float *dbig = nullptr;     // [M][4C]  gradient scratch (d_fc, d_qkv)
+  float *delta = nullptr;    // [B][NH][T]
+  std::vector<LayerActs> la;
+  const int *tokens = nullptr;  // of the last forward
+  float *h_losses = nullptr;    // pinned
+  long long device_bytes = 0;
+};
+
+#define CK(call)                      \
+  do {                                \
+    int _e = (call);                  \
+    if (_e != GPT2L_OK) return _e;    \
+  } while (0)
+
+static gpt2_linear_opts opts_for(const gpt2_model *m) {
+  gpt2_linear_opts o;
+  memset(&o, 0, sizeof(o));
+  o.mode = m->mode;
+  return o;
+}
+
+extern "C" {
+
+gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mode, int *err) {
+  int dummy;
+  if (!err) err = &dummy;
+  *err = GPT2L_ERR_BAD_ARG;
+  if (!cfg || B <= 0 || T <= 0) return nullptr;
+  const int C = cfg->n_embd, L = cfg->n_layer, V = cfg->vocab_size, Vp = cfg->padded_vocab_size;
+  if (C <= 0 || L <= 0 || cfg->n_head <= 0 || C != cfg->n_head * 64 || V <= 0 || Vp < V || (Vp & 3) || (C & 3) ||
+      T > cfg->n_positions)
+    return nullptr;
+  if (mode != GPT2L_MODE_TF32 && mode != GPT2L_MODE_TF32X3) return nullptr;
+  int e;
+  if (!ctx_current(&e)) { *err = e; return nullptr; }
+
+  gpt2_model *m = new gpt2_model();
+  m->cfg = *cfg;
+  m->B = B; m->T = T; m->mode = mode;
+  // ---- parameter layout (reference order) ----
+  long long off = 0;
+  auto take = [&](long long n) { long long o = off; m->tensor_offsets.push_back(o); off += n; return o; };
+  m->off_wte = take((long long)C * Vp);
+  m->off_wpe = take((long long)cfg->n_positions * C);
+  m->lp.resize(L);
+  for (int l = 0; l < L; ++l) {
+    LayerParams &p = m->lp[l];
+    p.ln1_w = take(C); p.ln1_b = take(C);
+    p.qkv_w = take((long long)C * 3 * C); p.qkv_b = take(3 * C);
+    p.proj_w = take((long long)C * C); p.proj_b = take(C);
+    p.ln2_w = take(C); p.ln2_b = take(C);
+    p.fc_w = take((long long)C * 4 * C); p.fc_b = take(4 * C);
+    p.fcproj_w = take((long long)4 * C * C); p.fcproj_b = take(C);
+  }
+  m->off_lnf_w = take(C);
+  m->off_lnf_b = take(C);
+  m->n_params = off;
+
+  // ---- activations ----
+  const long long M = (long long)B * T;
+  const int NH = cfg->n_head;
+  long long a = 0;
+  auto act = [&](long long n) { long long o = a; a += (n + 3) / 4 * 4; return o; };
+  std::vector<long long> o_layer(L * 13);
+  const long long o_encoded = act(M * C);
+  for (int l = 0; l < L; ++l) {
+    long long *o = &o_layer[l * 13];
+    o[0] = act(M * C); o[1] = act(M); o[2] = act(M);          // ln1, mean, rstd
+    o[3] = act(M * 3 * C);                                    // qkv
+    o[4] = act(M * C);                                        // atty
+    o[5] = act((long long)B * NH * T);                        // lse
+    o[6] = act(M * C);                                        // res2
+    o[7] = act(M * C); o[8] = act(M); o[9] = act(M);          // ln2, mean, rstd
+    o[10] = act(M * 4 * C); o[11] = act(M * 4 * C);           // fc, fc_gelu
+    o[12] = act(M * C);                                       // res3
+  }
+  const long long o_lnf = act(M * C), o_lnf_mean = act(M), o_lnf_rstd = act(M);
+  const long long o_logits = act(M * Vp), o_losses = act(M);
+  const long long o_tmp = act(M * C), o_dres = act(M * C), o_dbig = act(M * 4 * C);
+  const long long o_delta = act((long long)B * NH * T);
+  m->acts_floats = a;
+
+  bool ok = true;
+  const size_t pbytes = (size_t)m->n_params * sizeof(float);
+  ok = ok && cudaMalloc(reinterpret_cast<void **>(&m->params), pbytes) == cudaSuccess;
+  ok = ok && cudaMalloc(reinterpret_cast<void **>(&m->grads), pbytes) == cudaSuccess;
+  ok = ok && cudaMalloc(reinterpret_cast<void **>(&m->m1), pbytes) == cudaSuccess;
+  ok = ok && cudaMalloc(reinterpret_cast<void **>(&m->m2), pbytes) == cudaSuccess;
+  ok = ok && cudaMalloc(reinterpret_cast<void **>(&m->acts), (size_t)a * sizeof(float)) == cudaSuccess;
+  ok = ok && cudaMallocHost(reinterpret_cast<void **>(&m->h_losses), (size_t)M * sizeof(float)) == cudaSuccess;
+  if (!ok) {
+    (void)cudaGetLastError();
+    *err = GPT2L_ERR_CUDA;
+    gpt2_model_destroy(m);
+    return nullptr;
+  }
+  cudaMemset(m->params, 0, pbytes);
+  cudaMemset(m->grads, 0, pbytes);
+  cudaMemset(m->m1, 0, pbytes);
+  cudaMemset(m->m2, 0, pbytes);
+  m->device_bytes = 4ll * (long long)pbytes + a * (long long)sizeof(float);
+  float *A = m->acts;
+  m->encoded = A + o_encoded;
+  m->la.resize(L);
+  for (int l = 0; l < L; ++l) {
+    const long long *o = &o_layer[l * 13];
+    LayerActs &x = m->la[l];
+    x.ln1 = A + o[0]; x.ln1_mean = A + o[1]; x.ln1_rstd = A + o[2]; x.qkv = A + o[3]; x.atty = A + o[4];
+    x.lse = A + o[5]; x.res2 = A + o[6]; x.ln2 = A + o[7]; x.ln2_mean = A + o[8]; x.ln2_rstd = A + o[9];
+    x.fc = A + o[10]; x.fc_gelu = A + o[11]; x.res3 = A + o[12];
+  }
+  m->lnf = A + o_lnf; m->lnf_mean = A + o_lnf_mean; m->lnf_rstd = A + o_lnf_rstd;
+  m->logits = A + o_logits; m->losses = A + o_losses;
+  m->tmp_c = A + o_tmp; m->dresid = A + o_dres; m->dbig = A + o_dbig; m->delta = A + o_delta;
+  *err = GPT2L_OK;
+  return m;
+}
+
+void gpt2_model_destroy(gpt2_model *m) {
+  if (!m) return;
+  if (m->params) cudaFree(m->params);
+  if (m->grads) cudaFree(m->grads);
+  if (m->m1) cudaFree(m->m1);
+  if (m->m2) cudaFree(m->m2);
+  if (m->acts) cudaFree(m->acts);
+  if (m->h_losses) cudaFreeHost(m->h_losses);
+  delete m;
+}
+
+long long gpt2_model_num_params(const gpt2_model *m) { return m ? m->n_params : 0; }
+float *gpt2_model_params(gpt2_model *m) { return m ? m->params : nullptr; }
+float *gpt2_model_grads(gpt2_model *m) { return m ? m->grads : nullptr; }
+long long gpt2_model_device_bytes(const gpt2_model *m) { return m ? m->device_bytes : 0; }
+
+int gpt2_model_param_offsets(const gpt2_model *m, long long *offsets, int max) {
+  if (!m || !offsets) return GPT2L_ERR_BAD_ARG;
+  const int n = (int)m->tensor_offsets.size();
+  if (max < n) return GPT2L_ERR_TOO_LARGE;
+  for (int i = 0; i < n; ++i) offsets[i] = m->tensor_offsets[i];
+  return n;
+}
+
+int gpt2_model_set_params(gpt2_model *m, const float *host, long long count) {
+  if (!m || !host || count != m->n_params) return GPT2L_ERR_BAD_ARG;
+  return cudaMemcpy(m->params, host, (size_t)count * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess
+             ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+int gpt2_model_get_params(gpt2_model *m, float *host, long long count) {
+  if (!m || !host || count != m->n_params) return GPT2L_ERR_BAD_ARG;
+  return cudaMemcpy(host, m->params, (size_t)count * sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess
+             ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+int gpt2_model_get_grads(gpt2_model *m, float *host, long long count) {
+  if (!m || !host || count != m->n_params) return GPT2L_ERR_BAD_ARG;
+  return cudaMemcpy(host, m->grads, (size_t)count * sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess
+             ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt2l_stream_t stream) {
+  if (!m || !tokens || !targets) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int B = m->B, T = m->T, C = m->cfg.n_embd, L = m->cfg.n_layer, NH = m->cfg.n_head;
+  const int V = m->cfg.vocab_size, Vp = m->cfg.padded_vocab_size;
+  const int M = B * T;
+  float *P = m->params;
+  gpt2_linear_opts o = opts_for(m);
+  m->tokens = tokens;
+  CK(embedding_forward(m->encoded, tokens, P + m->off_wte, P + m->off_wpe, B, T, C, Vp, st));
+  const float *res = m->encoded;
+  for (int l = 0; l < L; ++l) {
+    const LayerParams &p = m->lp[l];
+    LayerActs &a = m->la[l];
+    CK(layernorm_forward(a.ln1, a.ln1_mean, a.ln1_rstd, res, P + p.ln1_w, P + p.ln1_b, M, C, st));
+    CK(gpt2_linear_forward(a.qkv, a.ln1, P + p.qkv_w, P + p.qkv_b, B, T, C, 3 * C, &o, stream));
+    CK(attention_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st));
+    CK(gpt2_linear_forward(m->tmp_c, a.atty, P + p.proj_w, P + p.proj_b, B, T, C, C, &o, stream));
+    CK(add_forward(a.res2, res, m->tmp_c, (long long)M * C, st));
+    CK(layernorm_forward(a.ln2, a.ln2_mean, a.ln2_rstd, a.res2, P + p.ln2_w, P + p.ln2_b, M, C, st));
+    gpt2_linear_opts og = o;  // fc: the epilogue stores the pre-activation and its GELU in one pass
+    og.flags = GPT2L_EPI_GELU_DUAL;
+    og.out2 = a.fc_gelu;
+    CK(gpt2_linear_forward(a.fc, a.ln2, P + p.fc_w, P + p.fc_b, B, T, C, 4 * C, &og, stream));
+    CK(gpt2_linear_forward(m->tmp_c, a.fc_gelu, P + p.fcproj_w, P + p.fcproj_b, B, T, 4 * C, C, &o, stream));
+    CK(add_forward(a.res3, a.res2, m->tmp_c, (long long)M * C, st));
+    res = a.res3;
+  }
+  CK(layernorm_forward(m->lnf, m->lnf_mean, m->lnf_rstd, res, P + m->off_lnf_w, P + m->off_lnf_b, M, C, st));
+  CK(gpt2_linear_forward(m->logits, m->lnf, P + m->off_wte, nullptr, B, T, C, Vp, &o, stream));
+  CK(softmax_xent(m->logits, m->losses, targets, M, V, Vp, st));
+  return GPT2L_OK;
+}
+
+int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream) {
+  if (!m || !m->tokens) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int B = m->B, T = m->T, C = m->cfg.n_embd, L = m->cfg.n_layer, NH = m->cfg.n_head;
+  const int Vp = m->cfg.padded_vocab_size;
+  const int M = B * T;
+  float *P = m->params, *G = m->grads;
+  gpt2_linear_opts o = opts_for(m);
+  if (cudaMemsetAsync(G, 0, (size_t)m->n_params * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
+  if (cudaMemsetAsync(m->dresid, 0, (size_t)M * C * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
+  // lm_head: the logits buffer holds dlogits since the forward pass
+  CK(gpt2_linear_backward_input(m->tmp_c, m->logits, P + m->off_wte, B, T, C, Vp, &o, stream));
+  CK(gpt2_linear_backward_weight(G + m->off_wte, nullptr, m->logits, m->lnf, B, T, C, Vp, &o, stream));
+  const float *res_last = L > 0 ? m->la[L - 1].res3 : m->encoded;
+  CK(layernorm_backward(m->dresid, G + m->off_lnf_w, G + m->off_lnf_b, m->tmp_c, res_last, P + m->off_lnf_w,
+                        m->lnf_mean, m->lnf_rstd, M, C, st));
+  for (int l = L - 1; l >= 0; --l) {
+    const LayerParams &p = m->lp[l];
+    LayerActs &a = m->la[l];
+    const float *res_in = l > 0 ? m->la[l - 1].res3 : m->encoded;
+    // MLP: res3 = res2 + fcproj(gelu(fc(ln2(res2))))
+    CK(gpt2_linear_backward_input(m->dbig, m->dresid, P + p.fcproj_w, B, T, 4 * C, C, &o, stream));
+    CK(gpt2_linear_backward_weight(G + p.fcproj_w, G + p.fcproj_b, m->dresid, a.fc_gelu, B, T, 4 * C, C, &o, stream));
+    CK(gelu_backward(m->dbig, a.fc, (long long)M * 4 * C, st));
+    CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.fc_w, B, T, C, 4 * C, &o, stream));
+    CK(gpt2_linear_backward_weight(G + p.fc_w, G + p.fc_b, m->dbig, a.ln2, B, T, C, 4 * C, &o, stream));
+    CK(layernorm_backward(m->dresid, G + p.ln2_w, G + p.ln2_b, m->tmp_c, a.res2, P + p.ln2_w, a.ln2_mean, a.ln2_rstd,
+                          M, C, st));
+    // attention: res2 = res_in + proj(attention(qkv(ln1(res_in))))
+    CK(gpt2_linear_backward_input(m->tmp_c, m->dresid, P + p.proj_w, B, T, C, C, &o, stream));
+    CK(gpt2_linear_backward_weight(G + p.proj_w, G + p.proj_b, m->dresid, a.atty, B, T, C, C, &o, stream));
+    CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
+    CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.qkv_w, B, T, C, 3 * C, &o, stream));
+    CK(gpt2_linear_backward_weight(G + p.qkv_w, G + p.qkv_b, m->dbig, a.ln1, B, T, C, 3 * C, &o, stream));
+    CK(layernorm_backward(m->dresid, G + p.ln1_w, G + p.ln1_b, m->tmp_c, res_in, P + p.ln1_w, a.ln1_mean, a.ln1_rstd,
+                          M, C, st));
+  }
+  CK(embedding_backward(G + m->off_wte, G + m->off_wpe, m->dresid, m->tokens, B, T, C, Vp, st));
+  return GPT2L_OK;
+}
+
+int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
+                      gpt2l_stream_t stream) {
+  if (!m || t < 1) return GPT2L_ERR_BAD_ARG;
+  return adamw_update(m->params, m->m1, m->m2, m->grads, m->n_params, lr, beta1, beta2, eps, weight_decay, t,
+                      static_cast<cudaStream_t>(stream));
+}
+
+float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream) {
+  if (!m) return NAN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long M = (long long)m->B * m->T;
+  if (cudaMemcpyAsync(m->h_losses, m->losses, (size_t)M * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    return NAN;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return NAN;
+  double s = 0.0;
+  for (long long i = 0; i < M; ++i) s += m->h_losses[i];
+  return (float)(s / (double)M);
+}
+
+}  // extern "C"

@@ -1,0 +1,70 @@
+/*
+ * gpt2_model.h — C ABI of the GPT-2 training step built around the linear-layer GEMM path.
+ *
+ * This is the caller side of the hot path: what src/train.cu of vnnm404/gpt2.cu does with
+ * setup_train_buffers / forward / cross_entropy / backward / gpt2_update / gpt2_zero_grad /
+ * compute_mean_loss (include/gpt2/train.h:49-58), with the reference's parameter order and tensor
+ * layouts (src/gpt2.cu:48-198: wte[C][V], wpe[n_positions][C], then per layer ln_1.w, ln_1.b,
+ * qkv_w[C][3C], qkv_b, proj_w[C][C], proj_b, ln_2.w, ln_2.b, fc_w[C][4C], fc_b, fcproj_w[4C][C],
+ * fcproj_b, then ln_f.w, ln_f.b), every linear weight stored [in][out]. The vocabulary dimension of
+ * wte and of the logits is padded (50257 -> 50304) so that the lm_head GEMMs run on the tensor cores;
+ * pad columns of wte are kept at zero.
+ *
+ * All 15 GEMM kinds of a step go through gpt2_linear_forward / _backward_input / _backward_weight;
+ * the other layers are CUDA-core kernels of this library (attention is flash-style: no [B,NH,T,T]
+ * tensors). Requires gpt2_linear_init() on the device first.
+ */
+#ifndef GPT2_MODEL_H
+#define GPT2_MODEL_H
+
+#include "gpt2_linear.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gpt2_model_config {
+  int vocab_size;        /* 50257                                          */
+  int padded_vocab_size; /* row stride of wte / logits, multiple of 4      */
+  int n_layer;
+  int n_head;            /* n_embd / n_head must be 64                     */
+  int n_embd;
+  int n_positions;       /* rows of wpe (1024)                             */
+} gpt2_model_config;
+
+typedef struct gpt2_model gpt2_model; /* opaque: parameters, gradients, AdamW moments, activations */
+
+/* Allocates everything for batches of B sequences of T tokens. mode = enum gpt2l_mode for every
+ * GEMM. Parameters start at zero: fill them with gpt2_model_set_params. */
+gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mode, int *err);
+void gpt2_model_destroy(gpt2_model *m);
+
+long long gpt2_model_num_params(const gpt2_model *m); /* floats, padded vocabulary included */
+float *gpt2_model_params(gpt2_model *m);              /* device pointer, flat, order above   */
+float *gpt2_model_grads(gpt2_model *m);               /* device pointer, same layout         */
+/* Offsets (in floats) of the 4 + 12*n_layer tensors inside the flat buffers, in order; returns
+ * the number of tensors, or a negative error when `max` is too small. */
+int gpt2_model_param_offsets(const gpt2_model *m, long long *offsets, int max);
+int gpt2_model_set_params(gpt2_model *m, const float *host, long long count);
+int gpt2_model_get_params(gpt2_model *m, float *host, long long count);
+int gpt2_model_get_grads(gpt2_model *m, float *host, long long count);
+
+/* embedding -> blocks -> ln_f -> lm_head -> softmax/cross-entropy. tokens/targets: device int32
+ * [B*T]. Leaves the per-token losses and dlogits in the model (forward + cross_entropy of the
+ * reference, src/train.cu:334-389). */
+int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt2l_stream_t stream);
+/* Zeroes the gradients, then the whole backward pass (gpt2_zero_grad + backward, src/train.cu:391-448). */
+int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream);
+/* AdamW over the flat parameter buffer, step count t >= 1 (gpt2_update, src/train.cu:450-481). */
+int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
+                      gpt2l_stream_t stream);
+/* Synchronises the stream and returns the mean of the per-token losses of the last forward
+ * (compute_mean_loss, src/train.cu:36-49). NaN on error. */
+float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream);
+/* Bytes of device memory the model holds. */
+long long gpt2_model_device_bytes(const gpt2_model *m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPT2_MODEL_H */

@@ -9,8 +9,8 @@ import pytest
 from conftest import ROOT
 
 
-def header_functions():
-    src = open(os.path.join(ROOT, "include", "gpt2_linear.h")).read()
+def header_functions(name="gpt2_linear.h"):
+    src = open(os.path.join(ROOT, "include", name)).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
     return sorted(set(re.findall(r"\b(gpt2_[a-z0-9_]+)\s*\(", src)))
 
@@ -21,6 +21,13 @@ def test_library_exports_every_declared_symbol(g):
     for n in names:
         assert hasattr(g.lib, n), f"{n} declared in include/gpt2_linear.h but not exported"
     assert sorted(names) == sorted(g.EXPORTS)
+
+
+def test_library_exports_every_model_symbol(g):
+    names = [n for n in header_functions("gpt2_model.h") if n.startswith("gpt2_model_")]
+    assert sorted(names) == sorted(g.MODEL_EXPORTS)
+    for n in names:
+        assert hasattr(g.lib, n)
 
 
 def test_version(g):
