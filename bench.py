@@ -366,6 +366,10 @@ def run_ours(args):
     e2e = measure_e2e(g, torch, opts, stream, world, barrier, dist if world > 1 else None,
                       steps=max(1, min(args.steps, 2)))
 
+    # ---- the GEMM path inside a whole training step (GPT-2 small, B=16 per GPU, T=1024)
+    train = None if args.no_train else measure_train(g, dp, torch, local_rank, rank, world, barrier,
+                                                      dist if world > 1 else None, mode)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -395,6 +399,8 @@ def run_ours(args):
     }
     if base:
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if train:
+        line["train"] = train
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -404,6 +410,55 @@ def run_ours(args):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over the
 # 15 launches of one step, from the ncu capture summarised under profiles/ (None until captured).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=16, T=1024, steps=5, warmup=2):
+    """Tokens/s of whole training steps (forward, backward, gradient all-reduce over NCCL overlapped
+    with the backward pass, AdamW) of GPT-2 small at B sequences of T tokens per GPU, random-init
+    weights and uniform random tokens: the configuration BASELINE.json calls the megakernel step."""
+    import numpy as np
+
+    C, V, Vp, L = 768, 50257, 50304, 12
+    model = g.Model(V, Vp, L, 12, C, 1024, B, T, mode=mode)
+    rng = np.random.default_rng(42)  # same weights on every rank
+    params = rng.standard_normal(model.num_params, dtype=np.float32) * np.float32(0.02)
+    offs = model.offsets()
+    params[: C * Vp].reshape(C, Vp)[:, V:] = 0
+    for i in [2 + 12 * l + k for l in range(L) for k in (0, 6)] + [2 + 12 * L]:
+        params[offs[i]: offs[i] + C] = 1.0  # layernorm weights
+    model.set_params(params)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    tok = torch.randint(0, V, (B * T,), dtype=torch.int32, device="cuda", generator=gen)
+    tgt = torch.randint(0, V, (B * T,), dtype=torch.int32, device="cuda", generator=gen)
+    step = dp.DataParallelStep(model, torch.device("cuda", local_rank))
+    stream = torch.cuda.current_stream().cuda_stream
+    hyper = (3e-4, 0.9, 0.95, 1e-8, 0.1)
+    t = 0
+    for _ in range(warmup):
+        t += 1
+        if step(tok, tgt, *hyper, t, stream) != 0:
+            raise SystemExit("training step failed")
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        t += 1
+        step(tok, tgt, *hyper, t, stream)
+    e.record()
+    barrier()
+    ms = s.elapsed_time(e)
+    loss = model.mean_loss()
+    if dist is not None:
+        tt = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = tt.item()
+    out = {"tokens_per_s": B * T * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps,
+           "config": f"GPT-2 small (12 layers, 768 wide, vocabulary 50257 padded to 50304), B={B} per GPU, T={T}, "
+                     f"AdamW lr 3e-4 betas 0.9/0.95 wd 0.1, fp32 master weights, {'3xTF32' if mode else 'TF32'} GEMMs, "
+                     "flash-style CUDA-core attention", "loss_after": loss,
+           "gradient_exchange": "none (1 GPU)" if world == 1 else "NCCL average, one bucket per block, overlapped"}
+    model.close()
+    return out
 
 
 def measure_e2e(g, torch, opts, stream, world, barrier, dist, steps):
@@ -461,6 +516,7 @@ def main():
     ap.add_argument("--rows", type=int, default=M_ROWS, help="rows per GPU (profiling aid; default is the workload)")
     ap.add_argument("--only", default="", help="comma list like lm_head.fwd,qkv.wgrad (profiling aid)")
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true", help="kernel-only run (profiling aid)")
+    ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the whole-training-step leg")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

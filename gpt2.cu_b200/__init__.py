@@ -52,6 +52,7 @@ MODEL_EXPORTS = [
     "gpt2_model_create", "gpt2_model_destroy", "gpt2_model_num_params", "gpt2_model_params", "gpt2_model_grads",
     "gpt2_model_param_offsets", "gpt2_model_set_params", "gpt2_model_get_params", "gpt2_model_get_grads",
     "gpt2_model_forward", "gpt2_model_backward", "gpt2_model_update", "gpt2_model_mean_loss",
+    "gpt2_model_backward_head", "gpt2_model_backward_layer", "gpt2_model_backward_embedding",
     "gpt2_model_device_bytes",
 ]
 
@@ -172,6 +173,12 @@ def _load():
     lib.gpt2_model_forward.restype = I
     lib.gpt2_model_backward.argtypes = [V, V]
     lib.gpt2_model_backward.restype = I
+    lib.gpt2_model_backward_head.argtypes = [V, V]
+    lib.gpt2_model_backward_head.restype = I
+    lib.gpt2_model_backward_layer.argtypes = [V, I, V]
+    lib.gpt2_model_backward_layer.restype = I
+    lib.gpt2_model_backward_embedding.argtypes = [V, V]
+    lib.gpt2_model_backward_embedding.restype = I
     lib.gpt2_model_update.argtypes = [V, F, F, F, F, F, I, V]
     lib.gpt2_model_update.restype = I
     lib.gpt2_model_mean_loss.argtypes = [V, V]
@@ -331,6 +338,15 @@ class Model:
 
     def backward(self, stream=None):
         return lib.gpt2_model_backward(self.handle, stream)
+
+    def backward_head(self, stream=None):
+        return lib.gpt2_model_backward_head(self.handle, stream)
+
+    def backward_layer(self, l, stream=None):
+        return lib.gpt2_model_backward_layer(self.handle, l, stream)
+
+    def backward_embedding(self, stream=None):
+        return lib.gpt2_model_backward_embedding(self.handle, stream)
 
     def update(self, lr, beta1, beta2, eps, weight_decay, t, stream=None):
         return lib.gpt2_model_update(self.handle, lr, beta1, beta2, eps, weight_decay, t, stream)

@@ -231,10 +231,12 @@ int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt
   return GPT2L_OK;
 }
 
-int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream) {
+// The backward pass in three parts, so that a data-parallel driver can hand each finished slice of
+// the gradient buffer to the all-reduce while the next part computes.
+int gpt2_model_backward_head(gpt2_model *m, gpt2l_stream_t stream) {
   if (!m || !m->tokens) return GPT2L_ERR_BAD_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int B = m->B, T = m->T, C = m->cfg.n_embd, L = m->cfg.n_layer, NH = m->cfg.n_head;
+  const int B = m->B, T = m->T, C = m->cfg.n_embd, L = m->cfg.n_layer;
   const int Vp = m->cfg.padded_vocab_size;
   const int M = B * T;
   float *P = m->params, *G = m->grads;
@@ -247,29 +249,49 @@ int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream) {
   const float *res_last = L > 0 ? m->la[L - 1].res3 : m->encoded;
   CK(layernorm_backward(m->dresid, G + m->off_lnf_w, G + m->off_lnf_b, m->tmp_c, res_last, P + m->off_lnf_w,
                         m->lnf_mean, m->lnf_rstd, M, C, st));
-  for (int l = L - 1; l >= 0; --l) {
-    const LayerParams &p = m->lp[l];
-    LayerActs &a = m->la[l];
-    const float *res_in = l > 0 ? m->la[l - 1].res3 : m->encoded;
-    // MLP: res3 = res2 + fcproj(gelu(fc(ln2(res2))))
-    CK(gpt2_linear_backward_input(m->dbig, m->dresid, P + p.fcproj_w, B, T, 4 * C, C, &o, stream));
-    CK(gpt2_linear_backward_weight(G + p.fcproj_w, G + p.fcproj_b, m->dresid, a.fc_gelu, B, T, 4 * C, C, &o, stream));
-    CK(gelu_backward(m->dbig, a.fc, (long long)M * 4 * C, st));
-    CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.fc_w, B, T, C, 4 * C, &o, stream));
-    CK(gpt2_linear_backward_weight(G + p.fc_w, G + p.fc_b, m->dbig, a.ln2, B, T, C, 4 * C, &o, stream));
-    CK(layernorm_backward(m->dresid, G + p.ln2_w, G + p.ln2_b, m->tmp_c, a.res2, P + p.ln2_w, a.ln2_mean, a.ln2_rstd,
-                          M, C, st));
-    // attention: res2 = res_in + proj(attention(qkv(ln1(res_in))))
-    CK(gpt2_linear_backward_input(m->tmp_c, m->dresid, P + p.proj_w, B, T, C, C, &o, stream));
-    CK(gpt2_linear_backward_weight(G + p.proj_w, G + p.proj_b, m->dresid, a.atty, B, T, C, C, &o, stream));
-    CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
-    CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.qkv_w, B, T, C, 3 * C, &o, stream));
-    CK(gpt2_linear_backward_weight(G + p.qkv_w, G + p.qkv_b, m->dbig, a.ln1, B, T, C, 3 * C, &o, stream));
-    CK(layernorm_backward(m->dresid, G + p.ln1_w, G + p.ln1_b, m->tmp_c, res_in, P + p.ln1_w, a.ln1_mean, a.ln1_rstd,
-                          M, C, st));
-  }
-  CK(embedding_backward(G + m->off_wte, G + m->off_wpe, m->dresid, m->tokens, B, T, C, Vp, st));
   return GPT2L_OK;
+}
+
+int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream) {
+  if (!m || !m->tokens || l < 0 || l >= m->cfg.n_layer) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int B = m->B, T = m->T, C = m->cfg.n_embd, NH = m->cfg.n_head;
+  const int M = B * T;
+  float *P = m->params, *G = m->grads;
+  gpt2_linear_opts o = opts_for(m);
+  const LayerParams &p = m->lp[l];
+  LayerActs &a = m->la[l];
+  const float *res_in = l > 0 ? m->la[l - 1].res3 : m->encoded;
+  // MLP: res3 = res2 + fcproj(gelu(fc(ln2(res2))))
+  CK(gpt2_linear_backward_input(m->dbig, m->dresid, P + p.fcproj_w, B, T, 4 * C, C, &o, stream));
+  CK(gpt2_linear_backward_weight(G + p.fcproj_w, G + p.fcproj_b, m->dresid, a.fc_gelu, B, T, 4 * C, C, &o, stream));
+  CK(gelu_backward(m->dbig, a.fc, (long long)M * 4 * C, st));
+  CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.fc_w, B, T, C, 4 * C, &o, stream));
+  CK(gpt2_linear_backward_weight(G + p.fc_w, G + p.fc_b, m->dbig, a.ln2, B, T, C, 4 * C, &o, stream));
+  CK(layernorm_backward(m->dresid, G + p.ln2_w, G + p.ln2_b, m->tmp_c, a.res2, P + p.ln2_w, a.ln2_mean, a.ln2_rstd,
+                        M, C, st));
+  // attention: res2 = res_in + proj(attention(qkv(ln1(res_in))))
+  CK(gpt2_linear_backward_input(m->tmp_c, m->dresid, P + p.proj_w, B, T, C, C, &o, stream));
+  CK(gpt2_linear_backward_weight(G + p.proj_w, G + p.proj_b, m->dresid, a.atty, B, T, C, C, &o, stream));
+  CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
+  CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.qkv_w, B, T, C, 3 * C, &o, stream));
+  CK(gpt2_linear_backward_weight(G + p.qkv_w, G + p.qkv_b, m->dbig, a.ln1, B, T, C, 3 * C, &o, stream));
+  CK(layernorm_backward(m->dresid, G + p.ln1_w, G + p.ln1_b, m->tmp_c, res_in, P + p.ln1_w, a.ln1_mean, a.ln1_rstd,
+                        M, C, st));
+  return GPT2L_OK;
+}
+
+int gpt2_model_backward_embedding(gpt2_model *m, gpt2l_stream_t stream) {
+  if (!m || !m->tokens) return GPT2L_ERR_BAD_ARG;
+  return embedding_backward(m->grads + m->off_wte, m->grads + m->off_wpe, m->dresid, m->tokens, m->B, m->T,
+                            m->cfg.n_embd, m->cfg.padded_vocab_size, static_cast<cudaStream_t>(stream));
+}
+
+int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream) {
+  if (!m) return GPT2L_ERR_BAD_ARG;
+  CK(gpt2_model_backward_head(m, stream));
+  for (int l = m->cfg.n_layer - 1; l >= 0; --l) CK(gpt2_model_backward_layer(m, l, stream));
+  return gpt2_model_backward_embedding(m, stream);
 }
 
 int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,

@@ -73,3 +73,57 @@ class GradientExchange:
         for ev in self.pending:
             torch.cuda.current_stream().wait_event(ev)
         self.pending = []
+
+
+class _DeviceView:
+    """Exposes a raw device pointer of `count` fp32 values through __cuda_array_interface__."""
+
+    def __init__(self, ptr, count):
+        self.__cuda_array_interface__ = {"shape": (int(count),), "typestr": "<f4", "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+
+
+def device_tensor(ptr, count, device):
+    """A torch tensor aliasing `count` floats at device address `ptr` (no copy, no ownership)."""
+    return torch.as_tensor(_DeviceView(ptr, count), device=device)
+
+
+class DataParallelStep:
+    """One data-parallel training step of a gpt2_model (include/gpt2_model.h) per call.
+
+    Every rank runs the forward and backward pass on its own batch; the flat gradient buffer is
+    averaged across ranks in buckets, in the order the backward pass completes them — ln_f with the
+    last block, then one bucket per block going down, then wte + wpe after the embedding backward —
+    each on the side stream while the next block's backward runs on the compute stream (the
+    backward_weight GEMMs of block l-1 hide the exchange of block l). AdamW runs replicated after the
+    last bucket has landed. With one rank the exchange is a no-op."""
+
+    def __init__(self, model, device, group=None):
+        self.model = model
+        self.exchange = GradientExchange(group)
+        self.L = model.cfg.n_layer
+        offs = model.offsets() + [model.num_params]
+        self.flat = device_tensor(model.grads_ptr(), model.num_params, device)
+        # tensor index: 0 wte, 1 wpe, 2 + 12*l ... block l, then ln_f.w, ln_f.b
+        self.block = [(offs[2 + 12 * l], offs[2 + 12 * (l + 1)]) for l in range(self.L)]
+        self.embed = (offs[0], offs[2])
+        self.lnf = (offs[2 + 12 * self.L], offs[-1])
+
+    def _slice(self, rng):
+        return self.flat[rng[0]:rng[1]]
+
+    def __call__(self, tokens, targets, lr, beta1, beta2, eps, weight_decay, t, stream=None):
+        m = self.model
+        rc = m.forward(tokens, targets, stream)
+        rc |= m.backward_head(stream)
+        for l in range(self.L - 1, -1, -1):
+            rc |= m.backward_layer(l, stream)
+            bucket = [self._slice(self.block[l])]
+            if l == self.L - 1:
+                bucket.append(self._slice(self.lnf))
+            self.exchange.exchange(bucket)
+        rc |= m.backward_embedding(stream)
+        self.exchange.exchange([self._slice(self.embed)])
+        self.exchange.finish()
+        rc |= m.update(lr, beta1, beta2, eps, weight_decay, t, stream)
+        return rc

@@ -55,6 +55,13 @@ int gpt2_model_get_grads(gpt2_model *m, float *host, long long count);
 int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt2l_stream_t stream);
 /* Zeroes the gradients, then the whole backward pass (gpt2_zero_grad + backward, src/train.cu:391-448). */
 int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream);
+/* The same backward pass in parts, for data-parallel drivers that overlap the gradient exchange with
+ * the computation: head (zeroes the gradients; lm_head and ln_f), one transformer block (call with
+ * l = n_layer-1 ... 0; afterwards the gradients of block l are final), and the embedding (afterwards
+ * wte and wpe are final). gpt2_model_backward is exactly head, every layer, embedding. */
+int gpt2_model_backward_head(gpt2_model *m, gpt2l_stream_t stream);
+int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream);
+int gpt2_model_backward_embedding(gpt2_model *m, gpt2l_stream_t stream);
 /* AdamW over the flat parameter buffer, step count t >= 1 (gpt2_update, src/train.cu:450-481). */
 int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
                       gpt2l_stream_t stream);

@@ -1,0 +1,82 @@
+"""Two-GPU test of the data-parallel training step: two ranks, each with half of a batch, must end
+up with the gradients (and, after AdamW, the parameters) that one GPU computes on the whole batch.
+Needs two GPUs; on a one-GPU machine it is skipped (the host logic is covered by the gloo tests)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch.distributed as dist
+
+    import __graft_entry__ as ge
+    import gpt2_ref
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    g = ge.load_package()
+    g.init(rank)
+    dp = ge._load_module("gpt2cu_b200_dp", os.path.join(ROOT, "gpt2.cu_b200", "dp.py"))
+    z = golden("llm_train_tiny.npz")
+    n_layer, n_head, n_embd, vocab, padded, block, B, T, steps = (int(v) for v in z["meta"])
+    params = gpt2_ref.to_flat(gpt2_ref.init_params(vocab, block, n_layer, n_head, n_embd), n_layer, padded)
+    tokens, targets = z["tokens"], z["targets"]  # [B, T] with B = 2: one sequence per rank
+    hyper = tuple(float(v) for v in z["hyper"])
+    per = B // world
+    m = g.Model(vocab, padded, n_layer, n_head, n_embd, block, per, T, mode=g.MODE_TF32X3)
+    m.set_params(params)
+    tok = torch.from_numpy(tokens[rank * per:(rank + 1) * per].reshape(-1).copy()).cuda()
+    tgt = torch.from_numpy(targets[rank * per:(rank + 1) * per].reshape(-1).copy()).cuda()
+    step = dp.DataParallelStep(m, torch.device("cuda", rank))
+    assert step(tok, tgt, *hyper, 1) == 0
+    torch.cuda.synchronize()
+    grads = np.empty_like(params)
+    m.get_grads(grads)
+    after = np.empty_like(params)
+    m.get_params(after)
+    ok = True
+    if rank == 0:
+        full = g.Model(vocab, padded, n_layer, n_head, n_embd, block, B, T, mode=g.MODE_TF32X3)
+        full.set_params(params)
+        ft = torch.from_numpy(tokens.reshape(-1).copy()).cuda()
+        fg = torch.from_numpy(targets.reshape(-1).copy()).cuda()
+        assert full.forward(ft, fg) == 0 and full.backward() == 0 and full.update(*hyper, 1) == 0
+        torch.cuda.synchronize()
+        want_g = np.empty_like(params)
+        full.get_grads(want_g)
+        want_p = np.empty_like(params)
+        full.get_params(want_p)
+        eg = np.abs(grads - want_g).max() / np.abs(want_g).max()
+        ep = np.abs(after - want_p).max()
+        ok = bool(eg <= 1e-5 and ep <= 1e-5 and step.exchange.calls == n_layer + 1)
+        out["err"] = (float(eg), float(ep), step.exchange.calls)
+    # every rank holds the same averaged gradients
+    t = torch.from_numpy(grads).cuda()
+    ref = t.clone()
+    dist.broadcast(ref, 0)
+    ok = ok and bool(torch.equal(t, ref))
+    out[rank] = ok
+    dist.destroy_process_group()
+
+
+def test_two_gpu_step_equals_one_gpu_step_on_the_whole_batch(gpu):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(2, 29600 + os.getpid() % 1000, out), nprocs=2, join=True)
+    assert out.get(0) and out.get(1), dict(out)
