@@ -60,7 +60,9 @@ def _worker(rank, world, port, out):
         full.get_params(want_p)
         eg = np.abs(grads - want_g).max() / np.abs(want_g).max()
         ep = np.abs(after - want_p).max()
-        ok = bool(eg <= 1e-5 and ep <= 1e-5 and step.exchange.calls == n_layer + 1)
+        # AdamW's first step moves every weight by about lr * sign(g): where g is within rounding of zero
+        # the two runs may disagree on the sign, so the parameters are only required to agree within 2 * lr
+        ok = bool(eg <= 1e-5 and ep <= 2 * hyper[0] and step.exchange.calls == n_layer + 1)
         out["err"] = (float(eg), float(ep), step.exchange.calls)
     # every rank holds the same averaged gradients
     t = torch.from_numpy(grads).cuda()
