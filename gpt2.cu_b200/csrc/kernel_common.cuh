@@ -28,6 +28,8 @@ static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
 struct Tile {
   int m_tile, n_tile, split;
   int kb0, kb1;
+  int bh, bb;  // inner / outer batch index (batched GEMMs)
+  int skip;    // nothing to compute: above the causal diagonal, or an empty reduction range
 };
 
 // Advances `cursor` to the op that owns global tile `t` and decodes the tile.
@@ -40,10 +42,33 @@ __device__ __forceinline__ const GemmOp *decode_tile(const GemmOp *ops, int n_op
                                                      Tile &tc) {
   while (cursor + 1 < n_ops && t >= ops[cursor].tile_base + ops[cursor].n_tiles) ++cursor;
   const GemmOp *op = ops + cursor;
-  decode_local(t - op->tile_base, op->tiles_dec, op->tiles_n, op->band_m, tc.m_tile, tc.n_tile, tc.split);
+  int local = t - op->tile_base;
+  tc.bh = 0;
+  tc.bb = 0;
+  if (op->batch > 1) {
+    const int bi = local / op->tiles_per_batch;
+    local -= bi * op->tiles_per_batch;
+    tc.bh = bi % op->batch_inner;
+    tc.bb = bi / op->batch_inner;
+  }
+  decode_local(local, op->tiles_dec, op->tiles_n, op->band_m, tc.m_tile, tc.n_tile, tc.split);
   tc.kb0 = tc.split * op->kb_per_split;
   int kb1 = tc.kb0 + op->kb_per_split;
   tc.kb1 = kb1 < op->kb_total ? kb1 : op->kb_total;
+  tc.skip = 0;
+  if (op->causal) {
+    const int m0 = tc.m_tile * BM;
+    if (op->causal == 1) {
+      tc.skip = (tc.n_tile * op->bn >= m0 + BM) ? 1 : 0;
+    } else if (op->causal == 2) {
+      const int lim = (m0 + BM + BK - 1) / BK;
+      if (tc.kb1 > lim) tc.kb1 = lim;
+    } else {
+      const int lo = m0 / BK;
+      if (tc.kb0 < lo) tc.kb0 = lo;
+    }
+    if (tc.kb0 >= tc.kb1) tc.skip = 1;
+  }
   return op;
 }
 

@@ -22,4 +22,11 @@ int attention_backward(float *dqkv, float *delta, const float *dout, const float
 int adamw_update(float *p, float *m, float *v, const float *g, long long n, float lr, float b1, float b2, float eps,
                  float wd, int t, cudaStream_t s);
 
+// attention on the tensor cores (attention_gemm.cu); needs T % 32 == 0 and head size 64
+bool attention_gemm_supported(int T, int C, int NH);
+int attention_forward_gemm(float *out, float *P, const float *qkv, int B, int T, int C, int NH, int mode,
+                           cudaStream_t s);
+int attention_backward_gemm(float *dqkv, float *dP, const float *dout, const float *P, const float *qkv, int B, int T,
+                            int C, int NH, int mode, cudaStream_t s);
+
 }  // namespace g2l

@@ -80,6 +80,15 @@ struct alignas(64) GemmOp {
   int tiles_m, tiles_n, splits, kb_total, kb_per_split;
   int band_m;           // rasterisation: tile rows per band (see decode_local)
   int pair;             // 1: tiles are 256 rows, computed by a CTA pair (cta_group::2)
+  // batched GEMMs (attention): `batch` independent products whose operands sit batch_inner (heads)
+  // x batch / batch_inner (sequences) apart; the tensor maps carry two extra dimensions for them
+  int batch;            // 0 or 1 = plain GEMM
+  int batch_inner;
+  int tiles_per_batch;
+  long long c_bs_outer, c_bs_inner;  // C offset per outer / inner batch index, in floats
+  // causal structure of attention: 1 skip output tiles entirely above the diagonal; 2 the reduction
+  // ends with the tile's last row (A is lower-triangular); 3 it starts at the tile's first row
+  int causal;
   int tiles_dec;        // tile rows in scheduling units: tiles_m, or ceil(tiles_m / 2) for pairs
   int tile_base;        // global index of this op's first tile
   int n_tiles;          // tiles_m * tiles_n * splits
@@ -105,6 +114,21 @@ struct LaunchParams {
   long long wait_limit_ns;
   int xform_active;  // 0: no op needs the transform warps (TF32 mode, no fused bias gradient)
 };
+
+// Host-side description of a batched, strided GEMM C_b[Mc][Nc] = A_b . B_b (no bias, no split).
+// a_mn / b_mn as in GemmOp; ld* are row pitches in floats of the arrays as stored ([rows][inner]);
+// *_bs_outer / *_bs_inner are the offsets in floats between outer / inner batch entries.
+struct BatchedDesc {
+  int Mc, Nc, Kc, a_mn, b_mn;
+  const float *a, *b;
+  float *c;
+  long long lda, ldb, ldc;
+  int batch_outer, batch_inner;
+  long long a_bs_outer, a_bs_inner, b_bs_outer, b_bs_inner, c_bs_outer, c_bs_inner;
+  int causal;
+  int mode;
+};
+int build_batched_op(const BatchedDesc &d, int num_sms, GemmOp *op);
 
 // host-side description used to build a GemmOp
 struct GemmDesc {

@@ -98,6 +98,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      if (tc.skip) continue;  // every role skips the same tiles, so no barrier phase is consumed
       // ---- dependency counters: do not touch the operands before their producers are done
       bool waited = false;
 #pragma unroll
@@ -133,6 +134,13 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
           const uint32_t b_dst = a_dst + A_TILE_BYTES;
           mbar_arrive_expect_tx(bar, tx_bytes);
           const int k0 = kb * BK;
+          if (op->batch > 1) {
+            // batched operands: two trailing coordinates select the head and the sequence
+            if (!a_mn) tma_load_4d(a_dst, &op->tmA, bar, k0, m0, tc.bh, tc.bb);
+            else tma_load_5d(a_dst, &op->tmA, bar, 0, k0, m0 >> 5, tc.bh, tc.bb);
+            if (!b_mn) tma_load_4d(b_dst, &op->tmB, bar, k0, n0, tc.bh, tc.bb);
+            else tma_load_5d(b_dst, &op->tmB, bar, 0, k0, n0 >> 5, tc.bh, tc.bb);
+          } else {
           if (!a_mn) {
             tma_load_2d(a_dst, &op->tmA, bar, k0, m0);
           } else if (op->a_3d) {
@@ -147,6 +155,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             tma_load_3d(b_dst, &op->tmB, bar, 0, k0, n0 >> 5);
           } else {
             for (int c = 0; c < bn / 32; ++c) tma_load_2d(b_dst + c * 4096, &op->tmB, bar, n0 + c * 32, k0);
+          }
           }
         }
         __syncwarp();
@@ -170,6 +179,10 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       Tile tc_next = tc;
       const GemmOp *op_next = op;
       if (have_next) op_next = decode_tile(ops, n_ops, t_next, cursor, tc_next);
+      if (tc.skip) {
+        t = t_next; tc = tc_next; op = op_next; have = have_next;
+        continue;
+      }
 
       const uint32_t as = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
@@ -243,6 +256,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      if (tc.skip) continue;
       const int bn = op->bn;
       const bool do_colsum = (op->colsum != nullptr) && tc.m_tile == 0 && op->b_mn;
       // column-sum mapping: `groups` float4 column groups, `parts` threads share a group and
@@ -334,11 +348,13 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     int cursor = 0;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++tcount) {
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      if (tc.skip) continue;
       const uint32_t as = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
+      ++tcount;
       int okl = 1;
       if (lane == 0)
         okl = wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128);
@@ -387,7 +403,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
             }
-            store_chunk(v, sbuf, pass == 0 ? op->C : op->C2, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0);
+            float *cbase = (pass == 0 ? op->C : op->C2) + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
+            store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0);
           }
         }
       } else
@@ -669,6 +686,89 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   e = encode_map(&op->tmC, op->C, (uint64_t)op->Nc, (uint64_t)op->Mc, 32, 32, false);
   if (e) return e;
   if (op->C2) e = encode_map(&op->tmC2, op->C2, (uint64_t)op->Nc, (uint64_t)op->Mc, 32, 32, false);
+  return e;
+}
+
+// K-major batched operand: [outer][inner][rows][red] -> dims {red, rows, inner batches, outer batches}
+static int encode_map_batched_k(CUtensorMap *map, const float *base, uint64_t red, uint64_t rows, uint64_t ld,
+                                uint64_t nb_inner, uint64_t bs_inner, uint64_t nb_outer, uint64_t bs_outer,
+                                uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return GPT2L_ERR_CUDA;
+  cuuint64_t dims[4] = {red, rows, nb_inner, nb_outer};
+  cuuint64_t strides[3] = {ld * 4, (bs_inner ? bs_inner : rows * ld) * 4, (bs_outer ? bs_outer : rows * ld) * 4};
+  cuuint32_t box[4] = {32, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+// MN-major batched operand stored [red rows][mn] (mn a multiple of 32), viewed in 32-column chunks:
+// dims {32, red rows, mn / 32, inner batches, outer batches}
+static int encode_map_batched_mn(CUtensorMap *map, const float *base, uint64_t mn, uint64_t red_rows, uint64_t ld,
+                                 uint64_t nb_inner, uint64_t bs_inner, uint64_t nb_outer, uint64_t bs_outer,
+                                 uint32_t chunks) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return GPT2L_ERR_CUDA;
+  cuuint64_t dims[5] = {32, red_rows, mn / 32, nb_inner, nb_outer};
+  cuuint64_t strides[4] = {ld * 4, 128, (bs_inner ? bs_inner : red_rows * ld) * 4,
+                           (bs_outer ? bs_outer : red_rows * ld) * 4};
+  cuuint32_t box[5] = {32, 32, chunks, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+int build_batched_op(const BatchedDesc &d, int num_sms, GemmOp *op) {
+  (void)num_sms;
+  memset(op, 0, sizeof(*op));
+  if (d.Mc <= 0 || d.Nc <= 0 || d.Kc <= 0 || !d.a || !d.b || !d.c || d.batch_outer <= 0 || d.batch_inner <= 0)
+    return GPT2L_ERR_BAD_ARG;
+  if ((d.lda & 3) || (d.ldb & 3) || (d.ldc & 3) || !aligned16(d.a) || !aligned16(d.b) || !aligned16(d.c))
+    return GPT2L_ERR_BAD_ARG;
+  if ((d.a_mn && (d.Mc & 31)) || (d.b_mn && (d.Nc & 31))) return GPT2L_ERR_BAD_ARG;
+  op->Mc = d.Mc; op->Nc = d.Nc; op->Kc = d.Kc;
+  op->a_mn = d.a_mn; op->b_mn = d.b_mn;
+  op->C = d.c;
+  op->ldc = d.ldc;
+  op->mode = d.mode;
+  op->kb_total = ceil_div(d.Kc, BK);
+  op->bn = d.Nc <= 64 ? 64 : (d.Nc <= 128 ? 128 : 256);
+  op->splits = 1;
+  op->kb_per_split = op->kb_total;
+  op->tiles_m = ceil_div(d.Mc, BM);
+  op->tiles_n = ceil_div(d.Nc, op->bn);
+  op->tiles_dec = op->tiles_m;
+  op->band_m = op->tiles_m;
+  op->batch = d.batch_outer * d.batch_inner;
+  op->batch_inner = d.batch_inner;
+  op->tiles_per_batch = op->tiles_m * op->tiles_n;
+  op->n_tiles = op->batch * op->tiles_per_batch;
+  op->c_bs_outer = d.c_bs_outer;
+  op->c_bs_inner = d.c_bs_inner;
+  op->causal = d.causal;
+  op->idesc = make_idesc_tf32(BM, op->bn, op->a_mn, op->b_mn);
+  for (int w = 0; w < MAX_WAITS; ++w) op->wait_ctr[w] = -1;
+  op->pub_rb_base = -1;
+  op->pub_op_ctr = -1;
+  if (op->batch < 2) op->batch = 2;  // the batched load path is keyed on batch > 1
+  int e;
+  if (!d.a_mn)
+    e = encode_map_batched_k(&op->tmA, d.a, d.Kc, d.Mc, d.lda, d.batch_inner, d.a_bs_inner, d.batch_outer,
+                             d.a_bs_outer, BM);
+  else
+    e = encode_map_batched_mn(&op->tmA, d.a, d.Mc, d.Kc, d.lda, d.batch_inner, d.a_bs_inner, d.batch_outer,
+                              d.a_bs_outer, BM / 32);
+  if (e) return e;
+  if (!d.b_mn)
+    e = encode_map_batched_k(&op->tmB, d.b, d.Kc, d.Nc, d.ldb, d.batch_inner, d.b_bs_inner, d.batch_outer,
+                             d.b_bs_outer, op->bn);
+  else
+    e = encode_map_batched_mn(&op->tmB, d.b, d.Nc, d.Kc, d.ldb, d.batch_inner, d.b_bs_inner, d.batch_outer,
+                              d.b_bs_outer, op->bn / 32);
   return e;
 }
 

@@ -3,6 +3,7 @@
 // vnnm404/gpt2.cu (same parameter order and tensor layouts, new kernels).
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -21,6 +22,7 @@ struct LayerParams {  // offsets into the flat parameter / gradient buffers
 
 struct LayerActs {  // device pointers into the activation buffer
   float *ln1, *ln1_mean, *ln1_rstd, *qkv, *atty, *lse, *res2, *ln2, *ln2_mean, *ln2_rstd, *fc, *fc_gelu, *res3;
+  float *att;  // [B][NH][T][T] attention probabilities (tensor-core attention only)
 };
 
 }  // namespace
@@ -41,6 +43,8 @@ struct gpt2_model {
   float *dresid = nullptr;   // [M][C]   gradient of the residual stream
   float *dbig = nullptr;     // [M][4C]  gradient scratch (d_fc, d_qkv)
   float *delta = nullptr;    // [B][NH][T]
+  float *datt = nullptr;     // [B][NH][T][T] gradient scratch (tensor-core attention only)
+  bool attn_gemm = false;    // attention as batched GEMMs on the tensor cores
   std::vector<LayerActs> la;
   const int *tokens = nullptr;  // of the last forward
   float *h_losses = nullptr;    // pinned
@@ -102,10 +106,17 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
   const int NH = cfg->n_head;
   long long a = 0;
   auto act = [&](long long n) { long long o = a; a += (n + 3) / 4 * 4; return o; };
-  std::vector<long long> o_layer(L * 13);
+  // attention on the tensor cores needs T % 32 == 0; GPT2_ATTENTION=simt forces the CUDA-core kernels
+  m->attn_gemm = attention_gemm_supported(T, C, NH);
+  if (const char *env = getenv("GPT2_ATTENTION")) {
+    if (!strcmp(env, "simt")) m->attn_gemm = false;
+  }
+  const long long att_floats = m->attn_gemm ? (long long)B * NH * T * T : 0;
+  std::vector<long long> o_layer(L * 14);
   const long long o_encoded = act(M * C);
   for (int l = 0; l < L; ++l) {
-    long long *o = &o_layer[l * 13];
+    long long *o = &o_layer[l * 14];
+    o[13] = act(att_floats);
     o[0] = act(M * C); o[1] = act(M); o[2] = act(M);          // ln1, mean, rstd
     o[3] = act(M * 3 * C);                                    // qkv
     o[4] = act(M * C);                                        // atty
@@ -119,6 +130,7 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
   const long long o_logits = act(M * Vp), o_losses = act(M);
   const long long o_tmp = act(M * C), o_dres = act(M * C), o_dbig = act(M * 4 * C);
   const long long o_delta = act((long long)B * NH * T);
+  const long long o_datt = act(att_floats);
   m->acts_floats = a;
 
   bool ok = true;
@@ -144,15 +156,16 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
   m->encoded = A + o_encoded;
   m->la.resize(L);
   for (int l = 0; l < L; ++l) {
-    const long long *o = &o_layer[l * 13];
+    const long long *o = &o_layer[l * 14];
     LayerActs &x = m->la[l];
+    x.att = A + o[13];
     x.ln1 = A + o[0]; x.ln1_mean = A + o[1]; x.ln1_rstd = A + o[2]; x.qkv = A + o[3]; x.atty = A + o[4];
     x.lse = A + o[5]; x.res2 = A + o[6]; x.ln2 = A + o[7]; x.ln2_mean = A + o[8]; x.ln2_rstd = A + o[9];
     x.fc = A + o[10]; x.fc_gelu = A + o[11]; x.res3 = A + o[12];
   }
   m->lnf = A + o_lnf; m->lnf_mean = A + o_lnf_mean; m->lnf_rstd = A + o_lnf_rstd;
   m->logits = A + o_logits; m->losses = A + o_losses;
-  m->tmp_c = A + o_tmp; m->dresid = A + o_dres; m->dbig = A + o_dbig; m->delta = A + o_delta;
+  m->tmp_c = A + o_tmp; m->dresid = A + o_dres; m->dbig = A + o_dbig; m->delta = A + o_delta; m->datt = A + o_datt;
   *err = GPT2L_OK;
   return m;
 }
@@ -213,7 +226,8 @@ int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt
     LayerActs &a = m->la[l];
     CK(layernorm_forward(a.ln1, a.ln1_mean, a.ln1_rstd, res, P + p.ln1_w, P + p.ln1_b, M, C, st));
     CK(gpt2_linear_forward(a.qkv, a.ln1, P + p.qkv_w, P + p.qkv_b, B, T, C, 3 * C, &o, stream));
-    CK(attention_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st));
+    if (m->attn_gemm) CK(attention_forward_gemm(a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
+    else CK(attention_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st));
     CK(gpt2_linear_forward(m->tmp_c, a.atty, P + p.proj_w, P + p.proj_b, B, T, C, C, &o, stream));
     CK(add_forward(a.res2, res, m->tmp_c, (long long)M * C, st));
     CK(layernorm_forward(a.ln2, a.ln2_mean, a.ln2_rstd, a.res2, P + p.ln2_w, P + p.ln2_b, M, C, st));
@@ -273,7 +287,8 @@ int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream) {
   // attention: res2 = res_in + proj(attention(qkv(ln1(res_in))))
   CK(gpt2_linear_backward_input(m->tmp_c, m->dresid, P + p.proj_w, B, T, C, C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.proj_w, G + p.proj_b, m->dresid, a.atty, B, T, C, C, &o, stream));
-  CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
+  if (m->attn_gemm) CK(attention_backward_gemm(m->dbig, m->datt, m->tmp_c, a.att, a.qkv, B, T, C, NH, m->mode, st));
+  else CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
   CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.qkv_w, B, T, C, 3 * C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.qkv_w, G + p.qkv_b, m->dbig, a.ln1, B, T, C, 3 * C, &o, stream));
   CK(layernorm_backward(m->dresid, G + p.ln1_w, G + p.ln1_b, m->tmp_c, res_in, P + p.ln1_w, a.ln1_mean, a.ln1_rstd,

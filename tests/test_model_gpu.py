@@ -96,3 +96,35 @@ def test_gpt2_small_tf32_mode_tracks_the_curve(gpu):
     losses = train(m, tok, tgt, steps, z["hyper"])
     assert np.abs(losses - z["losses"]).max() <= 2e-2, losses - z["losses"]
     m.close()
+
+
+def test_tensor_core_attention_matches_cuda_core_attention(gpu, monkeypatch):
+    """T = 256 (two 128-row blocks per head: skipped tiles, clipped reductions) and T = 160 (ragged
+    blocks): the batched-GEMM attention and the flash-style CUDA-core attention give the same loss
+    and the same gradients."""
+    for T in (256, 160):
+        n_layer, n_head, n_embd, vocab, block, B = 2, 2, 128, 96, 256, 2
+        params = gpt2_ref.to_flat(gpt2_ref.init_params(vocab, block, n_layer, n_head, n_embd), n_layer, vocab)
+        rng = np.random.default_rng(T)
+        tok = torch.from_numpy(rng.integers(0, vocab, B * T).astype(np.int32)).cuda()
+        tgt = torch.from_numpy(rng.integers(0, vocab, B * T).astype(np.int32)).cuda()
+        res = {}
+        for kind in ("gemm", "simt"):
+            monkeypatch.setenv("GPT2_ATTENTION", kind)
+            m = gpu.Model(vocab, vocab, n_layer, n_head, n_embd, block, B, T, mode=1)
+            m.set_params(params)
+            assert m.forward(tok, tgt) == 0
+            loss = m.mean_loss()
+            assert m.backward() == 0
+            torch.cuda.synchronize()
+            st, rec = gpu.last_status()
+            assert st == 0, rec
+            g = np.empty_like(params)
+            m.get_grads(g)
+            res[kind] = (loss, g)
+            m.close()
+        monkeypatch.delenv("GPT2_ATTENTION")
+        assert abs(res["gemm"][0] - res["simt"][0]) <= 1e-5, T
+        a, b = res["gemm"][1], res["simt"][1]
+        assert np.isfinite(a).all()
+        assert np.abs(a - b).max() / np.abs(b).max() <= 1e-4, (T, np.abs(a - b).max() / np.abs(b).max())
