@@ -67,9 +67,11 @@ layernorm_forward_kernel(float *out, float *mean, float *rstd, const float *in, 
   if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
 }
 
-// g_in[row] += layernorm backward of g_out[row]; g_w / g_b accumulate over rows. Each block handles
-// `rows_per_block` rows, keeps per-column partial sums in registers (thread = column slot) and adds
-// them to g_w / g_b once at the end.
+// g_in[row] += layernorm backward of g_out[row]; g_w / g_b accumulate over rows. A warp owns a row at a
+// time and lane l always owns columns l, l+32, ...: the column sums for g_w / g_b stay in registers
+// across the rows of the block and are combined once (shared memory, then one atomicAdd per column
+// per block).
+template <int PER_LANE>  // columns per lane: C <= 32 * PER_LANE
 __global__ void __launch_bounds__(256)
 layernorm_backward_kernel(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
                           const float *mean, const float *rstd, int M, int C, int rows_per_block) {
@@ -78,28 +80,48 @@ layernorm_backward_kernel(float *g_in, float *g_w, float *g_b, const float *g_ou
   for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) sm[c] = 0.f;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  float aw[PER_LANE], ab[PER_LANE], wr[PER_LANE];
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    aw[k] = 0.f; ab[k] = 0.f;
+    const int c = lane + 32 * k;
+    wr[k] = c < C ? w[c] : 0.f;
+  }
   const int r0 = blockIdx.x * rows_per_block;
   const int r1 = min(M, r0 + rows_per_block);
   for (int row = r0 + warp; row < r1; row += nwarps) {
     const float *x = in + (long long)row * C;
     const float *go = g_out + (long long)row * C;
     const float mu = mean[row], rs = rstd[row];
+    float nh[PER_LANE], g[PER_LANE];
     float s1 = 0.f, s2 = 0.f;
-    for (int c = lane; c < C; c += 32) {
-      const float nh = (x[c] - mu) * rs;
-      const float dn = go[c] * w[c];
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+      const int c = lane + 32 * k;
+      const bool in_row = c < C;
+      nh[k] = in_row ? (x[c] - mu) * rs : 0.f;
+      g[k] = in_row ? go[c] : 0.f;
+      const float dn = g[k] * wr[k];
       s1 += dn;
-      s2 += dn * nh;
+      s2 += dn * nh[k];
     }
     s1 = warp_sum(s1) / C;
     s2 = warp_sum(s2) / C;
     float *gi = g_in + (long long)row * C;
-    for (int c = lane; c < C; c += 32) {
-      const float nh = (x[c] - mu) * rs;
-      const float dn = go[c] * w[c];
-      gi[c] += (dn - s1 - nh * s2) * rs;
-      atomicAdd(sw + c, go[c] * nh);
-      atomicAdd(sb + c, go[c]);
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+      const int c = lane + 32 * k;
+      if (c < C) gi[c] += (g[k] * wr[k] - s1 - nh[k] * s2) * rs;
+      aw[k] += g[k] * nh[k];
+      ab[k] += g[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < PER_LANE; ++k) {
+    const int c = lane + 32 * k;
+    if (c < C) {
+      atomicAdd(sw + c, aw[k]);
+      atomicAdd(sb + c, ab[k]);
     }
   }
   __syncthreads();
@@ -147,8 +169,51 @@ __global__ void gelu_backward_kernel(float *g, const float *pre, long long n) {
 // logits row is overwritten with dlogits = (p - onehot) * scale (pad columns V..Vp-1 get 0).
 // (reference: softmax.cu, cross_entropy.cu:24-93; scale = 1 / (B*T).)
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 softmax_xent_kernel(float *logits, float *losses, const int *targets, int V, int Vp, float scale) {
+  // the row (V floats, 196 KiB for GPT-2) is read from HBM once and kept in shared memory
+  extern __shared__ float srow[];
+  __shared__ float red[32];
+  float *row = logits + (long long)blockIdx.x * Vp;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  float mx = -INFINITY;
+  const int V4 = V & ~3;
+  for (int c = tid * 4; c < V4; c += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4 *>(row + c);
+    *reinterpret_cast<float4 *>(srow + c) = v;
+    mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+  }
+  for (int c = V4 + tid; c < V; c += blockDim.x) { const float v = row[c]; srow[c] = v; mx = fmaxf(mx, v); }
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int i = 1; i < nw; ++i) mx = fmaxf(mx, red[i]);
+  __syncthreads();
+  float s = 0.f;
+  for (int c = tid; c < V; c += blockDim.x) { const float e = __expf(srow[c] - mx); srow[c] = e; s += e; }
+  s = warp_sum(s);
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  s = 0.f;
+  for (int i = 0; i < nw; ++i) s += red[i];
+  const int tgt = targets[blockIdx.x];
+  const float inv = 1.f / s;
+  if (tid == 0) losses[blockIdx.x] = -logf(srow[tgt] * inv);
+  const float k = inv * scale;
+  for (int c = tid * 4; c < Vp; c += blockDim.x * 4) {  // Vp is a multiple of 4
+    float4 g;
+    g.x = c + 0 < V ? srow[c + 0] * k - (c + 0 == tgt ? scale : 0.f) : 0.f;
+    g.y = c + 1 < V ? srow[c + 1] * k - (c + 1 == tgt ? scale : 0.f) : 0.f;
+    g.z = c + 2 < V ? srow[c + 2] * k - (c + 2 == tgt ? scale : 0.f) : 0.f;
+    g.w = c + 3 < V ? srow[c + 3] * k - (c + 3 == tgt ? scale : 0.f) : 0.f;
+    *reinterpret_cast<float4 *>(row + c) = g;
+  }
+}
+
+// the same in three passes over global memory, for vocabularies that do not fit in shared memory
+__global__ void __launch_bounds__(512)
+softmax_xent_large_kernel(float *logits, float *losses, const int *targets, int V, int Vp, float scale) {
   __shared__ float red[32];
   float *row = logits + (long long)blockIdx.x * Vp;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -475,9 +540,13 @@ int layernorm_forward(float *out, float *mean, float *rstd, const float *in, con
 }
 int layernorm_backward(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
                        const float *mean, const float *rstd, int M, int C, cudaStream_t s) {
-  const int rows_per_block = 64;
-  layernorm_backward_kernel<<<cdiv(M, rows_per_block), 256, 2 * C * sizeof(float), s>>>(
-      g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
+  const int rows_per_block = 32;
+  const int blocks = cdiv(M, rows_per_block);
+  const size_t smem = 2 * C * sizeof(float);
+  if (C <= 32 * 4) layernorm_backward_kernel<4><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
+  else if (C <= 32 * 24) layernorm_backward_kernel<24><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
+  else if (C <= 32 * 40) layernorm_backward_kernel<40><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
+  else return GPT2L_ERR_TOO_LARGE;
   return LAUNCH_OK();
 }
 int add_forward(float *out, const float *a, const float *b, long long n, cudaStream_t s) {
@@ -489,7 +558,16 @@ int gelu_backward(float *g, const float *pre, long long n, cudaStream_t s) {
   return LAUNCH_OK();
 }
 int softmax_xent(float *logits, float *losses, const int *targets, int M, int V, int Vp, cudaStream_t s) {
-  softmax_xent_kernel<<<M, 512, 0, s>>>(logits, losses, targets, V, Vp, 1.f / (float)M);
+  const size_t row_bytes = (size_t)V * sizeof(float);
+  if (row_bytes <= 220 * 1024) {
+    // per device and cheap: set every time rather than tracking which devices have seen it
+    if (cudaFuncSetAttribute(softmax_xent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) !=
+        cudaSuccess)
+      return GPT2L_ERR_CUDA;
+    softmax_xent_kernel<<<M, 1024, row_bytes, s>>>(logits, losses, targets, V, Vp, 1.f / (float)M);
+  } else {
+    softmax_xent_large_kernel<<<M, 512, 0, s>>>(logits, losses, targets, V, Vp, 1.f / (float)M);
+  }
   return LAUNCH_OK();
 }
 int attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t s) {
