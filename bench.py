@@ -259,6 +259,19 @@ def run_ours(args):
     g = ge.load_package()
     g.init(local_rank)
     dp = ge._load_module("gpt2cu_b200_dp", os.path.join(ROOT, "gpt2.cu_b200", "dp.py"))
+    if args.only_train:
+        def barrier0():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+        mode0 = g.MODE_TF32X3 if args.mode == "tf32x3" else g.MODE_TF32
+        train = measure_train(g, dp, torch, local_rank, rank, world, barrier0, dist if world > 1 else None, mode0,
+                              steps=args.steps, warmup=args.warmup)
+        if rank == 0:
+            print(json.dumps({"partial": True, "train": train}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     exch = dp.GradientExchange()
     mode = g.MODE_TF32X3 if args.mode == "tf32x3" else g.MODE_TF32
     opts = g.make_opts(mode=mode)
@@ -408,8 +421,8 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over the
-# 15 launches of one step, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# 15 launches of one step, from the ncu capture summarised under profiles/.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 483.4e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
 
 
 def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=16, T=1024, steps=5, warmup=2):
@@ -455,7 +468,7 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
     out = {"tokens_per_s": B * T * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps,
            "config": f"GPT-2 small (12 layers, 768 wide, vocabulary 50257 padded to 50304), B={B} per GPU, T={T}, "
                      f"AdamW lr 3e-4 betas 0.9/0.95 wd 0.1, fp32 master weights, {'3xTF32' if mode else 'TF32'} GEMMs, "
-                     "flash-style CUDA-core attention", "loss_after": loss,
+                     "attention as batched causal GEMMs on the same tensor-core kernel", "loss_after": loss,
            "gradient_exchange": "none (1 GPU)" if world == 1 else "NCCL average, one bucket per block, overlapped"}
     model.close()
     return out
@@ -517,6 +530,8 @@ def main():
     ap.add_argument("--only", default="", help="comma list like lm_head.fwd,qkv.wgrad (profiling aid)")
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true", help="kernel-only run (profiling aid)")
     ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the whole-training-step leg")
+    ap.add_argument("--only-train", dest="only_train", action="store_true",
+                    help="run only the whole-training-step leg (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
