@@ -75,6 +75,108 @@ class GradientExchange:
         self.pending = []
 
 
+def shard_bounds(lo, hi, world):
+    """Splits floats [lo, hi) among `world` ranks: rank r owns [lo + r*per, lo + (r+1)*per); the
+    remainder [body_end, hi) (fewer than `world` floats) is kept replicated. Returns (per, body_end)."""
+    per = (hi - lo) // world
+    return per, lo + per * world
+
+
+class ShardedExchange:
+    """Optimizer-state sharding over the flat buffers (ZeRO stage 1 style): gradients are
+    reduce-scattered instead of all-reduced, every rank runs AdamW on its own slice of each bucket
+    only, and the updated parameter slices are all-gathered. Bytes on the links are the same as an
+    all-reduce; the update touches 1/world of the parameters per rank.
+
+    reduce(lo, hi) is called right after the kernels producing grads[lo:hi] were enqueued; it runs on
+    a side stream (GPU) like GradientExchange. owned() lists the (first, count) ranges this rank must
+    update once finish() has been called; gather() then rebuilds the full parameters everywhere.
+    The reference updates the whole buffer on its one GPU (gpt2_update, src/train.cu:450-481)."""
+
+    def __init__(self, grads, params, group=None):
+        self.grads, self.params, self.group = grads, params, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.comm_stream = None
+        self.pending = []
+        self.ranges = []
+        self.calls = 0
+
+    def _mine(self, lo, per):
+        return lo + self.rank * per, lo + (self.rank + 1) * per
+
+    def reduce(self, lo, hi):
+        self.ranges.append((lo, hi))
+        if self.world == 1:
+            return
+        self.calls += 1
+        per, body_end = shard_bounds(lo, hi, self.world)
+        a, b = self._mine(lo, per)
+
+        def issue():
+            if per:
+                if self.grads.is_cuda:
+                    dist.reduce_scatter_tensor(self.grads[a:b], self.grads[lo:body_end], op=dist.ReduceOp.AVG,
+                                               group=self.group)
+                else:  # gloo has no AVG
+                    dist.reduce_scatter_tensor(self.grads[a:b], self.grads[lo:body_end], op=dist.ReduceOp.SUM,
+                                               group=self.group)
+                    self.grads[a:b].div_(self.world)
+            if body_end < hi:
+                if self.grads.is_cuda:
+                    dist.all_reduce(self.grads[body_end:hi], op=dist.ReduceOp.AVG, group=self.group)
+                else:
+                    dist.all_reduce(self.grads[body_end:hi], op=dist.ReduceOp.SUM, group=self.group)
+                    self.grads[body_end:hi].div_(self.world)
+
+        if self.grads.is_cuda:
+            if self.comm_stream is None:
+                self.comm_stream = torch.cuda.Stream()
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ready)
+                issue()
+                done = torch.cuda.Event()
+                done.record()
+            self.pending.append(done)
+        else:
+            issue()
+
+    def finish(self):
+        for ev in self.pending:
+            torch.cuda.current_stream().wait_event(ev)
+        self.pending = []
+
+    def owned(self):
+        """(first, count) ranges whose gradients are final on this rank: its slice of every bucket
+        plus the replicated remainders."""
+        out = []
+        for lo, hi in self.ranges:
+            if self.world == 1:
+                out.append((lo, hi - lo))
+                continue
+            per, body_end = shard_bounds(lo, hi, self.world)
+            a, b = self._mine(lo, per)
+            if per:
+                out.append((a, per))
+            if body_end < hi:
+                out.append((body_end, hi - body_end))
+        return out
+
+    def gather(self):
+        """After the update of owned(): every rank receives the other ranks' parameter slices."""
+        if self.world > 1:
+            for lo, hi in self.ranges:
+                per, body_end = shard_bounds(lo, hi, self.world)
+                if not per:
+                    continue
+                a, b = self._mine(lo, per)
+                src = self.params[a:b] if self.params.is_cuda else self.params[a:b].clone()
+                dist.all_gather_into_tensor(self.params[lo:body_end], src, group=self.group)
+        self.ranges = []
+
+
 class _DeviceView:
     """Exposes a raw device pointer of `count` fp32 values through __cuda_array_interface__."""
 
@@ -96,11 +198,18 @@ class DataParallelStep:
     last block, then one bucket per block going down, then wte + wpe after the embedding backward —
     each on the side stream while the next block's backward runs on the compute stream (the
     backward_weight GEMMs of block l-1 hide the exchange of block l). AdamW runs replicated after the
-    last bucket has landed. With one rank the exchange is a no-op."""
+    last bucket has landed. With one rank the exchange is a no-op.
 
-    def __init__(self, model, device, group=None):
+    shard_optimizer=True swaps the all-reduce for ShardedExchange: reduce-scatter per bucket, AdamW on
+    this rank's slices only (gpt2_model_update_range), all-gather of the parameters."""
+
+    def __init__(self, model, device, group=None, shard_optimizer=False):
         self.model = model
         self.exchange = GradientExchange(group)
+        self.sharded = None
+        if shard_optimizer:
+            self.sharded = ShardedExchange(device_tensor(model.grads_ptr(), model.num_params, device),
+                                           device_tensor(model.params_ptr(), model.num_params, device), group)
         self.L = model.cfg.n_layer
         offs = model.offsets() + [model.num_params]
         self.flat = device_tensor(model.grads_ptr(), model.num_params, device)
@@ -114,6 +223,8 @@ class DataParallelStep:
 
     def __call__(self, tokens, targets, lr, beta1, beta2, eps, weight_decay, t, stream=None):
         m = self.model
+        if self.sharded is not None:
+            return self._sharded_step(tokens, targets, lr, beta1, beta2, eps, weight_decay, t, stream)
         rc = m.forward(tokens, targets, stream)
         rc |= m.backward_head(stream)
         for l in range(self.L - 1, -1, -1):
@@ -126,4 +237,21 @@ class DataParallelStep:
         self.exchange.exchange([self._slice(self.embed)])
         self.exchange.finish()
         rc |= m.update(lr, beta1, beta2, eps, weight_decay, t, stream)
+        return rc
+
+    def _sharded_step(self, tokens, targets, lr, beta1, beta2, eps, weight_decay, t, stream):
+        m, sx = self.model, self.sharded
+        rc = m.forward(tokens, targets, stream)
+        rc |= m.backward_head(stream)
+        for l in range(self.L - 1, -1, -1):
+            rc |= m.backward_layer(l, stream)
+            sx.reduce(*self.block[l])
+            if l == self.L - 1:
+                sx.reduce(*self.lnf)
+        rc |= m.backward_embedding(stream)
+        sx.reduce(*self.embed)
+        sx.finish()
+        for first, count in sx.owned():
+            rc |= m.update_range(first, count, lr, beta1, beta2, eps, weight_decay, t, stream)
+        sx.gather()
         return rc

@@ -62,3 +62,60 @@ def test_single_process_is_a_noop():
     ex.exchange([t])
     ex.finish()
     assert ex.calls == 0 and torch.equal(t, torch.ones(4))
+
+
+def test_shard_bounds():
+    dp = _dp()
+    assert dp.shard_bounds(10, 10 + 17, 4) == (4, 26)
+    assert dp.shard_bounds(0, 3, 8) == (0, 0)   # smaller than the world: wholly replicated
+    assert dp.shard_bounds(5, 5 + 16, 2) == (8, 21)
+
+
+def _sharded_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dp = _dp()
+    n = 1000
+    ranges = [(601, 1000), (600, 601), (37, 600), (0, 37)]  # odd sizes, one smaller than the world, reverse order
+    params0 = torch.randn(n, generator=torch.Generator().manual_seed(7))
+    grads_of = lambda r: torch.randn(n, generator=torch.Generator().manual_seed(50 + r))
+    params, grads = params0.clone(), grads_of(rank)
+    sx = dp.ShardedExchange(grads, params)
+    for lo, hi in ranges:
+        sx.reduce(lo, hi)
+    sx.finish()
+    owned = sx.owned()
+    touched = torch.zeros(n, dtype=torch.bool)
+    for first, count in owned:          # stand-in for gpt2_model_update_range: plain SGD on the owned floats only
+        params[first:first + count] -= 0.1 * grads[first:first + count]
+        touched[first:first + count] = True
+    sx.gather()
+    mean = sum(grads_of(r) for r in range(world)) / world
+    ok = torch.allclose(params, params0 - 0.1 * mean, atol=1e-6)
+    # this rank updated its share only: about 1/world of the floats plus the small remainders
+    ok = ok and int(touched.sum()) <= n // world + world * len(ranges)
+    ok = ok and sx.calls == len(ranges) and sx.ranges == []
+    out[rank] = bool(ok)
+    dist.destroy_process_group()
+
+
+def test_sharded_optimizer_exchange_world_size_2_gloo():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_sharded_worker, args=(world, port, out), nprocs=world, join=True)
+    assert dict(out) == {0: True, 1: True}
+
+
+def test_sharded_exchange_single_process_owns_everything():
+    dp = _dp()
+    g, p = torch.ones(10), torch.zeros(10)
+    sx = dp.ShardedExchange(g, p)
+    sx.reduce(4, 10)
+    sx.reduce(0, 4)
+    sx.finish()
+    assert sx.owned() == [(4, 6), (0, 4)]
+    sx.gather()
+    assert sx.ranges == []

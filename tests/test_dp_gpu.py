@@ -13,7 +13,7 @@ from conftest import ROOT, golden
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, shard):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch.distributed as dist
@@ -39,7 +39,7 @@ def _worker(rank, world, port, out):
     m.set_params(params)
     tok = torch.from_numpy(tokens[rank * per:(rank + 1) * per].reshape(-1).copy()).cuda()
     tgt = torch.from_numpy(targets[rank * per:(rank + 1) * per].reshape(-1).copy()).cuda()
-    step = dp.DataParallelStep(m, torch.device("cuda", rank))
+    step = dp.DataParallelStep(m, torch.device("cuda", rank), shard_optimizer=shard)
     assert step(tok, tgt, *hyper, 1) == 0
     torch.cuda.synchronize()
     grads = np.empty_like(params)
@@ -62,10 +62,20 @@ def _worker(rank, world, port, out):
         ep = np.abs(after - want_p).max()
         # AdamW's first step moves every weight by about lr * sign(g): where g is within rounding of zero
         # the two runs may disagree on the sign, so the parameters are only required to agree within 2 * lr
-        ok = bool(eg <= 1e-5 and ep <= 2 * hyper[0] and step.exchange.calls == n_layer + 1)
-        out["err"] = (float(eg), float(ep), step.exchange.calls)
-    # every rank holds the same averaged gradients
-    t = torch.from_numpy(grads).cuda()
+        calls = step.sharded.calls if shard else step.exchange.calls
+        if shard:
+            # only this rank's slices hold averaged gradients: compare those
+            mask = np.zeros(params.size, bool)
+            sx = dp.ShardedExchange(torch.zeros(1), torch.zeros(1))
+            sx.world, sx.rank = world, rank
+            sx.ranges = [step.block[l] for l in range(n_layer)] + [step.lnf, step.embed]
+            for first, count in sx.owned():
+                mask[first:first + count] = True
+            eg = np.abs(grads - want_g)[mask].max() / np.abs(want_g).max()
+        ok = bool(eg <= 1e-5 and ep <= 2 * hyper[0] and calls == n_layer + (2 if shard else 1))
+        out["err"] = (float(eg), float(ep), calls)
+    # every rank holds the same parameters (and, with the all-reduce, the same averaged gradients)
+    t = torch.from_numpy(after if shard else grads).cuda()
     ref = t.clone()
     dist.broadcast(ref, 0)
     ok = ok and bool(torch.equal(t, ref))
@@ -73,12 +83,13 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_gpu_step_equals_one_gpu_step_on_the_whole_batch(gpu):
+@pytest.mark.parametrize("shard", [False, True])  # all-reduce + replicated AdamW / reduce-scatter + sharded AdamW
+def test_two_gpu_step_equals_one_gpu_step_on_the_whole_batch(gpu, shard):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(2, 29600 + os.getpid() % 1000, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29600 + os.getpid() % 1000 + int(shard), out, shard), nprocs=2, join=True)
     assert out.get(0) and out.get(1), dict(out)
