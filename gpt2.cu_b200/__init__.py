@@ -27,6 +27,7 @@ DEV_TIMEOUT = 1
 MODE_TF32 = 0
 MODE_TF32X3 = 1
 EPI_GELU_DUAL = 1
+AUX_NONE, AUX_ADD, AUX_GELU_GRAD = 0, 1, 2
 
 OP_FORWARD = 0
 OP_BACKWARD_INPUT = 1
@@ -53,7 +54,8 @@ MODEL_EXPORTS = [
     "gpt2_model_param_offsets", "gpt2_model_set_params", "gpt2_model_get_params", "gpt2_model_get_grads",
     "gpt2_model_forward", "gpt2_model_backward", "gpt2_model_update", "gpt2_model_mean_loss",
     "gpt2_model_backward_head", "gpt2_model_backward_layer", "gpt2_model_backward_embedding",
-    "gpt2_model_device_bytes",
+    "gpt2_model_device_bytes", "gpt2_model_update_range", "gpt2_model_load_weights", "gpt2_model_dump_weights",
+    "gpt2_model_save_checkpoint", "gpt2_model_load_checkpoint",
 ]
 
 
@@ -67,6 +69,8 @@ class Opts(ctypes.Structure):
         ("out2", ctypes.c_void_p),
         ("force_simt", ctypes.c_int),
         ("cta_pair", ctypes.c_int),
+        ("aux", ctypes.c_void_p),
+        ("aux_op", ctypes.c_int),
     ]
 
 
@@ -183,6 +187,15 @@ def _load():
     lib.gpt2_model_update.restype = I
     lib.gpt2_model_mean_loss.argtypes = [V, V]
     lib.gpt2_model_mean_loss.restype = F
+    lib.gpt2_model_update_range.argtypes = [V, LL, LL, F, F, F, F, F, I, V]
+    lib.gpt2_model_update_range.restype = I
+    for name in ("gpt2_model_load_weights", "gpt2_model_dump_weights"):
+        getattr(lib, name).argtypes = [V, ctypes.c_char_p]
+        getattr(lib, name).restype = I
+    lib.gpt2_model_save_checkpoint.argtypes = [V, ctypes.c_char_p, I]
+    lib.gpt2_model_save_checkpoint.restype = I
+    lib.gpt2_model_load_checkpoint.argtypes = [V, ctypes.c_char_p, ctypes.POINTER(I)]
+    lib.gpt2_model_load_checkpoint.restype = I
     return lib
 
 
@@ -199,8 +212,9 @@ def init(device=0):
     check("gpt2_linear_init", lib.gpt2_linear_init(device))
 
 
-def make_opts(mode=MODE_TF32, flags=0, split_k=0, deterministic=0, out2=None, force_simt=0, cta_pair=0):
-    return Opts(mode, flags, split_k, deterministic, out2, force_simt, cta_pair)
+def make_opts(mode=MODE_TF32, flags=0, split_k=0, deterministic=0, out2=None, force_simt=0, cta_pair=0, aux=None,
+              aux_op=0):
+    return Opts(mode, flags, split_k, deterministic, out2, force_simt, cta_pair, aux, aux_op)
 
 
 def _p(t):
@@ -351,8 +365,26 @@ class Model:
     def update(self, lr, beta1, beta2, eps, weight_decay, t, stream=None):
         return lib.gpt2_model_update(self.handle, lr, beta1, beta2, eps, weight_decay, t, stream)
 
+    def update_range(self, first, count, lr, beta1, beta2, eps, weight_decay, t, stream=None):
+        return lib.gpt2_model_update_range(self.handle, first, count, lr, beta1, beta2, eps, weight_decay, t, stream)
+
     def mean_loss(self, stream=None):
         return lib.gpt2_model_mean_loss(self.handle, stream)
+
+    def load_weights(self, path):
+        check("gpt2_model_load_weights", lib.gpt2_model_load_weights(self.handle, os.fsencode(path)))
+
+    def dump_weights(self, path):
+        check("gpt2_model_dump_weights", lib.gpt2_model_dump_weights(self.handle, os.fsencode(path)))
+
+    def save_checkpoint(self, path, step):
+        check("gpt2_model_save_checkpoint", lib.gpt2_model_save_checkpoint(self.handle, os.fsencode(path), step))
+
+    def load_checkpoint(self, path):
+        step = ctypes.c_int(-1)
+        check("gpt2_model_load_checkpoint",
+              lib.gpt2_model_load_checkpoint(self.handle, os.fsencode(path), ctypes.byref(step)))
+        return step.value
 
     def device_bytes(self):
         return lib.gpt2_model_device_bytes(self.handle)

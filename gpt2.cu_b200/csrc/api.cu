@@ -55,7 +55,7 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   if (d.opts.mode != GPT2L_MODE_TF32 && d.opts.mode != GPT2L_MODE_TF32X3) return GPT2L_ERR_BAD_ARG;
   if ((long long)d.M * d.N >= (1ll << 40) || (long long)d.M * d.K >= (1ll << 40)) return GPT2L_ERR_TOO_LARGE;
   if (d.opts.force_simt || !tma_eligible(d)) {
-    if (d.opts.flags & GPT2L_EPI_GELU_DUAL) return GPT2L_ERR_BAD_ARG;
+    if ((d.opts.flags & GPT2L_EPI_GELU_DUAL) || d.opts.aux_op) return GPT2L_ERR_BAD_ARG;
     return launch_simt(d, st);
   }
   // bias gradient: fused into the kernel (column sums of the staged g_out blocks) unless a

@@ -3,8 +3,9 @@
 //   forward    S_bh = Q K^T         (tiles above the diagonal are skipped)
 //              P    = softmax(S / 8) row-wise, causal, in place (P is kept for the backward pass)
 //              O_bh = P V           (reduction stops at the tile's last row: P is lower-triangular)
-//   backward   dP   = dO V^T        (tiles above the diagonal skipped)
-//              dS   = P o (dP - rowsum(P o dP)) / 8, in place of dP
+//   backward   delta = rowsum(dO o O)   ( = rowsum(P o dP) )
+//              dS   = P o (dO V^T - delta) / 8     (one GEMM; the softmax gradient is its epilogue;
+//                                                   tiles above the diagonal skipped)
 //              dQ   = dS K          (reduction stops at the diagonal)
 //              dK   = dS^T Q,  dV = P^T dO    (reduction starts at the diagonal)
 //
@@ -43,22 +44,20 @@ attn_softmax_kernel(float *S, int T, long long rows, float scale) {
   for (int j = i + 1 + lane; j < end; j += 32) row[j] = 0.f;
 }
 
-// dS[i][j] = P[i][j] * (dP[i][j] - sum_k P[i][k] dP[i][k]) * scale for j <= i, written over dP; zeros
-// up to the end of the 128-column block.
+// delta[b][h][i] = sum_d dO[b,i,h,d] * O[b,i,h,d]  ( = sum_j P[i][j] dP[i][j], without touching the
+// T x T tensors): one warp per (b, i, h), two of the 64 head values per lane.
 __global__ void __launch_bounds__(256)
-attn_dsoftmax_kernel(float *dP, const float *P, int T, long long rows, float scale) {
-  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+attn_delta_kernel(float *delta, const float *dout, const float *out, int T, int C, int NH, long long rows) {
+  const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // (b*T + i)*NH + h
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
-  const int i = (int)(r % T);
-  float *g = dP + r * T;
-  const float *p = P + r * T;
-  float dot = 0.f;
-  for (int j = lane; j <= i; j += 32) dot += p[j] * g[j];
-  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-  for (int j = lane; j <= i; j += 32) g[j] = p[j] * (g[j] - dot) * scale;
-  const int end = min(T, (i | 127) + 1);
-  for (int j = i + 1 + lane; j < end; j += 32) g[j] = 0.f;
+  const int h = (int)(r % NH);
+  const long long bt = r / NH;
+  const float2 a = *reinterpret_cast<const float2 *>(dout + bt * C + h * AHS + 2 * lane);
+  const float2 b = *reinterpret_cast<const float2 *>(out + bt * C + h * AHS + 2 * lane);
+  float s = a.x * b.x + a.y * b.y;
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) delta[((bt / T) * NH + h) * T + bt % T] = s;
 }
 
 static int run(DeviceCtx *ctx, const BatchedDesc &d, cudaStream_t st) {
@@ -103,9 +102,11 @@ int attention_forward_gemm(float *out, float *P, const float *qkv, int B, int T,
   return run(ctx, d, st);
 }
 
-// dqkv[B*T][3C] from dout[B*T][C]; dP is scratch of the size of P
-int attention_backward_gemm(float *dqkv, float *dP, const float *dout, const float *P, const float *qkv, int B, int T,
-                            int C, int NH, int mode, cudaStream_t st) {
+// dqkv[B*T][3C] from dout[B*T][C]; dP is scratch of the size of P, delta scratch of [B][NH][T]; out is
+// the forward result (the softmax gradient's row term comes from dout . out, so that dS is formed in
+// the epilogue of the dP GEMM and never needs a pass of its own)
+int attention_backward_gemm(float *dqkv, float *dP, float *delta, const float *dout, const float *out, const float *P,
+                            const float *qkv, int B, int T, int C, int NH, int mode, cudaStream_t st) {
   int err;
   DeviceCtx *ctx = ctx_current(&err);
   if (!ctx) return err;
@@ -114,7 +115,12 @@ int attention_backward_gemm(float *dqkv, float *dP, const float *dout, const flo
   const long long qs = (long long)T * 3 * C, os = (long long)T * C;
   BatchedDesc d;
   d.batch_outer = B; d.batch_inner = NH; d.mode = mode;
-  // dP = dO V^T
+  const long long rows = (long long)B * NH * T;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(delta, dout, out, T, C, NH, rows);
+  count_launch();
+  if (cudaGetLastError() != cudaSuccess) return GPT2L_ERR_CUDA;
+  // dS = P o (dO V^T - delta) / 8   (P is zero past the diagonal inside the diagonal tiles, so dS is too)
+  d.aux = P; d.aux_row = delta; d.aux_scale = 0.125f; d.aux_op = AUX_SOFTMAX_GRAD;
   d.Mc = T; d.Nc = T; d.Kc = AHS; d.a_mn = 0; d.b_mn = 0;
   d.a = dout; d.b = qkv + 2 * C; d.c = dP;
   d.lda = C; d.ldb = 3 * C; d.ldc = T;
@@ -122,10 +128,7 @@ int attention_backward_gemm(float *dqkv, float *dP, const float *dout, const flo
   d.c_bs_outer = NH * TT; d.c_bs_inner = TT;
   d.causal = 1;
   if ((err = run(ctx, d, st))) return err;
-  const long long rows = (long long)B * NH * T;
-  attn_dsoftmax_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(dP, P, T, rows, 0.125f);
-  count_launch();
-  if (cudaGetLastError() != cudaSuccess) return GPT2L_ERR_CUDA;
+  d.aux = nullptr; d.aux_row = nullptr; d.aux_op = 0;
   // dQ = dS K   (K stored [T][64], its rows are the reduction index)
   d.Mc = T; d.Nc = AHS; d.Kc = T; d.a_mn = 0; d.b_mn = 1;
   d.a = dP; d.b = qkv + C; d.c = dqkv;

@@ -136,10 +136,21 @@ __device__ __forceinline__ bool wait_counter(const unsigned *ctr, unsigned expec
   }
 }
 
+// tanh(u) = 1 - 2 / (1 + e^{2u}) on the special-function unit (ex2.approx, rcp.approx): absolute error
+// about 2e-7, which is what GELU needs (it uses 1 + tanh and 1 - tanh^2, never tanh alone); tanhf
+// costs several times as many instructions, and the epilogue warps evaluate 32K of these per tile.
+__device__ __forceinline__ float tanh_sfu(float u) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * u)); }
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k = 0.7978845608028654f;  // sqrt(2/pi)
   float u = k * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  return 0.5f * x * (1.0f + tanh_sfu(u));
+}
+
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float th = tanh_sfu(k * (x + 0.044715f * x * x * x));
+  return 0.5f * (1.f + th) + x * 0.5f * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * x * x);
 }
 
 __device__ __forceinline__ float tf32_round(float x) {
@@ -156,23 +167,78 @@ __device__ __forceinline__ float tf32_round(float x) {
 // shared memory and comes back as "instruction = 4 rows x 128 bytes", so that every global store (or
 // split-K reduction) instruction covers four whole lines. Only the warp's own lanes are involved:
 // __syncwarp is the only synchronisation, and no asynchronous-proxy fence is needed.
+// The epilogue operand `e.aux` (same indexing as C) is read in the coalesced phase, so it costs one
+// more fully coalesced 16-byte load per lane: GPT2L_AUX_ADD adds it, GPT2L_AUX_GELU_GRAD multiplies by
+// gelu'(aux), AUX_SOFTMAX_GRAD computes aux * (acc - e.row[r]) * e.scale.
+struct EpiAux {
+  const float *aux = nullptr;
+  const float *row = nullptr;  // one value per output row (AUX_SOFTMAX_GRAD)
+  float scale = 1.f;
+  int op = 0;
+};
+
+// The operand values a chunk needs, fetched ahead of the accumulator read so that their latency
+// overlaps it (issued inside the store loop they would serialise behind each store).
+struct AuxRegs {
+  float4 a[8];
+  float drow = 0.f;  // AUX_SOFTMAX_GRAD: lane l holds the row term of row l of the warp's 32 rows
+};
+
+__device__ __forceinline__ void load_aux(AuxRegs &r, const EpiAux &e, long long ldc, int row0, int nb, int Mc, int Nc,
+                                         int lane) {
+  if (!e.op) return;
+  const int rr = lane >> 3, cc = lane & 7;
+  const int col = nb + cc * 4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int grow = row0 + 4 * i + rr;
+    r.a[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (grow < Mc && col < Nc) r.a[i] = __ldg(reinterpret_cast<const float4 *>(e.aux + (long long)grow * ldc + col));
+  }
+}
+
 __device__ __forceinline__ void store_chunk(const float (&v)[32], uint32_t sbuf, float *C, long long ldc,
-                                            int row0, int nb, int Mc, int Nc, int lane, bool atomic) {
+                                            int row0, int nb, int Mc, int Nc, int lane, bool atomic,
+                                            const EpiAux &e, const AuxRegs &r) {
+  __syncwarp();  // the previous chunk's reads of this box are done
 #pragma unroll
   for (int j = 0; j < 8; ++j)
     st_shared_v4(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
   __syncwarp();
   const int rr = lane >> 3, cc = lane & 7;
   const int col = nb + cc * 4;
+  float4 x[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int rl = 4 * i + rr;
-    const float4 x = ld_shared_v4(sbuf + rl * 128 + ((cc ^ (rl & 7)) << 4));
-    const int grow = row0 + rl;
+    x[i] = ld_shared_v4(sbuf + rl * 128 + ((cc ^ (rl & 7)) << 4));
+  }
+  if (e.op == GPT2L_AUX_ADD) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x[i].x += r.a[i].x; x[i].y += r.a[i].y; x[i].z += r.a[i].z; x[i].w += r.a[i].w;
+    }
+  } else if (e.op == GPT2L_AUX_GELU_GRAD) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x[i].x *= gelu_tanh_grad(r.a[i].x); x[i].y *= gelu_tanh_grad(r.a[i].y);
+      x[i].z *= gelu_tanh_grad(r.a[i].z); x[i].w *= gelu_tanh_grad(r.a[i].w);
+    }
+  } else if (e.op != 0) {  // AUX_SOFTMAX_GRAD
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float d = __shfl_sync(0xffffffffu, r.drow, 4 * i + rr);
+      x[i].x = r.a[i].x * (x[i].x - d) * e.scale; x[i].y = r.a[i].y * (x[i].y - d) * e.scale;
+      x[i].z = r.a[i].z * (x[i].z - d) * e.scale; x[i].w = r.a[i].w * (x[i].w - d) * e.scale;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int grow = row0 + 4 * i + rr;
     if (grow < Mc && col < Nc) {
       float *dst = C + (long long)grow * ldc + col;
-      if (atomic) red_add_v4(dst, x.x, x.y, x.z, x.w);
-      else *reinterpret_cast<float4 *>(dst) = x;
+      if (atomic) red_add_v4(dst, x[i].x, x[i].y, x[i].z, x[i].w);
+      else *reinterpret_cast<float4 *>(dst) = x[i];
     }
   }
 }

@@ -71,8 +71,8 @@ layernorm_forward_kernel(float *out, float *mean, float *rstd, const float *in, 
 // time and lane l always owns columns l, l+32, ...: the column sums for g_w / g_b stay in registers
 // across the rows of the block and are combined once (shared memory, then one atomicAdd per column
 // per block).
-template <int PER_LANE>  // columns per lane: C <= 32 * PER_LANE
-__global__ void __launch_bounds__(256)
+template <int K4>  // float4 columns per lane: C <= 128 * K4 (C is a multiple of 4)
+__global__ void __launch_bounds__(256, (K4 <= 6 ? 2 : 1))
 layernorm_backward_kernel(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
                           const float *mean, const float *rstd, int M, int C, int rows_per_block) {
   extern __shared__ float sm[];  // [2][C] column sums of this block
@@ -80,12 +80,11 @@ layernorm_backward_kernel(float *g_in, float *g_w, float *g_b, const float *g_ou
   for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) sm[c] = 0.f;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  float aw[PER_LANE], ab[PER_LANE], wr[PER_LANE];
+  float4 aw[K4], ab[K4];
 #pragma unroll
-  for (int k = 0; k < PER_LANE; ++k) {
-    aw[k] = 0.f; ab[k] = 0.f;
-    const int c = lane + 32 * k;
-    wr[k] = c < C ? w[c] : 0.f;
+  for (int k = 0; k < K4; ++k) {
+    aw[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    ab[k] = aw[k];
   }
   const int r0 = blockIdx.x * rows_per_block;
   const int r1 = min(M, r0 + rows_per_block);
@@ -93,35 +92,45 @@ layernorm_backward_kernel(float *g_in, float *g_w, float *g_b, const float *g_ou
     const float *x = in + (long long)row * C;
     const float *go = g_out + (long long)row * C;
     const float mu = mean[row], rs = rstd[row];
-    float nh[PER_LANE], g[PER_LANE];
+    float4 nh[K4], g[K4];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int k = 0; k < PER_LANE; ++k) {
-      const int c = lane + 32 * k;
-      const bool in_row = c < C;
-      nh[k] = in_row ? (x[c] - mu) * rs : 0.f;
-      g[k] = in_row ? go[c] : 0.f;
-      const float dn = g[k] * wr[k];
-      s1 += dn;
-      s2 += dn * nh[k];
+    for (int k = 0; k < K4; ++k) {
+      const int c = 4 * (lane + 32 * k);
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 xv = c < C ? *reinterpret_cast<const float4 *>(x + c) : make_float4(mu, mu, mu, mu);
+      g[k] = c < C ? *reinterpret_cast<const float4 *>(go + c) : zero;
+      nh[k] = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
+      const float4 wv = c < C ? __ldg(reinterpret_cast<const float4 *>(w + c)) : zero;
+      const float4 dn = make_float4(g[k].x * wv.x, g[k].y * wv.y, g[k].z * wv.z, g[k].w * wv.w);
+      s1 += dn.x + dn.y + dn.z + dn.w;
+      s2 += dn.x * nh[k].x + dn.y * nh[k].y + dn.z * nh[k].z + dn.w * nh[k].w;
     }
     s1 = warp_sum(s1) / C;
     s2 = warp_sum(s2) / C;
     float *gi = g_in + (long long)row * C;
 #pragma unroll
-    for (int k = 0; k < PER_LANE; ++k) {
-      const int c = lane + 32 * k;
-      if (c < C) gi[c] += (g[k] * wr[k] - s1 - nh[k] * s2) * rs;
-      aw[k] += g[k] * nh[k];
-      ab[k] += g[k];
+    for (int k = 0; k < K4; ++k) {
+      const int c = 4 * (lane + 32 * k);
+      if (c < C) {
+        float4 o = *reinterpret_cast<float4 *>(gi + c);
+        const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + c));
+        o.x += (g[k].x * wv.x - s1 - nh[k].x * s2) * rs;
+        o.y += (g[k].y * wv.y - s1 - nh[k].y * s2) * rs;
+        o.z += (g[k].z * wv.z - s1 - nh[k].z * s2) * rs;
+        o.w += (g[k].w * wv.w - s1 - nh[k].w * s2) * rs;
+        *reinterpret_cast<float4 *>(gi + c) = o;
+      }
+      aw[k].x += g[k].x * nh[k].x; aw[k].y += g[k].y * nh[k].y; aw[k].z += g[k].z * nh[k].z; aw[k].w += g[k].w * nh[k].w;
+      ab[k].x += g[k].x; ab[k].y += g[k].y; ab[k].z += g[k].z; ab[k].w += g[k].w;
     }
   }
 #pragma unroll
-  for (int k = 0; k < PER_LANE; ++k) {
-    const int c = lane + 32 * k;
+  for (int k = 0; k < K4; ++k) {
+    const int c = 4 * (lane + 32 * k);
     if (c < C) {
-      atomicAdd(sw + c, aw[k]);
-      atomicAdd(sb + c, ab[k]);
+      atomicAdd(sw + c, aw[k].x); atomicAdd(sw + c + 1, aw[k].y); atomicAdd(sw + c + 2, aw[k].z); atomicAdd(sw + c + 3, aw[k].w);
+      atomicAdd(sb + c, ab[k].x); atomicAdd(sb + c + 1, ab[k].y); atomicAdd(sb + c + 2, ab[k].z); atomicAdd(sb + c + 3, ab[k].w);
     }
   }
   __syncthreads();
@@ -543,10 +552,17 @@ int layernorm_backward(float *g_in, float *g_w, float *g_b, const float *g_out, 
   const int rows_per_block = 32;
   const int blocks = cdiv(M, rows_per_block);
   const size_t smem = 2 * C * sizeof(float);
-  if (C <= 32 * 4) layernorm_backward_kernel<4><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
-  else if (C <= 32 * 24) layernorm_backward_kernel<24><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
-  else if (C <= 32 * 40) layernorm_backward_kernel<40><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block);
+  if (C & 3) return GPT2L_ERR_BAD_ARG;
+#define LN_BWD(K4) layernorm_backward_kernel<K4><<<blocks, 256, smem, s>>>(g_in, g_w, g_b, g_out, in, w, mean, rstd, M, C, rows_per_block)
+  if (C <= 128) LN_BWD(1);
+  else if (C <= 256) LN_BWD(2);
+  else if (C <= 512) LN_BWD(4);
+  else if (C <= 768) LN_BWD(6);
+  else if (C <= 1024) LN_BWD(8);
+  else if (C <= 1280) LN_BWD(10);
+  else if (C <= 2048) LN_BWD(16);
   else return GPT2L_ERR_TOO_LARGE;
+#undef LN_BWD
   return LAUNCH_OK();
 }
 int add_forward(float *out, const float *a, const float *b, long long n, cudaStream_t s) {

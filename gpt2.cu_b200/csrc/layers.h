@@ -26,7 +26,7 @@ int adamw_update(float *p, float *m, float *v, const float *g, long long n, floa
 bool attention_gemm_supported(int T, int C, int NH);
 int attention_forward_gemm(float *out, float *P, const float *qkv, int B, int T, int C, int NH, int mode,
                            cudaStream_t s);
-int attention_backward_gemm(float *dqkv, float *dP, const float *dout, const float *P, const float *qkv, int B, int T,
-                            int C, int NH, int mode, cudaStream_t s);
+int attention_backward_gemm(float *dqkv, float *dP, float *delta, const float *dout, const float *out, const float *P,
+                            const float *qkv, int B, int T, int C, int NH, int mode, cudaStream_t st);
 
 }  // namespace g2l

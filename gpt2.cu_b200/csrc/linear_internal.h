@@ -28,6 +28,9 @@ constexpr int EPI_WARP0 = 6;
 constexpr int XFORM_WARP0 = 2;
 constexpr int NUM_XFORM_WARPS = 4;
 constexpr int NUM_EPI_WARPS = 4;
+// counter arrivals one finished tile produces in the one-CTA kernel: the transform warps double as
+// epilogue warps (and publish) in launches that need no transform
+constexpr int epi_arrivals(bool xform_active) { return xform_active ? NUM_EPI_WARPS : 2 * NUM_EPI_WARPS; }
 constexpr int SMEM_CTRL_BYTES = 512;  // mbarriers + tmem pointer + abort flag
 constexpr int EPI_BUF_BYTES = 32 * 32 * 4;                       // one 32 x 32 fp32 store box
 constexpr int EPI_BYTES = NUM_EPI_WARPS * 2 * EPI_BUF_BYTES;    // two boxes per epilogue warp
@@ -67,6 +70,10 @@ struct alignas(64) GemmOp {
   CUtensorMap tmC2; // second output of the GELU dual store
   float *C;
   float *C2;            // gelu(C) when flags & GPT2L_EPI_GELU_DUAL
+  const float *aux;     // epilogue operand shaped like C (residual to add / pre-activation for GELU')
+  int aux_op;           // GPT2L_AUX_* or AUX_SOFTMAX_GRAD
+  const float *aux_row; // AUX_SOFTMAX_GRAD: one value per (batch, output row), [batch][Mc]
+  float aux_scale;
   const float *bias;    // [Nc] or null
   float *colsum;        // wgrad: g_b[Nc] or null (column sums of B over the reduction)
   float *ws;            // deterministic split-K: partial tiles [n_tiles][BM*bn]
@@ -118,6 +125,9 @@ struct LaunchParams {
 // Host-side description of a batched, strided GEMM C_b[Mc][Nc] = A_b . B_b (no bias, no split).
 // a_mn / b_mn as in GemmOp; ld* are row pitches in floats of the arrays as stored ([rows][inner]);
 // *_bs_outer / *_bs_inner are the offsets in floats between outer / inner batch entries.
+// internal epilogue op of the attention backward: out = aux * (acc - aux_row[row]) * aux_scale
+constexpr int AUX_SOFTMAX_GRAD = 3;
+
 struct BatchedDesc {
   int Mc, Nc, Kc, a_mn, b_mn;
   const float *a, *b;
@@ -127,6 +137,10 @@ struct BatchedDesc {
   long long a_bs_outer, a_bs_inner, b_bs_outer, b_bs_inner, c_bs_outer, c_bs_inner;
   int causal;
   int mode;
+  const float *aux = nullptr;      // epilogue operand shaped and batched like c
+  const float *aux_row = nullptr;  // [batch_outer * batch_inner][Mc]
+  float aux_scale = 1.f;
+  int aux_op = 0;
 };
 int build_batched_op(const BatchedDesc &d, int num_sms, GemmOp *op);
 

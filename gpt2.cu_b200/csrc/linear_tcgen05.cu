@@ -75,7 +75,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[a]), NUM_EPI_WARPS);
+      mbar_init(smem_u32(&ctrl->tmem_empty[a]), NUM_EPI_WARPS * (p.xform_active ? 1 : 2));
     }
     ctrl->abort = 0;
     fence_mbar_init();
@@ -245,10 +245,10 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       have = have_next;
       ++tcount;
     }
-  } else if (warp < EPI_WARP0) {
+  } else if (warp < EPI_WARP0 && p.xform_active) {
     // =============================== operand transform ===============================
-    // (these warps leave at once when no op of the launch needs a split or a column sum)
-    if (p.xform_active) {
+    // (in launches where no op needs a split or a column sum these warps join the epilogue instead)
+    {
     const int x = tid - XFORM_WARP0 * 32;  // 0..127
     int cursor = 0;
     uint32_t it = 0;
@@ -342,9 +342,16 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     }
   } else {
     // =============================== epilogue ===============================
+    // Warps 6-9 always work here. When the transform warps 2-5 have nothing to transform they
+    // help: warp w and warp w + 4 read the same TMEM lane quarter and take alternate 32-column
+    // chunks of every tile, which halves the time a tile spends in the epilogue (what bounds
+    // short reductions such as the attention score GEMMs, and every CTA's last tile).
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const uint32_t epi_base = ring + RING_BYTES + (uint32_t)(warp - EPI_WARP0) * 2u * EPI_BUF_BYTES;
-    uint32_t epi_cc = 0;  // boxes this warp has handed to the copy engine so far
+    const bool helper = warp < EPI_WARP0;
+    const int n_epi = p.xform_active ? 1 : 2;
+    const int c_first = helper ? 1 : 0;
+    const uint32_t sbuf = ring + RING_BYTES +
+                          (uint32_t)(helper ? (warp - XFORM_WARP0) * 2 + 1 : (warp - EPI_WARP0) * 2) * EPI_BUF_BYTES;
     int cursor = 0;
     uint32_t tcount = 0;
     bool ok = true;
@@ -381,9 +388,21 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         // ---- registers -> swizzled 32x32 box in shared memory -> coalesced stores (or vector
         // reductions for split-K partials); see store_chunk
         const int row0 = tc.m_tile * BM + q * 32;
-        for (int c = 0; c < bn / 32; ++c) {
+        EpiAux ea;
+        if (op->aux_op && tc.split == 0) {
+          ea.aux = op->aux + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
+          ea.op = op->aux_op;
+          ea.scale = op->aux_scale;
+          if (op->aux_row) ea.row = op->aux_row + ((long long)tc.bb * op->batch_inner + tc.bh) * Mc;
+        }
+        const EpiAux none;
+        const float drow = (ea.row && row0 + lane < Mc) ? __ldg(ea.row + row0 + lane) : 0.f;
+        for (int c = c_first; c < bn / 32; c += n_epi) {
           const int nb = n0 + c * 32;
           if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
+          AuxRegs ar;
+          ar.drow = drow;
+          load_aux(ar, ea, ldc, row0, nb, Mc, Nc, lane);  // in flight while the accumulator is read
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
@@ -397,17 +416,18 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
             v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
           }
-          for (int pass = 0; pass < (dual ? 2 : 1); ++pass, ++epi_cc) {
-            const uint32_t sbuf = epi_base + (epi_cc & 1u) * EPI_BUF_BYTES;
+          for (int pass = 0; pass < (dual ? 2 : 1); ++pass) {
             if (pass == 1) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
             }
             float *cbase = (pass == 0 ? op->C : op->C2) + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
-            store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0);
+            // the epilogue operand applies to the first output only, and once per element: with
+            // split-K reduce-adds the split that also adds the bias carries it
+            store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, pass == 0 ? ea : none, ar);
           }
         }
-      } else
+      } else if (!helper)  // fixed-order split-K: the quarter's own warp parks whole rows
       for (int c = 0; c < bn / 32; ++c) {
         const int nb = n0 + c * 32;
         if (nb >= Nc) break;  // warp-uniform
@@ -427,7 +447,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[as]));
 
-      if (det_split) {
+      if (det_split && !helper) {
         // Deterministic split-K: every split parks its partial rows in the workspace; the
         // warp that arrives last for this (output tile, lane quarter) adds the partials in
         // split order and writes C. No ordering between splits is ever waited for.
@@ -476,7 +496,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         }
       }
 
-      // ---- publish: everything this warp stored is visible before the counters move
+      // ---- publish: everything this warp stored is visible before the counters move (helpers
+      // publish too, so a tile counts NUM_EPI_WARPS or 2 * NUM_EPI_WARPS arrivals: epi_arrivals())
       if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
         __threadfence();
         __syncwarp();
@@ -530,6 +551,7 @@ bool tma_eligible(const GemmDesc &d) {
   if (!aligned16(d.out) || !aligned16(d.a) || !aligned16(d.b)) return false;
   if (d.bias && !aligned16(d.bias)) return false;
   if (d.opts.out2 && !aligned16(d.opts.out2)) return false;
+  if (d.opts.aux_op && !aligned16(d.opts.aux)) return false;
   return true;
 }
 
@@ -631,9 +653,19 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   op->flags = (d.kind == GPT2L_OP_FORWARD) ? d.opts.flags : 0u;
   op->C2 = (op->flags & GPT2L_EPI_GELU_DUAL) ? d.opts.out2 : nullptr;
   if ((op->flags & GPT2L_EPI_GELU_DUAL) && !op->C2) return GPT2L_ERR_BAD_ARG;
+  // epilogue operand: a product with gelu' cannot be applied to partial sums, and the fixed-order
+  // combine does not carry it, so those cases run unsplit
+  op->aux = d.opts.aux_op ? d.opts.aux : nullptr;
+  op->aux_op = op->aux ? d.opts.aux_op : 0;
+  op->aux_row = nullptr;
+  op->aux_scale = 1.f;
+  if (d.opts.aux_op && !d.opts.aux) return GPT2L_ERR_BAD_ARG;
+  if (d.opts.aux_op < 0 || d.opts.aux_op > GPT2L_AUX_GELU_GRAD) return GPT2L_ERR_BAD_ARG;
+  if (op->aux_op && d.kind == GPT2L_OP_BACKWARD_WEIGHT) return GPT2L_ERR_BAD_ARG;
   op->kb_total = ceil_div(op->Kc, BK);
   int bn, splits;
   int forced = d.opts.split_k;
+  if (op->aux_op == GPT2L_AUX_GELU_GRAD || (op->aux_op && d.opts.deterministic) || (op->aux_op && op->C2)) forced = 1;
   if (forced > op->kb_total) forced = op->kb_total;
   // CTA pairs (256-row tiles, B split between the two CTAs) cut operand traffic per flop by a
   // third, but measured no faster than single CTAs on these shapes (both reach the same ~480 ns
@@ -750,6 +782,11 @@ int build_batched_op(const BatchedDesc &d, int num_sms, GemmOp *op) {
   op->c_bs_outer = d.c_bs_outer;
   op->c_bs_inner = d.c_bs_inner;
   op->causal = d.causal;
+  op->aux = d.aux_op ? d.aux : nullptr;
+  op->aux_op = op->aux ? d.aux_op : 0;
+  op->aux_row = d.aux_row;
+  op->aux_scale = d.aux_scale;
+  if (op->aux_op == AUX_SOFTMAX_GRAD && !op->aux_row) return GPT2L_ERR_BAD_ARG;
   op->idesc = make_idesc_tf32(BM, op->bn, op->a_mn, op->b_mn);
   for (int w = 0; w < MAX_WAITS; ++w) op->wait_ctr[w] = -1;
   op->pub_rb_base = -1;

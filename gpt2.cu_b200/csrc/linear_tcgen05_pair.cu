@@ -425,7 +425,11 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
             }
-            store_chunk(v, sbuf, pass == 0 ? op->C : op->C2, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0);
+            EpiAux ea;
+            if (pass == 0 && op->aux_op && tc.split == 0) { ea.aux = op->aux; ea.op = op->aux_op; }
+            AuxRegs ar;
+            load_aux(ar, ea, ldc, row0, nb, Mc, Nc, lane);
+            store_chunk(v, sbuf, pass == 0 ? op->C : op->C2, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, ea, ar);
           }
         }
       } else if (live) {

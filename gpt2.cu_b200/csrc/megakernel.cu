@@ -3,9 +3,10 @@
 // the schedule by replaying it on the host, and launches the kernel once per run.
 //
 // Counter layout: op i owns tiles_m(i) row-block counters followed by one op-level counter.
-// Each of the four epilogue warps of a tile publishes once to the row-block counter of its
-// tile row and once to the op counter, so a complete row block shows
-// 4 * tiles_n * splits arrivals and a complete op 4 * n_tiles.
+// Each epilogue warp of a tile publishes once to the row-block counter of its tile row and once
+// to the op counter, so with A arrivals per tile (4 epilogue warps; 8 in one-CTA launches whose
+// transform warps help in the epilogue) a complete row block shows A * tiles_n * splits arrivals
+// and a complete op A * n_tiles.
 #include <cuda_runtime.h>
 #include <string.h>
 
@@ -15,8 +16,6 @@
 
 namespace g2l {
 
-constexpr unsigned ARRIVALS_PER_TILE = NUM_EPI_WARPS;
-
 struct Plan {
   std::vector<GemmOp> ops;
   int total_tiles = 0;
@@ -24,6 +23,7 @@ struct Plan {
   bool any_3x = false;
   bool any_colsum = false;
   bool pair = false;  // every op runs on CTA pairs (256-row tiles)
+  int arrivals = NUM_EPI_WARPS;  // counter arrivals per finished 128-row tile (see epi_arrivals)
 };
 
 static GemmDesc desc_from(const gpt2l_op &o) {
@@ -70,6 +70,9 @@ static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
     if (g.mode == GPT2L_MODE_TF32X3) plan->any_3x = true;
     if (g.colsum) plan->any_colsum = true;
   }
+  // the pair kernel always publishes from its four epilogue warps per CTA
+  plan->arrivals = plan->pair ? NUM_EPI_WARPS : epi_arrivals(plan->any_3x || plan->any_colsum);
+  const unsigned ARRIVALS_PER_TILE = (unsigned)plan->arrivals;
   for (int i = 0; i < n_ops; ++i) {
     GemmOp &g = plan->ops[i];
     for (int w = 0; w < GPT2L_MAX_DEPS; ++w) {
@@ -106,6 +109,7 @@ static int replay(const Plan &plan, int grid) {
   for (int c = 0; c < grid; ++c) next[c] = c;
   int remaining = plan.total_tiles;
   std::vector<int> cursor(grid, 0);
+  const int ARRIVALS_PER_TILE = plan.arrivals;
   while (remaining > 0) {
     bool progress = false;
     for (int c = 0; c < grid; ++c) {

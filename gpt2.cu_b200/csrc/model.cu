@@ -3,6 +3,7 @@
 // vnnm404/gpt2.cu (same parameter order and tensor layouts, new kernels).
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -228,15 +229,17 @@ int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt
     CK(gpt2_linear_forward(a.qkv, a.ln1, P + p.qkv_w, P + p.qkv_b, B, T, C, 3 * C, &o, stream));
     if (m->attn_gemm) CK(attention_forward_gemm(a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
     else CK(attention_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st));
-    CK(gpt2_linear_forward(m->tmp_c, a.atty, P + p.proj_w, P + p.proj_b, B, T, C, C, &o, stream));
-    CK(add_forward(a.res2, res, m->tmp_c, (long long)M * C, st));
+    gpt2_linear_opts orr = o;  // both projections add the residual stream in their epilogue
+    orr.aux_op = GPT2L_AUX_ADD;
+    orr.aux = res;
+    CK(gpt2_linear_forward(a.res2, a.atty, P + p.proj_w, P + p.proj_b, B, T, C, C, &orr, stream));
     CK(layernorm_forward(a.ln2, a.ln2_mean, a.ln2_rstd, a.res2, P + p.ln2_w, P + p.ln2_b, M, C, st));
     gpt2_linear_opts og = o;  // fc: the epilogue stores the pre-activation and its GELU in one pass
     og.flags = GPT2L_EPI_GELU_DUAL;
     og.out2 = a.fc_gelu;
     CK(gpt2_linear_forward(a.fc, a.ln2, P + p.fc_w, P + p.fc_b, B, T, C, 4 * C, &og, stream));
-    CK(gpt2_linear_forward(m->tmp_c, a.fc_gelu, P + p.fcproj_w, P + p.fcproj_b, B, T, 4 * C, C, &o, stream));
-    CK(add_forward(a.res3, a.res2, m->tmp_c, (long long)M * C, st));
+    orr.aux = a.res2;
+    CK(gpt2_linear_forward(a.res3, a.fc_gelu, P + p.fcproj_w, P + p.fcproj_b, B, T, 4 * C, C, &orr, stream));
     res = a.res3;
   }
   CK(layernorm_forward(m->lnf, m->lnf_mean, m->lnf_rstd, res, P + m->off_lnf_w, P + m->off_lnf_b, M, C, st));
@@ -277,9 +280,11 @@ int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream) {
   LayerActs &a = m->la[l];
   const float *res_in = l > 0 ? m->la[l - 1].res3 : m->encoded;
   // MLP: res3 = res2 + fcproj(gelu(fc(ln2(res2))))
-  CK(gpt2_linear_backward_input(m->dbig, m->dresid, P + p.fcproj_w, B, T, 4 * C, C, &o, stream));
+  gpt2_linear_opts ogb = o;  // the GELU backward rides in the epilogue: dbig = (dresid . W^T) * gelu'(fc)
+  ogb.aux_op = GPT2L_AUX_GELU_GRAD;
+  ogb.aux = a.fc;
+  CK(gpt2_linear_backward_input(m->dbig, m->dresid, P + p.fcproj_w, B, T, 4 * C, C, &ogb, stream));
   CK(gpt2_linear_backward_weight(G + p.fcproj_w, G + p.fcproj_b, m->dresid, a.fc_gelu, B, T, 4 * C, C, &o, stream));
-  CK(gelu_backward(m->dbig, a.fc, (long long)M * 4 * C, st));
   CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.fc_w, B, T, C, 4 * C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.fc_w, G + p.fc_b, m->dbig, a.ln2, B, T, C, 4 * C, &o, stream));
   CK(layernorm_backward(m->dresid, G + p.ln2_w, G + p.ln2_b, m->tmp_c, a.res2, P + p.ln2_w, a.ln2_mean, a.ln2_rstd,
@@ -287,7 +292,7 @@ int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream) {
   // attention: res2 = res_in + proj(attention(qkv(ln1(res_in))))
   CK(gpt2_linear_backward_input(m->tmp_c, m->dresid, P + p.proj_w, B, T, C, C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.proj_w, G + p.proj_b, m->dresid, a.atty, B, T, C, C, &o, stream));
-  if (m->attn_gemm) CK(attention_backward_gemm(m->dbig, m->datt, m->tmp_c, a.att, a.qkv, B, T, C, NH, m->mode, st));
+  if (m->attn_gemm) CK(attention_backward_gemm(m->dbig, m->datt, m->delta, m->tmp_c, a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
   else CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
   CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.qkv_w, B, T, C, 3 * C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.qkv_w, G + p.qkv_b, m->dbig, a.ln1, B, T, C, 3 * C, &o, stream));
@@ -316,6 +321,14 @@ int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float e
                       static_cast<cudaStream_t>(stream));
 }
 
+int gpt2_model_update_range(gpt2_model *m, long long first, long long count, float lr, float beta1, float beta2,
+                            float eps, float weight_decay, int t, gpt2l_stream_t stream) {
+  if (!m || t < 1 || first < 0 || count < 0 || first + count > m->n_params) return GPT2L_ERR_BAD_ARG;
+  if (count == 0) return GPT2L_OK;
+  return adamw_update(m->params + first, m->m1 + first, m->m2 + first, m->grads + first, count, lr, beta1, beta2, eps,
+                      weight_decay, t, static_cast<cudaStream_t>(stream));
+}
+
 float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream) {
   if (!m) return NAN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -326,6 +339,126 @@ float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream) {
   double s = 0.0;
   for (long long i = 0; i < M; ++i) s += m->h_losses[i];
   return (float)(s / (double)M);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Files. A weight file is the reference's: headerless fp32, tensors in parameter order, wte as
+// [C][V] with the true vocabulary (no pad columns). In memory wte rows are padded_vocab_size long,
+// so the copy goes row by row through a host image of the flat buffer.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+long long file_floats(const gpt2_model *m) {
+  return m->n_params - (long long)m->cfg.n_embd * (m->cfg.padded_vocab_size - m->cfg.vocab_size);
+}
+
+// one flat device buffer -> file section
+int write_section(const gpt2_model *m, const float *dev, FILE *f, std::vector<float> &host) {
+  host.resize((size_t)m->n_params);
+  if (cudaMemcpy(host.data(), dev, host.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  const int C = m->cfg.n_embd, V = m->cfg.vocab_size, Vp = m->cfg.padded_vocab_size;
+  for (int c = 0; c < C; ++c)
+    if (fwrite(host.data() + m->off_wte + (size_t)c * Vp, sizeof(float), (size_t)V, f) != (size_t)V) return GPT2M_ERR_IO;
+  const size_t rest = (size_t)(m->n_params - m->off_wpe);
+  return fwrite(host.data() + m->off_wpe, sizeof(float), rest, f) == rest ? GPT2L_OK : GPT2M_ERR_IO;
+}
+
+// file section -> one flat device buffer (pad columns zero)
+int read_section(const gpt2_model *m, float *dev, FILE *f, std::vector<float> &host) {
+  host.assign((size_t)m->n_params, 0.f);
+  const int C = m->cfg.n_embd, V = m->cfg.vocab_size, Vp = m->cfg.padded_vocab_size;
+  for (int c = 0; c < C; ++c)
+    if (fread(host.data() + m->off_wte + (size_t)c * Vp, sizeof(float), (size_t)V, f) != (size_t)V) return GPT2M_ERR_IO;
+  const size_t rest = (size_t)(m->n_params - m->off_wpe);
+  if (fread(host.data() + m->off_wpe, sizeof(float), rest, f) != rest) return GPT2M_ERR_IO;
+  return cudaMemcpy(dev, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess
+             ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+long long size_of_file(FILE *f) {
+  if (fseek(f, 0, SEEK_END) != 0) return -1;
+  const long long n = ftell(f);
+  rewind(f);
+  return n;
+}
+
+struct CheckpointHeader {  // 64 bytes, little-endian ints
+  char magic[8];           // "G2CKPT1\0"
+  int vocab_size, n_layer, n_head, n_embd, n_positions;
+  int step;                // AdamW steps taken so far: the next update runs with t = step + 1
+  long long floats_per_section;
+  int reserved[6];
+};
+static_assert(sizeof(CheckpointHeader) == 64, "header layout");
+const char kMagic[8] = {'G', '2', 'C', 'K', 'P', 'T', '1', 0};
+
+}  // namespace
+
+extern "C" {
+
+int gpt2_model_load_weights(gpt2_model *m, const char *path) {
+  if (!m || !path) return GPT2L_ERR_BAD_ARG;
+  FILE *f = fopen(path, "rb");
+  if (!f) return GPT2M_ERR_IO;
+  std::vector<float> host;
+  int rc = size_of_file(f) == file_floats(m) * (long long)sizeof(float) ? GPT2L_OK : GPT2M_ERR_FORMAT;
+  if (rc == GPT2L_OK) rc = read_section(m, m->params, f, host);
+  fclose(f);
+  return rc;
+}
+
+int gpt2_model_dump_weights(gpt2_model *m, const char *path) {
+  if (!m || !path) return GPT2L_ERR_BAD_ARG;
+  FILE *f = fopen(path, "wb");
+  if (!f) return GPT2M_ERR_IO;
+  std::vector<float> host;
+  int rc = write_section(m, m->params, f, host);
+  if (fclose(f) != 0 && rc == GPT2L_OK) rc = GPT2M_ERR_IO;
+  return rc;
+}
+
+int gpt2_model_save_checkpoint(gpt2_model *m, const char *path, int step) {
+  if (!m || !path || step < 0) return GPT2L_ERR_BAD_ARG;
+  FILE *f = fopen(path, "wb");
+  if (!f) return GPT2M_ERR_IO;
+  CheckpointHeader h;
+  memset(&h, 0, sizeof(h));
+  memcpy(h.magic, kMagic, 8);
+  h.vocab_size = m->cfg.vocab_size; h.n_layer = m->cfg.n_layer; h.n_head = m->cfg.n_head;
+  h.n_embd = m->cfg.n_embd; h.n_positions = m->cfg.n_positions; h.step = step;
+  h.floats_per_section = file_floats(m);
+  int rc = fwrite(&h, sizeof(h), 1, f) == 1 ? GPT2L_OK : GPT2M_ERR_IO;
+  std::vector<float> host;
+  const float *sections[3] = {m->params, m->m1, m->m2};
+  for (int i = 0; i < 3 && rc == GPT2L_OK; ++i) rc = write_section(m, sections[i], f, host);
+  if (fclose(f) != 0 && rc == GPT2L_OK) rc = GPT2M_ERR_IO;
+  return rc;
+}
+
+int gpt2_model_load_checkpoint(gpt2_model *m, const char *path, int *step) {
+  if (!m || !path) return GPT2L_ERR_BAD_ARG;
+  FILE *f = fopen(path, "rb");
+  if (!f) return GPT2M_ERR_IO;
+  CheckpointHeader h;
+  int rc = GPT2L_OK;
+  const long long bytes = size_of_file(f);
+  if (fread(&h, sizeof(h), 1, f) != 1 || memcmp(h.magic, kMagic, 8) != 0) rc = GPT2M_ERR_FORMAT;
+  if (rc == GPT2L_OK &&
+      (h.vocab_size != m->cfg.vocab_size || h.n_layer != m->cfg.n_layer || h.n_head != m->cfg.n_head ||
+       h.n_embd != m->cfg.n_embd || h.n_positions != m->cfg.n_positions || h.step < 0 ||
+       h.floats_per_section != file_floats(m) ||
+       bytes != (long long)sizeof(h) + 3 * h.floats_per_section * (long long)sizeof(float)))
+    rc = GPT2M_ERR_FORMAT;
+  std::vector<float> host;
+  float *sections[3] = {m->params, m->m1, m->m2};
+  // a file that fails the checks above leaves the model untouched; a read error below does not
+  for (int i = 0; i < 3 && rc == GPT2L_OK; ++i) rc = read_section(m, sections[i], f, host);
+  fclose(f);
+  if (rc == GPT2L_OK && step) *step = h.step;
+  return rc;
 }
 
 }  // extern "C"

@@ -53,6 +53,14 @@ enum gpt2l_mode {
 
 /* epilogue flags */
 #define GPT2L_EPI_GELU_DUAL 1u /* forward only: also store gelu(out) (tanh form) to opts->out2 */
+/* epilogue operand (opts->aux, same shape as the output): what the reference does in separate
+ * kernels right after the GEMM (src/layers/residual.cu:24-31, src/layers/gelu.cu:49-63), folded
+ * into the store. aux must not overlap the output. Forward and backward_input only; the request runs
+ * unsplit where a split could not carry it. GPT2L_ERR_BAD_ARG on the CUDA-core path (shapes or
+ * pointers the tensor-core path cannot take) */
+#define GPT2L_AUX_NONE 0
+#define GPT2L_AUX_ADD 1       /* out = gemm (+ bias) + aux            (residual connection)          */
+#define GPT2L_AUX_GELU_GRAD 2 /* out = gemm * gelu'(aux)              (GELU backward; aux = fc output) */
 
 typedef struct gpt2_linear_opts {
   int mode;          /* enum gpt2l_mode                                                     */
@@ -62,6 +70,8 @@ typedef struct gpt2_linear_opts {
   float *out2;       /* second output for GPT2L_EPI_GELU_DUAL, [B*S][N]                     */
   int force_simt;    /* 1 = run the CUDA-core fallback kernel even where TMA is possible    */
   int cta_pair;      /* 0 = choose; 1 = one CTA per 128-row tile; 2 = CTA pairs, 256-row tiles */
+  const float *aux;  /* epilogue operand, [rows][cols] of the output; NULL = none           */
+  int aux_op;        /* GPT2L_AUX_*                                                         */
 } gpt2_linear_opts;
 
 /* One-time set-up for the current device: checks the architecture, raises the dynamic

@@ -65,11 +65,31 @@ int gpt2_model_backward_embedding(gpt2_model *m, gpt2l_stream_t stream);
 /* AdamW over the flat parameter buffer, step count t >= 1 (gpt2_update, src/train.cu:450-481). */
 int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
                       gpt2l_stream_t stream);
+/* AdamW over floats [first, first + count) of the flat buffers only: for drivers that shard the
+ * optimizer across data-parallel ranks (each rank updates its slice, then the slices are gathered). */
+int gpt2_model_update_range(gpt2_model *m, long long first, long long count, float lr, float beta1, float beta2,
+                            float eps, float weight_decay, int t, gpt2l_stream_t stream);
 /* Synchronises the stream and returns the mean of the per-token losses of the last forward
  * (compute_mean_loss, src/train.cu:36-49). NaN on error. */
 float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream);
 /* Bytes of device memory the model holds. */
 long long gpt2_model_device_bytes(const gpt2_model *m);
+
+/* ---- files (blocking; they synchronise the device) ---- */
+#define GPT2M_ERR_IO (-7)     /* open / read / write failed                                   */
+#define GPT2M_ERR_FORMAT (-8) /* size, magic or configuration does not match this model       */
+/* The reference's weight file (gpt2_load_weights / gpt2_dump_weights, src/gpt2.cu:206-314, written by
+ * scripts/hf_to_bin.py): headerless native-endian fp32, tensors in the parameter order above, wte
+ * stored [n_embd][vocab_size] with the true vocabulary. Loading pads wte rows with zeros; dumping
+ * drops the pad columns, so files interchange with the reference. The size must match exactly. */
+int gpt2_model_load_weights(gpt2_model *m, const char *path);
+int gpt2_model_dump_weights(gpt2_model *m, const char *path);
+/* Training checkpoint: a 64-byte header ("G2CKPT1", the configuration, the number of AdamW steps
+ * taken) followed by three sections in the weight-file layout: parameters, first moments, second
+ * moments. The reference has no counterpart (it can only dump weights, so its AdamW state is lost on
+ * restart). load returns the step count through *step (may be NULL); resume with t = step + 1. */
+int gpt2_model_save_checkpoint(gpt2_model *m, const char *path, int step);
+int gpt2_model_load_checkpoint(gpt2_model *m, const char *path, int *step);
 
 #ifdef __cplusplus
 }

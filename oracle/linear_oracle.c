@@ -201,3 +201,18 @@ void oracle_gelu_f32(float *out, const float *x, long n) {
     out[i] = 0.5f * v * (1.0f + tanhf(k * (v + 0.044715f * v * v * v)));
   }
 }
+
+/* Local gradient of the tanh GELU as the reference's backward kernel computes it
+ * (src/layers/gelu.cu:49-63: 0.5(1+tanh u) + x/2 * sech^2(u) * s * (1 + 3*0.044715 x^2), u = s(x + 0.044715 x^3)),
+ * in double, times the incoming gradient: out[i] = g[i] * gelu'(x[i]). Checks the fused GELU-backward epilogue. */
+void oracle_gelu_grad_mul_f64(double *out, const float *x, const double *g, long n) {
+  const double s = sqrt(2.0 / M_PI);
+  for (long i = 0; i < n; ++i) {
+    const double v = x[i];
+    const double u = s * (v + 0.044715 * v * v * v);
+    const double th = tanh(u);
+    const double ch = cosh(u);
+    const double sech2 = 1.0 / (ch * ch);
+    out[i] = g[i] * (0.5 * (1.0 + th) + v * 0.5 * sech2 * s * (1.0 + 3.0 * 0.044715 * v * v));
+  }
+}

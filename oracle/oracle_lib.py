@@ -38,6 +38,7 @@ def lib():
         L.oracle_linear_backward_weight_f32.argtypes = [F, F, F, F, I, I, I, I]
         L.oracle_linear_backward_weight_f64.argtypes = [D, D, F, F, I, I, I, I]
         L.oracle_gelu_f32.argtypes = [F, F, ctypes.c_long]
+        L.oracle_gelu_grad_mul_f64.argtypes = [D, F, D, ctypes.c_long]
         L.oracle_set_threads.argtypes = [I]
         L.oracle_get_threads.restype = I
         _lib = L
@@ -115,6 +116,15 @@ def gelu(x):
     x = _c(x)
     out = np.empty_like(x)
     lib().oracle_gelu_f32(_f(out), _f(x), x.size)
+    return out
+
+
+def gelu_grad_mul(x, g):
+    """g * gelu'(x) in float64 (the reference's GELU backward without its accumulate)"""
+    x = _c(x)
+    g = np.ascontiguousarray(g, np.float64)
+    out = np.empty(x.shape, np.float64)
+    lib().oracle_gelu_grad_mul_f64(_d(out), _f(x), _d(g), x.size)
     return out
 
 

@@ -173,6 +173,55 @@ def test_gelu_dual_store(gpu, orc, pair):
     assert np.allclose(y2.cpu().numpy(), orc.gelu(pre), atol=2e-6)
 
 
+@pytest.mark.parametrize("pair", [1, 2])
+@pytest.mark.parametrize("M,K,N,split", [(300, 64, 256, 0), (256, 768, 768, 0), (129, 36, 68, 0), (128, 1024, 128, 4)])
+def test_residual_add_in_the_epilogue(gpu, orc, M, K, N, split, pair):
+    """forward with GPT2L_AUX_ADD: out = x.w + b + residual (the reference runs residual_forward after
+    the projection); with an atomic split the residual must be added exactly once"""
+    x, w, b, dy = seeded(M, K, N, seed=21)
+    res = np.random.default_rng(5).standard_normal((M, N), dtype=np.float32)
+    resd = dev(res)
+    y = torch.full((M, N), float("nan"), device="cuda")
+    o = gpu.make_opts(mode=1, aux=resd.data_ptr(), aux_op=gpu.AUX_ADD, split_k=split, cta_pair=pair)
+    gpu.check("forward", gpu.forward(y, dev(x), dev(w), dev(b), 1, M, K, N, o))
+    torch.cuda.synchronize()
+    truth = orc.forward(x, w, b, f64=True) + res.astype(np.float64)
+    assert orc.max_rel_err(y.cpu().numpy(), truth) <= TIGHT[1]
+    assert np.array_equal(resd.cpu().numpy(), res)  # the operand is read-only
+
+
+@pytest.mark.parametrize("pair", [1, 2])
+@pytest.mark.parametrize("M,K,N", [(300, 256, 64), (256, 3072, 768), (130, 516, 260)])
+def test_gelu_backward_in_the_epilogue(gpu, orc, M, K, N, pair):
+    """backward_input with GPT2L_AUX_GELU_GRAD: dx = (dy.w^T) * gelu'(pre), pre shaped like dx (the
+    reference runs gelu_backward on the result); a requested split must be ignored, not misapplied"""
+    x, w, b, dy = seeded(M, K, N, seed=22)
+    pre = (np.random.default_rng(6).standard_normal((M, K)) * 2).astype(np.float32)
+    dx = torch.full((M, K), float("nan"), device="cuda")
+    pred = dev(pre)
+    for split in (0, 3):
+        o = gpu.make_opts(mode=1, aux=pred.data_ptr(), aux_op=gpu.AUX_GELU_GRAD, split_k=split, cta_pair=pair)
+        gpu.check("backward_input", gpu.backward_input(dx, dev(dy), dev(w), 1, M, K, N, o))
+        torch.cuda.synchronize()
+        truth = orc.gelu_grad_mul(pre, orc.backward_input(dy, w, f64=True))
+        assert orc.max_rel_err(dx.cpu().numpy(), truth) <= TIGHT[1]
+
+
+def test_epilogue_operand_argument_checks(gpu):
+    x, w, b, dy = seeded(128, 64, 64, seed=23)
+    y = torch.empty((128, 64), device="cuda")
+    aux = torch.zeros((128, 64), device="cuda")
+    dw = torch.empty((64, 64), device="cuda")
+    bad = gpu.make_opts(mode=1, aux=None, aux_op=gpu.AUX_ADD)
+    assert gpu.forward(y, dev(x), dev(w), dev(b), 1, 128, 64, 64, bad) == gpu.ERR_BAD_ARG
+    bad = gpu.make_opts(mode=1, aux=aux.data_ptr(), aux_op=7)
+    assert gpu.forward(y, dev(x), dev(w), dev(b), 1, 128, 64, 64, bad) == gpu.ERR_BAD_ARG
+    bad = gpu.make_opts(mode=1, aux=aux.data_ptr(), aux_op=gpu.AUX_ADD)
+    assert gpu.backward_weight(dw, None, dev(dy), dev(x), 1, 128, 64, 64, bad) == gpu.ERR_BAD_ARG
+    bad = gpu.make_opts(mode=1, aux=aux.data_ptr(), aux_op=gpu.AUX_ADD, force_simt=1)
+    assert gpu.forward(y, dev(x), dev(w), dev(b), 1, 128, 64, 64, bad) == gpu.ERR_BAD_ARG
+
+
 def test_outputs_are_overwritten_not_accumulated(gpu, orc):
     x, w, b, dy = seeded(256, 64, 128, seed=8)
     # deterministic=1: the default split-K combine uses floating-point atomics, whose order varies

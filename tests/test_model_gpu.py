@@ -128,3 +128,103 @@ def test_tensor_core_attention_matches_cuda_core_attention(gpu, monkeypatch):
         a, b = res["gemm"][1], res["simt"][1]
         assert np.isfinite(a).all()
         assert np.abs(a - b).max() / np.abs(b).max() <= 1e-4, (T, np.abs(a - b).max() / np.abs(b).max())
+
+
+def file_layout(params, m, vocab, padded, n_embd):
+    """The flat (padded) parameter vector as the reference's weight file lays it out: wte [C][V]
+    without pad columns, everything else unchanged (src/gpt2.cu:206-259 of the reference)."""
+    offs = m.offsets()
+    wte = params[offs[0]:offs[1]].reshape(n_embd, padded)[:, :vocab]
+    return np.concatenate([wte.reshape(-1), params[offs[1]:]])
+
+
+def test_weight_file_is_the_reference_layout_and_round_trips(gpu, tmp_path):
+    z = golden("llm_train_tiny.npz")
+    n_layer, n_head, n_embd, vocab, padded, block, B, T, _ = (int(v) for v in z["meta"])
+    m, params, tok, tgt, _ = build(gpu, z, 1)
+    path = str(tmp_path / "weights.bin")
+    m.dump_weights(path)
+    on_disk = np.fromfile(path, np.float32)
+    assert np.array_equal(on_disk, file_layout(params, m, vocab, padded, n_embd))
+    # a file written the way the reference's exporter writes it loads into the padded layout
+    rng = np.random.default_rng(3)
+    other = rng.standard_normal(on_disk.size).astype(np.float32)
+    other.tofile(path)
+    m2 = gpu.Model(vocab, padded, n_layer, n_head, n_embd, block, B, T, mode=1)
+    m2.load_weights(path)
+    got = np.empty_like(params)
+    m2.get_params(got)
+    assert np.array_equal(file_layout(got, m2, vocab, padded, n_embd), other)
+    offs = m2.offsets()
+    assert np.all(got[offs[0]:offs[1]].reshape(n_embd, padded)[:, vocab:] == 0)  # pad columns stay zero
+    # wrong size: rejected, model untouched
+    other[:-1].tofile(path)
+    assert gpu.lib.gpt2_model_load_weights(m2.handle, os.fsencode(path)) == -8
+    assert gpu.lib.gpt2_model_load_weights(m2.handle, os.fsencode(str(tmp_path / "missing.bin"))) == -7
+    again = np.empty_like(params)
+    m2.get_params(again)
+    assert np.array_equal(again, got)
+    m.close()
+    m2.close()
+
+
+def test_checkpoint_resumes_the_same_training_run(gpu, tmp_path):
+    """2 steps, save, 3 more steps == load into a fresh model, 3 more steps (AdamW moments and the
+    step count travel with the parameters)."""
+    z = golden("llm_train_tiny.npz")
+    n_layer, n_head, n_embd, vocab, padded, block, B, T, _ = (int(v) for v in z["meta"])
+    lr, b1, b2, eps, wd = (float(v) for v in z["hyper"])
+    m, params, tok, tgt, _ = build(gpu, z, 1)
+
+    def steps(model, first_t, n):
+        out = []
+        for t in range(first_t, first_t + n):
+            assert model.forward(tok, tgt) == 0
+            out.append(model.mean_loss())
+            assert model.backward() == 0
+            assert model.update(lr, b1, b2, eps, wd, t) == 0
+        return np.array(out)
+
+    steps(m, 1, 2)
+    path = str(tmp_path / "run.ckpt")
+    m.save_checkpoint(path, 2)
+    want = steps(m, 3, 3)
+    m2 = gpu.Model(vocab, padded, n_layer, n_head, n_embd, block, B, T, mode=1)
+    done = m2.load_checkpoint(path)
+    assert done == 2
+    got = steps(m2, done + 1, 3)
+    assert np.abs(got - want).max() <= 1e-5, (got, want)  # split-K atomics: not bitwise
+    # a checkpoint of another configuration is refused
+    m3 = gpu.Model(vocab, padded, n_layer + 1, n_head, n_embd, block, B, T, mode=1)
+    assert gpu.lib.gpt2_model_load_checkpoint(m3.handle, os.fsencode(path), None) == -8
+    for x in (m, m2, m3):
+        x.close()
+
+
+def test_ranged_update_equals_the_whole_update(gpu):
+    """AdamW over [0, n) in three uneven slices == one call over everything (sharded-optimizer drivers)"""
+    z = golden("llm_train_tiny.npz")
+    lr, b1, b2, eps, wd = (float(v) for v in z["hyper"])
+    outs = []
+    for sliced in (False, True):
+        m, params, tok, tgt, _ = build(gpu, z, 1)
+        assert m.forward(tok, tgt) == 0 and m.backward() == 0
+        g = np.empty_like(params)
+        m.get_grads(g)
+        n = m.num_params
+        if sliced:
+            cuts = [0, n // 3 + 1, n // 2 + 3, n]
+            for a, b in zip(cuts[:-1], cuts[1:]):
+                assert m.update_range(a, b - a, lr, b1, b2, eps, wd, 1) == 0
+            assert m.update_range(n, 1, lr, b1, b2, eps, wd, 1) == gpu.ERR_BAD_ARG
+        else:
+            assert m.update(lr, b1, b2, eps, wd, 1) == 0
+        p = np.empty_like(params)
+        m.get_params(p)
+        outs.append((g, p))
+        m.close()
+    # same gradients up to atomic split-K order, then the same update rule
+    assert np.abs(outs[0][0] - outs[1][0]).max() <= 1e-6
+    assert np.abs(outs[0][1] - outs[1][1]).max() <= 2.1 * lr
+    same = np.abs(outs[0][0] - outs[1][0]) == 0
+    assert np.array_equal(outs[0][1][same], outs[1][1][same])

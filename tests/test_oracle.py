@@ -73,3 +73,15 @@ def test_gelu_matches_formula(orc):
     x = np.linspace(-6, 6, 101, dtype=np.float32)
     want = 0.5 * x * (1 + np.tanh(np.sqrt(2 / np.pi) * (x + 0.044715 * x ** 3)))
     assert np.allclose(orc.gelu(x), want, atol=1e-6)
+
+
+def test_gelu_gradient_matches_a_central_difference(orc):
+    """the restated GELU backward (sech^2 form of the reference kernel) against d/dx of the forward"""
+    x = np.linspace(-6, 6, 2001).astype(np.float32)
+    g = np.full(x.shape, 1.5)
+    h = 1e-4
+    xd = x.astype(np.float64)
+    k = np.sqrt(2 / np.pi)
+    f = lambda v: 0.5 * v * (1 + np.tanh(k * (v + 0.044715 * v ** 3)))
+    fd = (f(xd + h) - f(xd - h)) / (2 * h)
+    assert np.allclose(orc.gelu_grad_mul(x, g), 1.5 * fd, atol=1e-7)
