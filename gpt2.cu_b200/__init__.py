@@ -49,6 +49,10 @@ EXPORTS = [
     "gpt2_megakernel_run", "gpt2_megakernel_status", "gpt2_schedule_debug_set_expected",
 ]
 # every symbol include/gpt2_model.h declares
+ATTENTION_EXPORTS = ["gpt2_attention_supported", "gpt2_attention_forward", "gpt2_attention_backward",
+                     "gpt2_attention_status"]
+ATT_FLASH, ATT_GEMM, ATT_SIMT = 0, 1, 2
+
 MODEL_EXPORTS = [
     "gpt2_model_create", "gpt2_model_destroy", "gpt2_model_num_params", "gpt2_model_params", "gpt2_model_grads",
     "gpt2_model_param_offsets", "gpt2_model_set_params", "gpt2_model_get_params", "gpt2_model_get_grads",
@@ -196,6 +200,14 @@ def _load():
     lib.gpt2_model_save_checkpoint.restype = I
     lib.gpt2_model_load_checkpoint.argtypes = [V, ctypes.c_char_p, ctypes.POINTER(I)]
     lib.gpt2_model_load_checkpoint.restype = I
+    # ---- gpt2_attention.h ----
+    lib.gpt2_attention_supported.argtypes = [I, I, I, I]
+    lib.gpt2_attention_supported.restype = I
+    lib.gpt2_attention_forward.argtypes = [P, P, P, P, I, I, I, I, I, I, V]
+    lib.gpt2_attention_forward.restype = I
+    lib.gpt2_attention_backward.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, V]
+    lib.gpt2_attention_backward.restype = I
+    lib.gpt2_attention_status.restype = I
     return lib
 
 
@@ -241,6 +253,18 @@ def backward_input(g_in, g_out, w, B, S, K, N, opts=None, stream=None, host=Fals
 def backward_weight(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=None, host=False):
     fn = lib.gpt2_linear_backward_weight_host if host else lib.gpt2_linear_backward_weight
     return fn(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def attention_forward(out, lse, probs, qkv, B, T, NH, C, impl=ATT_FLASH, mode=MODE_TF32, stream=None):
+    """gpt2_attention_forward (include/gpt2_attention.h)"""
+    return lib.gpt2_attention_forward(_p(out), _p(lse), _p(probs), _p(qkv), B, T, NH, C, impl, mode, stream)
+
+
+def attention_backward(g_qkv, g_out, qkv, out, lse, probs, row_scratch, tt_scratch, B, T, C, NH, impl=ATT_FLASH,
+                       mode=MODE_TF32, stream=None):
+    """gpt2_attention_backward (include/gpt2_attention.h)"""
+    return lib.gpt2_attention_backward(_p(g_qkv), _p(g_out), _p(qkv), _p(out), _p(lse), _p(probs), _p(row_scratch),
+                                       _p(tt_scratch), B, T, C, NH, impl, mode, stream)
 
 
 def backward_weight_noalloc(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=None):

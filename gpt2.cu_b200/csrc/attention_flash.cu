@@ -1,0 +1,567 @@
+// Causal self-attention without the T x T tensors: one tcgen05 kernel in three modes.
+//
+// A CTA owns 128 rows (the 128 TMEM lanes) of one (sequence, head) and walks 64-wide column blocks:
+//
+//   FWD    rows = queries i, columns = keys j <= i
+//          S = Q_i K_j^T -> online softmax (running max m, sum l) -> P_j -> O += P_j V_j
+//          out = O / l, lse = m + log2(l) (base-2 domain, kept for the backward pass)
+//   BWD_Q  rows = queries i, columns = keys j <= i
+//          S = Q_i K_j^T, dP = dO_i V_j^T -> dS = P o (dP - delta) / 8 -> dQ += dS K_j
+//   BWD_KV rows = keys j, columns = queries i >= j
+//          S^T = K_j Q_i^T, dP^T = V_j dO_i^T -> P^T, dS^T -> dV += P^T dO_i, dK += dS^T Q_i
+//
+// with P = 2^(S * log2(e)/8 - lse) recomputed in the backward modes and delta = rowsum(dO o O).
+// All three are "score MMAs into TMEM -> 128 threads turn a TMEM row into a K-major shared-memory
+// tile (written in the 128-byte swizzle the tensor core expects) -> accumulate MMAs", so they share
+// one skeleton: warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
+// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs, warps 2-5 do the row work.
+// The score accumulators are double-buffered in TMEM, so the score MMAs of block t+1 run while the
+// row work of block t is in progress.
+//
+// Operands are fp32 read as TF32 by the tensor core; P and dS are rounded to TF32 (to nearest) before
+// they are stored, so the second contraction carries no truncation bias. The reference computes the
+// same attention with one CTA per query row and materialised T x T tensors
+// (src/layers/attention.cu:43-363); buffers and layouts (qkv in, atty out) are the same.
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "layers.h"
+#include "linear_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace g2l {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int FHS = 64;        // head size
+constexpr int FROWS = 128;     // rows per CTA (TMEM lanes)
+constexpr int FCOLS = 64;      // columns per step
+constexpr int F_THREADS = 192; // warp 0 producer, warp 1 MMA, warps 2-5 row work
+
+enum { F_FWD = 0, F_BWD_Q = 1, F_BWD_KV = 2 };
+
+constexpr int TILE_A = FROWS * FHS * 4;   // 32 KiB: [128][64] K-major, two 16 KiB k-blocks
+constexpr int TILE_B = FCOLS * FHS * 4;   // 16 KiB: [64][64]  K-major (two 8 KiB k-blocks) or MN-major
+constexpr int TILE_P = FROWS * FCOLS * 4; // 32 KiB: [128][64] K-major, written by the row-work warps
+
+struct FlashMaps {
+  // K-major views [T rows][64] of one head (box 32 x 64) and MN-major views (box 32 x 32 x 2 chunks)
+  CUtensorMap k_major[4];   // Q, K, V, dO
+  CUtensorMap mn_major[4];  // Q, K, V, dO
+};
+enum { X_Q = 0, X_K = 1, X_V = 2, X_DO = 3 };
+
+struct FlashArgs {
+  int B, T, C, NH;
+  float *out;          // FWD: [B*T][C]
+  float *lse;          // [B][NH][T], base-2 log-sum-exp of the scaled scores
+  const float *delta;  // [B][NH][T]
+  float *dqkv;         // BWD: [B*T][3C]
+  int *status;         // 0, or the site of a wait that gave up
+  long long wait_limit_ns;
+};
+
+struct FlashCtrl {
+  unsigned long long fixed_full, sc_full, sc_empty, ac_full, ac_empty, s_full[2], p_ready, acc_done;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int MODE>
+struct Cfg {
+  static constexpr int NA = MODE == F_FWD ? 1 : 2;      // fixed A tiles; also score MMAs per step
+  static constexpr int NP = MODE == F_BWD_KV ? 2 : 1;   // tiles the row work writes; also accumulators
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_SB = OFF_A + NA * TILE_A;    // score-stage B operands (K-major)
+  static constexpr int OFF_AB = OFF_SB + NA * TILE_B;   // accumulate-stage B operands (MN-major)
+  static constexpr int OFF_P = OFF_AB + NP * TILE_B;
+  static constexpr int OFF_VEC = OFF_P + NP * TILE_P;   // BWD_KV: lse and delta of the step's 64 queries
+  static constexpr int OFF_CTRL = OFF_VEC + 4 * 2 * 128 * 4;  // per row-work warp, two buffers
+  static constexpr int SMEM = 1024 + OFF_CTRL + 128;
+  static constexpr int TMEM_COLS = MODE == F_FWD ? 256 : 512;
+  // TMEM columns: score buffers first (2 x NA x 64), then the accumulators
+  static constexpr int COL_ACC = 2 * NA * FCOLS;
+};
+
+__device__ __forceinline__ bool f_wait(uint32_t bar, uint32_t parity, FlashCtrl *ctrl, const FlashArgs &a, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
+      if (globaltimer_ns() - t0 > a.wait_limit_ns) {
+        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
+        atomicCAS(a.status, 0, site);
+        return false;
+      }
+    }
+  }
+}
+
+// Row-work warps wait as a warp: lane 0 polls and every lane takes its verdict, so a wait that
+// gives up can never split a warp (or leave part of it behind at a later warp-level sync).
+__device__ __forceinline__ bool w_wait(uint32_t bar, uint32_t parity, FlashCtrl *ctrl, const FlashArgs &a, int site,
+                                       int lane) {
+  int okl = 1;
+  if (lane == 0) okl = f_wait(bar, parity, ctrl, a, site) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, okl, 0) != 0;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float f_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// this thread's row (0..127) of a [128][64] K-major tile: 16 float4 chunks in the 128-byte swizzle
+__device__ __forceinline__ void store_row(uint32_t tile, int r, const float (&v)[FCOLS]) {
+  const uint32_t row = tile + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+#pragma unroll
+  for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      st_shared_v4(row + kb * 16384 + ((q ^ (r & 7)) << 4), v[kb * 32 + q * 4], v[kb * 32 + q * 4 + 1],
+                   v[kb * 32 + q * 4 + 2], v[kb * 32 + q * 4 + 3]);
+}
+
+__device__ __forceinline__ void load_cols64(uint32_t taddr, float (&v)[FCOLS]) {
+  uint32_t r0[32], r1[32];
+  tmem_ld_32x32(taddr, r0);
+  tmem_ld_32x32(taddr + 32, r1);
+  tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {
+    v[c] = __uint_as_float(r0[c]);
+    v[32 + c] = __uint_as_float(r1[c]);
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(F_THREADS, 1)
+attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
+  using K = Cfg<MODE>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - raw);
+  FlashCtrl *ctrl = reinterpret_cast<FlashCtrl *>(base_ptr + K::OFF_CTRL);
+  float *vec = reinterpret_cast<float *>(base_ptr + K::OFF_VEC);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_rb = a.T / FROWS;
+  // heavy row blocks first: FWD / BWD_Q rows near the end of the sequence see the most keys,
+  // BWD_KV rows near the start see the most queries
+  const int bh_count = a.B * a.NH;
+  const int order = blockIdx.x / bh_count;
+  const int rb = MODE == F_BWD_KV ? order : n_rb - 1 - order;
+  const int bh = blockIdx.x % bh_count;
+  const int b = bh / a.NH, h = bh % a.NH;
+  const int row0 = rb * FROWS;
+  // column blocks [cb0, cb1)
+  const int cb0 = MODE == F_BWD_KV ? 2 * rb : 0;
+  const int cb1 = MODE == F_BWD_KV ? a.T / FCOLS : 2 * rb + 2;
+  const int n_it = cb1 - cb0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctrl->fixed_full), 1);
+    mbar_init(smem_u32(&ctrl->sc_full), 1);
+    mbar_init(smem_u32(&ctrl->sc_empty), 1);
+    mbar_init(smem_u32(&ctrl->ac_full), 1);
+    mbar_init(smem_u32(&ctrl->ac_empty), 1);
+    mbar_init(smem_u32(&ctrl->s_full[0]), 1);
+    mbar_init(smem_u32(&ctrl->s_full[1]), 1);
+    mbar_init(smem_u32(&ctrl->p_ready), 128);
+    mbar_init(smem_u32(&ctrl->acc_done), 1);
+    ctrl->abort = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), K::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&ctrl->tmem_base);
+
+  // which tensors play which part
+  //              fixed A0, A1        score B0, B1      accumulate B (MN-major) 0, 1
+  //   FWD        Q                   K                 V
+  //   BWD_Q      Q, dO               K, V              K
+  //   BWD_KV     K, V                Q, dO             dO (with P^T), Q (with dS^T)
+  constexpr int A0 = MODE == F_BWD_KV ? X_K : X_Q;
+  constexpr int A1 = MODE == F_BWD_KV ? X_V : X_DO;
+  constexpr int SB0 = MODE == F_BWD_KV ? X_Q : X_K;
+  constexpr int SB1 = MODE == F_BWD_KV ? X_DO : X_V;
+  constexpr int AB0 = MODE == F_FWD ? X_V : (MODE == F_BWD_Q ? X_K : X_DO);
+  constexpr int AB1 = X_Q;
+
+  if (warp == 0) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      const uint32_t bar = smem_u32(&ctrl->fixed_full);
+      mbar_arrive_expect_tx(bar, K::NA * TILE_A);
+#pragma unroll
+      for (int x = 0; x < K::NA; ++x) {
+        const CUtensorMap *m = &maps.k_major[x == 0 ? A0 : A1];
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+            tma_load_4d(base + K::OFF_A + x * TILE_A + kb * 16384 + half * 8192, m, bar, kb * 32, row0 + half * 64, h, b);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int c0 = (cb0 + it) * FCOLS;
+        const uint32_t par = (uint32_t)(it & 1);
+        ok = f_wait(smem_u32(&ctrl->sc_empty), par ^ 1u, ctrl, a, 1);
+        if (!ok) break;
+        {
+          const uint32_t sb = smem_u32(&ctrl->sc_full);
+          mbar_arrive_expect_tx(sb, K::NA * TILE_B);
+#pragma unroll
+          for (int x = 0; x < K::NA; ++x) {
+            const CUtensorMap *m = &maps.k_major[x == 0 ? SB0 : SB1];
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+              tma_load_4d(base + K::OFF_SB + x * TILE_B + kb * 8192, m, sb, kb * 32, c0, h, b);
+          }
+        }
+        ok = f_wait(smem_u32(&ctrl->ac_empty), par ^ 1u, ctrl, a, 2);
+        if (!ok) break;
+        {
+          const uint32_t ab = smem_u32(&ctrl->ac_full);
+          mbar_arrive_expect_tx(ab, K::NP * TILE_B);
+#pragma unroll
+          for (int y = 0; y < K::NP; ++y) {
+            const CUtensorMap *m = &maps.mn_major[y == 0 ? AB0 : AB1];
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb)
+              tma_load_5d(base + K::OFF_AB + y * TILE_B + kb * 8192, m, ab, 0, c0 + kb * 32, 0, h, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      const uint64_t hiK = smem_desc_hi(16, 1024, 2);     // K-major, 128-byte swizzle
+      const uint64_t hiMN = smem_desc_hi(4096, 512, 1);   // MN-major, 32-byte swizzle atoms
+      const uint32_t idesc_sc = make_idesc_tf32(FROWS, FCOLS, 0, 0);
+      const uint32_t idesc_ac = make_idesc_tf32(FROWS, FHS, 0, 1);
+      bool ok = f_wait(smem_u32(&ctrl->fixed_full), 0, ctrl, a, 3);
+      tc_fence_after();
+      // score MMAs of step k into TMEM buffer k & 1
+      auto issue_score = [&](int k) -> bool {
+        if (!f_wait(smem_u32(&ctrl->sc_full), (uint32_t)(k & 1), ctrl, a, 4)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int x = 0; x < K::NA; ++x) {
+          const uint32_t d = tmem + (uint32_t)((k & 1) * K::NA + x) * FCOLS;
+          const uint32_t a_addr = base + K::OFF_A + x * TILE_A;
+          const uint32_t b_addr = base + K::OFF_SB + x * TILE_B;
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              mma_tf32(d, smem_desc(hiK, a_addr + kb * 16384 + ks * 32), smem_desc(hiK, b_addr + kb * 8192 + ks * 32),
+                       idesc_sc, (kb | ks) ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&ctrl->s_full[k & 1]));
+        mma_commit(smem_u32(&ctrl->sc_empty));
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_score(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (it + 1 < n_it) ok = issue_score(it + 1);
+        if (!ok) break;
+        ok = f_wait(smem_u32(&ctrl->p_ready), (uint32_t)(it & 1), ctrl, a, 5);
+        if (!ok) break;
+        ok = f_wait(smem_u32(&ctrl->ac_full), (uint32_t)(it & 1), ctrl, a, 6);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int y = 0; y < K::NP; ++y) {
+          const uint32_t d = tmem + K::COL_ACC + y * FHS;
+          const uint32_t a_addr = base + K::OFF_P + y * TILE_P;
+          const uint32_t b_addr = base + K::OFF_AB + y * TILE_B;
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              // FWD reads every step's product on its own (the rescaling happens in registers)
+              const uint32_t acc = (MODE == F_FWD ? 0u : (it > 0 ? 1u : 0u)) | ((kb | ks) ? 1u : 0u);
+              mma_tf32(d, smem_desc(hiK, a_addr + kb * 16384 + ks * 32),
+                       smem_desc(hiMN, b_addr + kb * 8192 + ks * 1024), idesc_ac, acc);
+            }
+        }
+        mma_commit(smem_u32(&ctrl->acc_done));
+        mma_commit(smem_u32(&ctrl->ac_empty));
+      }
+    }
+  } else {
+    // =============================== row work ===============================
+    const int q4 = warp & 3;                  // TMEM lane quarter of this warp
+    const int r = q4 * 32 + lane;             // row inside the block
+    const int grow = row0 + r;                // position in the sequence
+    const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
+    const float cs = 0.125f * 1.4426950408889634f;  // 1/sqrt(64) * log2(e)
+    const long long vbase = ((long long)b * a.NH + h) * a.T;
+    bool ok = true;
+
+    if (MODE == F_FWD) {
+      float o[FHS];
+#pragma unroll
+      for (int c = 0; c < FHS; ++c) o[c] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+      for (int it = 0; it < n_it && ok; ++it) {
+        ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 7, lane);
+        if (!ok) break;
+        tc_fence_after();
+        float s[FCOLS];
+        load_cols64(tlane + (uint32_t)(it & 1) * FCOLS, s);
+        const int c0 = (cb0 + it) * FCOLS;
+        float mx = m_run;
+#pragma unroll
+        for (int c = 0; c < FCOLS; ++c) {
+          s[c] = (c0 + c > grow) ? -INFINITY : s[c] * cs;
+          mx = fmaxf(mx, s[c]);
+        }
+        const float alpha = ex2(m_run - mx);  // first step: 2^(-inf) = 0; mx is finite from step 0 on (key 0 <= any query)
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < FCOLS; ++c) {
+          s[c] = f_tf32(ex2(s[c] - mx));
+          sum += s[c];
+        }
+        l_run = l_run * alpha + sum;
+        m_run = mx;
+        if (it > 0) {
+          // the previous product is complete: fold it in (it was formed with the previous maximum),
+          // and its operands in shared memory are free again
+          ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((it - 1) & 1), ctrl, a, 8, lane);
+          if (!ok) break;
+          tc_fence_after();
+          float pv[FHS];
+          load_cols64(tlane + K::COL_ACC, pv);
+#pragma unroll
+          for (int c = 0; c < FHS; ++c) o[c] = o[c] * alpha_prev + pv[c];
+        }
+        alpha_prev = alpha;
+        store_row(base + K::OFF_P, r, s);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->p_ready));
+      }
+      if (ok && n_it > 0) {
+        ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((n_it - 1) & 1), ctrl, a, 9, lane);
+        if (ok) {
+          tc_fence_after();
+          float pv[FHS];
+          load_cols64(tlane + K::COL_ACC, pv);
+          const float inv = 1.f / l_run;
+          float *dst = a.out + ((long long)b * a.T + grow) * a.C + h * FHS;
+#pragma unroll
+          for (int c = 0; c < FHS; c += 4)
+            *reinterpret_cast<float4 *>(dst + c) =
+                make_float4((o[c] * alpha_prev + pv[c]) * inv, (o[c + 1] * alpha_prev + pv[c + 1]) * inv,
+                            (o[c + 2] * alpha_prev + pv[c + 2]) * inv, (o[c + 3] * alpha_prev + pv[c + 3]) * inv);
+          a.lse[vbase + grow] = m_run + log2f(l_run);
+        }
+      }
+    } else if (MODE == F_BWD_Q) {
+      const float lse = a.lse[vbase + grow];
+      const float dlt = a.delta[vbase + grow];
+      for (int it = 0; it < n_it && ok; ++it) {
+        ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 10, lane);
+        if (!ok) break;
+        tc_fence_after();
+        float s[FCOLS], dp[FCOLS];
+        load_cols64(tlane + (uint32_t)((it & 1) * 2) * FCOLS, s);
+        load_cols64(tlane + (uint32_t)((it & 1) * 2 + 1) * FCOLS, dp);
+        const int c0 = (cb0 + it) * FCOLS;
+#pragma unroll
+        for (int c = 0; c < FCOLS; ++c) {
+          const float p = (c0 + c > grow) ? 0.f : ex2(s[c] * cs - lse);
+          s[c] = f_tf32(p * (dp[c] - dlt) * 0.125f);
+        }
+        if (it > 0) {
+          ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((it - 1) & 1), ctrl, a, 11, lane);
+          if (!ok) break;
+        }
+        store_row(base + K::OFF_P, r, s);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->p_ready));
+      }
+      if (ok && n_it > 0) {
+        ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((n_it - 1) & 1), ctrl, a, 12, lane);
+        if (ok) {
+          tc_fence_after();
+          float dq[FHS];
+          load_cols64(tlane + K::COL_ACC, dq);
+          float *dst = a.dqkv + ((long long)b * a.T + grow) * 3 * a.C + h * FHS;
+#pragma unroll
+          for (int c = 0; c < FHS; c += 4)
+            *reinterpret_cast<float4 *>(dst + c) = make_float4(dq[c], dq[c + 1], dq[c + 2], dq[c + 3]);
+        }
+      }
+    } else {
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int c0 = (cb0 + it) * FCOLS;
+        // lse and delta of the step's 64 queries: every warp keeps its own copy (double-buffered by
+        // step parity), so only warp-level synchronisation is involved
+        float *vv = vec + ((warp - 2) * 2 + (it & 1)) * 128;
+        vv[lane] = a.lse[vbase + c0 + lane];
+        vv[32 + lane] = a.lse[vbase + c0 + 32 + lane];
+        vv[64 + lane] = a.delta[vbase + c0 + lane];
+        vv[96 + lane] = a.delta[vbase + c0 + 32 + lane];
+        __syncwarp();
+        ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 13, lane);
+        if (!ok) break;
+        tc_fence_after();
+        float s[FCOLS], dp[FCOLS];
+        load_cols64(tlane + (uint32_t)((it & 1) * 2) * FCOLS, s);
+        load_cols64(tlane + (uint32_t)((it & 1) * 2 + 1) * FCOLS, dp);
+#pragma unroll
+        for (int c = 0; c < FCOLS; ++c) {
+          const float p = (grow > c0 + c) ? 0.f : ex2(s[c] * cs - vv[c]);  // key after the query: masked
+          s[c] = f_tf32(p);
+          dp[c] = f_tf32(p * (dp[c] - vv[64 + c]) * 0.125f);
+        }
+        if (it > 0) {
+          ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((it - 1) & 1), ctrl, a, 14, lane);
+          if (!ok) break;
+        }
+        store_row(base + K::OFF_P, r, s);
+        store_row(base + K::OFF_P + TILE_P, r, dp);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->p_ready));
+      }
+      if (ok && n_it > 0) {
+        ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((n_it - 1) & 1), ctrl, a, 15, lane);
+        if (ok) {
+          tc_fence_after();
+          float g[FHS];
+          float *dst = a.dqkv + ((long long)b * a.T + grow) * 3 * a.C + h * FHS;
+          load_cols64(tlane + K::COL_ACC, g);  // dV (with P^T)
+#pragma unroll
+          for (int c = 0; c < FHS; c += 4)
+            *reinterpret_cast<float4 *>(dst + 2 * a.C + c) = make_float4(g[c], g[c + 1], g[c + 2], g[c + 3]);
+          load_cols64(tlane + K::COL_ACC + FHS, g);  // dK (with dS^T)
+#pragma unroll
+          for (int c = 0; c < FHS; c += 4)
+            *reinterpret_cast<float4 *>(dst + a.C + c) = make_float4(g[c], g[c + 1], g[c + 2], g[c + 3]);
+        }
+      }
+    }
+  }
+
+  // =============================== teardown ===============================
+  if (*reinterpret_cast<volatile int *>(&ctrl->abort)) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies and MMAs in flight land
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, K::TMEM_COLS);
+  }
+}
+
+// status word shared by the three modes (device memory, one per process and device would be
+// cleaner; attention runs on one device per process here)
+int *flash_status_ptr() {
+  static int *p = nullptr;
+  if (!p) {
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+  }
+  return p;
+}
+
+int build_maps(FlashMaps *m, const float *qkv, const float *dout, int B, int T, int C, int NH) {
+  const float *src[4] = {qkv, qkv + C, qkv + 2 * C, dout};
+  const long long ld[4] = {3LL * C, 3LL * C, 3LL * C, (long long)C};
+  for (int x = 0; x < 4; ++x) {
+    if (!src[x]) continue;
+    int e = encode_map_batched_k(&m->k_major[x], src[x], FHS, T, ld[x], NH, FHS, B, (long long)T * ld[x], FCOLS);
+    if (e) return e;
+    e = encode_map_batched_mn(&m->mn_major[x], src[x], FHS, T, ld[x], NH, FHS, B, (long long)T * ld[x], 2);
+    if (e) return e;
+  }
+  return GPT2L_OK;
+}
+
+template <int MODE>
+int launch(const FlashMaps &maps, const FlashArgs &args, cudaStream_t st) {
+  static bool attr_set = false;  // per process; one device per process
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_flash_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MODE>::SMEM) !=
+        cudaSuccess)
+      return GPT2L_ERR_CUDA;
+    attr_set = true;
+  }
+  const int grid = args.B * args.NH * (args.T / FROWS);
+  attn_flash_kernel<MODE><<<grid, F_THREADS, Cfg<MODE>::SMEM, st>>>(maps, args);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+}  // namespace
+
+bool attention_flash_supported(int T, int C, int NH) { return C == NH * FHS && T % FROWS == 0 && (C & 3) == 0; }
+
+int attention_flash_status() {
+  int *p = flash_status_ptr();
+  int v = -1;
+  if (!p || cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}
+
+int attention_flash_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t st) {
+  if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
+  FlashMaps maps;
+  int e = build_maps(&maps, qkv, nullptr, B, T, C, NH);
+  if (e) return e;
+  FlashArgs a = {};
+  a.B = B; a.T = T; a.C = C; a.NH = NH;
+  a.out = out; a.lse = lse;
+  a.status = flash_status_ptr();
+  a.wait_limit_ns = 2000000000LL;
+  if (!a.status) return GPT2L_ERR_CUDA;
+  return launch<F_FWD>(maps, a, st);
+}
+
+// dqkv[B*T][3C] from dout[B*T][C]; out and lse are the forward pass's; delta is scratch of [B][NH][T]
+int attention_flash_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
+                             const float *lse, int B, int T, int C, int NH, cudaStream_t st) {
+  if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
+  int e = attention_row_dot(delta, dout, out, B, T, C, NH, st);
+  if (e) return e;
+  FlashMaps maps;
+  e = build_maps(&maps, qkv, dout, B, T, C, NH);
+  if (e) return e;
+  FlashArgs a = {};
+  a.B = B; a.T = T; a.C = C; a.NH = NH;
+  a.lse = const_cast<float *>(lse); a.delta = delta; a.dqkv = dqkv;
+  a.status = flash_status_ptr();
+  a.wait_limit_ns = 2000000000LL;
+  if (!a.status) return GPT2L_ERR_CUDA;
+  e = launch<F_BWD_KV>(maps, a, st);
+  if (e) return e;
+  return launch<F_BWD_Q>(maps, a, st);
+}
+
+}  // namespace g2l

@@ -60,6 +60,14 @@ attn_delta_kernel(float *delta, const float *dout, const float *out, int T, int 
   if (lane == 0) delta[((bt / T) * NH + h) * T + bt % T] = s;
 }
 
+// delta[B][NH][T] = rowsum(dout o out) per head
+int attention_row_dot(float *delta, const float *dout, const float *out, int B, int T, int C, int NH, cudaStream_t st) {
+  const long long rows = (long long)B * NH * T;
+  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(delta, dout, out, T, C, NH, rows);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
 static int run(DeviceCtx *ctx, const BatchedDesc &d, cudaStream_t st) {
   GemmOp op;
   int e = build_batched_op(d, ctx->num_sms, &op);
@@ -115,10 +123,7 @@ int attention_backward_gemm(float *dqkv, float *dP, float *delta, const float *d
   const long long qs = (long long)T * 3 * C, os = (long long)T * C;
   BatchedDesc d;
   d.batch_outer = B; d.batch_inner = NH; d.mode = mode;
-  const long long rows = (long long)B * NH * T;
-  attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(delta, dout, out, T, C, NH, rows);
-  count_launch();
-  if (cudaGetLastError() != cudaSuccess) return GPT2L_ERR_CUDA;
+  if ((err = attention_row_dot(delta, dout, out, B, T, C, NH, st))) return err;
   // dS = P o (dO V^T - delta) / 8   (P is zero past the diagonal inside the diagonal tiles, so dS is too)
   d.aux = P; d.aux_row = delta; d.aux_scale = 0.125f; d.aux_op = AUX_SOFTMAX_GRAD;
   d.Mc = T; d.Nc = T; d.Kc = AHS; d.a_mn = 0; d.b_mn = 0;

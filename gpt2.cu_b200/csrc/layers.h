@@ -29,4 +29,16 @@ int attention_forward_gemm(float *out, float *P, const float *qkv, int B, int T,
 int attention_backward_gemm(float *dqkv, float *dP, float *delta, const float *dout, const float *out, const float *P,
                             const float *qkv, int B, int T, int C, int NH, int mode, cudaStream_t st);
 
+int attention_row_dot(float *delta, const float *dout, const float *out, int B, int T, int C, int NH, cudaStream_t st);
+
+// attention without T x T tensors (attention_flash.cu); needs T % 128 == 0 and head size 64. lse is
+// [B][NH][T] (base-2 log-sum-exp of the scaled scores), written by the forward pass and read by the
+// backward pass; delta is scratch of the same size. attention_flash_status() returns 0, or the
+// number of the wait that gave up in a kernel (bounded waits), or -1 when it cannot be read.
+bool attention_flash_supported(int T, int C, int NH);
+int attention_flash_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t st);
+int attention_flash_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
+                             const float *lse, int B, int T, int C, int NH, cudaStream_t st);
+int attention_flash_status();
+
 }  // namespace g2l

@@ -143,6 +143,13 @@ struct BatchedDesc {
   int aux_op = 0;
 };
 int build_batched_op(const BatchedDesc &d, int num_sms, GemmOp *op);
+// Batched tensor maps over [outer][inner] slices of a row-major matrix with row pitch ld (floats):
+// K-major view {red, rows, inner, outer} with box 32 x box_rows (128-byte swizzle), and MN-major view
+// {32, red_rows, mn / 32, inner, outer} with box 32 x 32 x chunks (32-byte swizzle atoms).
+int encode_map_batched_k(CUtensorMap *map, const float *base, uint64_t red, uint64_t rows, uint64_t ld,
+                         uint64_t nb_inner, uint64_t bs_inner, uint64_t nb_outer, uint64_t bs_outer, uint32_t box_rows);
+int encode_map_batched_mn(CUtensorMap *map, const float *base, uint64_t mn, uint64_t red_rows, uint64_t ld,
+                          uint64_t nb_inner, uint64_t bs_inner, uint64_t nb_outer, uint64_t bs_outer, uint32_t chunks);
 
 // host-side description used to build a GemmOp
 struct GemmDesc {

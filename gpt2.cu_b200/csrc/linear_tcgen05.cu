@@ -722,7 +722,7 @@ int build_op(const GemmDesc &d, int num_sms, GemmOp *op) {
 }
 
 // K-major batched operand: [outer][inner][rows][red] -> dims {red, rows, inner batches, outer batches}
-static int encode_map_batched_k(CUtensorMap *map, const float *base, uint64_t red, uint64_t rows, uint64_t ld,
+int encode_map_batched_k(CUtensorMap *map, const float *base, uint64_t red, uint64_t rows, uint64_t ld,
                                 uint64_t nb_inner, uint64_t bs_inner, uint64_t nb_outer, uint64_t bs_outer,
                                 uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
@@ -738,7 +738,7 @@ static int encode_map_batched_k(CUtensorMap *map, const float *base, uint64_t re
 }
 // MN-major batched operand stored [red rows][mn] (mn a multiple of 32), viewed in 32-column chunks:
 // dims {32, red rows, mn / 32, inner batches, outer batches}
-static int encode_map_batched_mn(CUtensorMap *map, const float *base, uint64_t mn, uint64_t red_rows, uint64_t ld,
+int encode_map_batched_mn(CUtensorMap *map, const float *base, uint64_t mn, uint64_t red_rows, uint64_t ld,
                                  uint64_t nb_inner, uint64_t bs_inner, uint64_t nb_outer, uint64_t bs_outer,
                                  uint32_t chunks) {
   EncodeTiledFn fn = get_encode_fn();

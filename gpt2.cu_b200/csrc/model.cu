@@ -46,6 +46,7 @@ struct gpt2_model {
   float *delta = nullptr;    // [B][NH][T]
   float *datt = nullptr;     // [B][NH][T][T] gradient scratch (tensor-core attention only)
   bool attn_gemm = false;    // attention as batched GEMMs on the tensor cores
+  bool attn_flash = false;   // attention as one fused tensor-core kernel per pass
   std::vector<LayerActs> la;
   const int *tokens = nullptr;  // of the last forward
   float *h_losses = nullptr;    // pinned
@@ -107,11 +108,17 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
   const int NH = cfg->n_head;
   long long a = 0;
   auto act = [&](long long n) { long long o = a; a += (n + 3) / 4 * 4; return o; };
-  // attention on the tensor cores needs T % 32 == 0; GPT2_ATTENTION=simt forces the CUDA-core kernels
+  // Attention: the fused tensor-core kernel (no T x T tensors; T % 128 == 0) in TF32 mode, batched
+  // GEMMs on the linear-layer kernel (T % 32 == 0; they follow the 3xTF32 mode) otherwise, CUDA-core
+  // kernels for everything else. GPT2_ATTENTION = flash | gemm | simt overrides the choice.
   m->attn_gemm = attention_gemm_supported(T, C, NH);
+  m->attn_flash = attention_flash_supported(T, C, NH) && mode == GPT2L_MODE_TF32;
   if (const char *env = getenv("GPT2_ATTENTION")) {
-    if (!strcmp(env, "simt")) m->attn_gemm = false;
+    if (!strcmp(env, "simt")) m->attn_gemm = m->attn_flash = false;
+    else if (!strcmp(env, "gemm")) m->attn_flash = false;
+    else if (!strcmp(env, "flash")) m->attn_flash = attention_flash_supported(T, C, NH);
   }
+  if (m->attn_flash) m->attn_gemm = false;
   const long long att_floats = m->attn_gemm ? (long long)B * NH * T * T : 0;
   std::vector<long long> o_layer(L * 14);
   const long long o_encoded = act(M * C);
@@ -227,7 +234,8 @@ int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt
     LayerActs &a = m->la[l];
     CK(layernorm_forward(a.ln1, a.ln1_mean, a.ln1_rstd, res, P + p.ln1_w, P + p.ln1_b, M, C, st));
     CK(gpt2_linear_forward(a.qkv, a.ln1, P + p.qkv_w, P + p.qkv_b, B, T, C, 3 * C, &o, stream));
-    if (m->attn_gemm) CK(attention_forward_gemm(a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
+    if (m->attn_flash) CK(attention_flash_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st));
+    else if (m->attn_gemm) CK(attention_forward_gemm(a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
     else CK(attention_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st));
     gpt2_linear_opts orr = o;  // both projections add the residual stream in their epilogue
     orr.aux_op = GPT2L_AUX_ADD;
@@ -292,7 +300,8 @@ int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream) {
   // attention: res2 = res_in + proj(attention(qkv(ln1(res_in))))
   CK(gpt2_linear_backward_input(m->tmp_c, m->dresid, P + p.proj_w, B, T, C, C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.proj_w, G + p.proj_b, m->dresid, a.atty, B, T, C, C, &o, stream));
-  if (m->attn_gemm) CK(attention_backward_gemm(m->dbig, m->datt, m->delta, m->tmp_c, a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
+  if (m->attn_flash) CK(attention_flash_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
+  else if (m->attn_gemm) CK(attention_backward_gemm(m->dbig, m->datt, m->delta, m->tmp_c, a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st));
   else CK(attention_backward(m->dbig, m->delta, m->tmp_c, a.atty, a.qkv, a.lse, B, T, C, NH, st));
   CK(gpt2_linear_backward_input(m->tmp_c, m->dbig, P + p.qkv_w, B, T, C, 3 * C, &o, stream));
   CK(gpt2_linear_backward_weight(G + p.qkv_w, G + p.qkv_b, m->dbig, a.ln1, B, T, C, 3 * C, &o, stream));

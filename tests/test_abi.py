@@ -30,6 +30,19 @@ def test_library_exports_every_model_symbol(g):
         assert hasattr(g.lib, n)
 
 
+def test_library_exports_every_attention_symbol(g):
+    names = [n for n in header_functions("gpt2_attention.h") if n.startswith("gpt2_attention_")]
+    assert sorted(names) == sorted(g.ATTENTION_EXPORTS)
+    for n in names:
+        assert hasattr(g.lib, n)
+    # shape checks are host-only
+    assert g.lib.gpt2_attention_supported(g.ATT_FLASH, 1024, 768, 12) == 1
+    assert g.lib.gpt2_attention_supported(g.ATT_FLASH, 1000, 768, 12) == 0
+    assert g.lib.gpt2_attention_supported(g.ATT_GEMM, 992, 768, 12) == 1
+    assert g.lib.gpt2_attention_supported(g.ATT_SIMT, 7, 768, 12) == 1
+    assert g.lib.gpt2_attention_supported(g.ATT_SIMT, 7, 768, 8) == 0
+
+
 def test_version(g):
     assert g.lib.gpt2_linear_version() == 100
 
