@@ -468,7 +468,9 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
     out = {"tokens_per_s": B * T * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps,
            "config": f"GPT-2 small (12 layers, 768 wide, vocabulary 50257 padded to 50304), B={B} per GPU, T={T}, "
                      f"AdamW lr 3e-4 betas 0.9/0.95 wd 0.1, fp32 master weights, {'3xTF32' if mode else 'TF32'} GEMMs, "
-                     "attention as batched causal GEMMs on the same tensor-core kernel", "loss_after": loss,
+                     + ("attention as batched causal GEMMs on the linear-layer kernel" if mode else
+                        "fused causal attention on the tensor cores (no T x T tensors)")
+                     + "; residual adds and GELU backward in GEMM epilogues", "loss_after": loss,
            "gradient_exchange": "none (1 GPU)" if world == 1 else "NCCL average, one bucket per block, overlapped"}
     model.close()
     return out

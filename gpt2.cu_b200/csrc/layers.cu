@@ -6,6 +6,8 @@
 // softmax and cross-entropy are one pass that leaves dlogits in place of the logits, and layernorm
 // works a row per warp. All fp32 CUDA-core code; the GEMMs around them are the tcgen05 path.
 #include <cuda_runtime.h>
+#include <stdlib.h>
+#include <string.h>
 #include <math.h>
 
 #include "layers.h"
@@ -216,6 +218,63 @@ softmax_xent_kernel(float *logits, float *losses, const int *targets, int V, int
     g.y = c + 1 < V ? srow[c + 1] * k - (c + 1 == tgt ? scale : 0.f) : 0.f;
     g.z = c + 2 < V ? srow[c + 2] * k - (c + 2 == tgt ? scale : 0.f) : 0.f;
     g.w = c + 3 < V ? srow[c + 3] * k - (c + 3 == tgt ? scale : 0.f) : 0.f;
+    *reinterpret_cast<float4 *>(row + c) = g;
+  }
+}
+
+// The same without shared-memory staging: pass 1 streams the row from HBM once and keeps a running
+// (max, sum) pair per thread; pass 2 reads the row again (from L2: the rows in flight on all SMs are a few
+// tens of MB) and writes dlogits. No large shared-memory footprint, so several blocks share an SM and
+// the loads of one row overlap the stores of another.
+__global__ void __launch_bounds__(512, 3)
+softmax_xent_online_kernel(float *logits, float *losses, const int *targets, int V, int Vp, float scale) {
+  __shared__ float red_m[16], red_s[16];
+  float *row = logits + (long long)blockIdx.x * Vp;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float L2E = 1.4426950408889634f;
+  float m = -INFINITY, s = 0.f;  // base-2 domain: m = max(x * log2e), s = sum 2^(x*log2e - m)
+  const int V4 = V & ~3;
+  for (int c = tid * 4; c < V4; c += 512 * 4) {
+    float4 v = *reinterpret_cast<const float4 *>(row + c);
+    v.x *= L2E; v.y *= L2E; v.z *= L2E; v.w *= L2E;
+    const float mn = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    s = s * exp2f(m - mn) + exp2f(v.x - mn) + exp2f(v.y - mn) + exp2f(v.z - mn) + exp2f(v.w - mn);
+    m = mn;
+  }
+  for (int c = V4 + tid; c < V; c += 512) {
+    const float v = row[c] * L2E;
+    const float mn = fmaxf(m, v);
+    s = s * exp2f(m - mn) + exp2f(v - mn);
+    m = mn;
+  }
+  // combine (m, s) pairs: warp, then block. A thread that saw no element holds (-inf, 0); guard the
+  // -inf - -inf case.
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f(m - mn)) + (m2 == -INFINITY ? 0.f : s2 * exp2f(m2 - mn));
+    m = mn;
+  }
+  if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
+  __syncthreads();
+  m = red_m[0]; s = red_s[0];
+  for (int i = 1; i < 16; ++i) {
+    const float m2 = red_m[i], s2 = red_s[i];
+    const float mn = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * exp2f(m - mn)) + (m2 == -INFINITY ? 0.f : s2 * exp2f(m2 - mn));
+    m = mn;
+  }
+  const int tgt = targets[blockIdx.x];
+  // loss = -(x_t - max - ln(sum)) in natural units
+  if (tid == 0) losses[blockIdx.x] = -((row[tgt] * L2E - m) - log2f(s)) * 0.6931471805599453f;
+  __syncthreads();  // the target logit is read before anyone overwrites it
+  const float k = scale / s;
+  for (int c = tid * 4; c < Vp; c += 512 * 4) {  // Vp is a multiple of 4
+    float4 g = *reinterpret_cast<const float4 *>(row + c);
+    g.x = c + 0 < V ? exp2f(g.x * L2E - m) * k - (c + 0 == tgt ? scale : 0.f) : 0.f;
+    g.y = c + 1 < V ? exp2f(g.y * L2E - m) * k - (c + 1 == tgt ? scale : 0.f) : 0.f;
+    g.z = c + 2 < V ? exp2f(g.z * L2E - m) * k - (c + 2 == tgt ? scale : 0.f) : 0.f;
+    g.w = c + 3 < V ? exp2f(g.w * L2E - m) * k - (c + 3 == tgt ? scale : 0.f) : 0.f;
     *reinterpret_cast<float4 *>(row + c) = g;
   }
 }
@@ -575,7 +634,10 @@ int gelu_backward(float *g, const float *pre, long long n, cudaStream_t s) {
 }
 int softmax_xent(float *logits, float *losses, const int *targets, int M, int V, int Vp, cudaStream_t s) {
   const size_t row_bytes = (size_t)V * sizeof(float);
-  if (row_bytes <= 220 * 1024) {
+  static const bool staged = [] { const char *e = getenv("GPT2_SOFTMAX_XENT"); return e && !strcmp(e, "staged"); }();
+  if (!staged && (Vp & 3) == 0) {
+    softmax_xent_online_kernel<<<M, 512, 0, s>>>(logits, losses, targets, V, Vp, 1.f / (float)M);
+  } else if (row_bytes <= 220 * 1024) {
     // per device and cheap: set every time rather than tracking which devices have seen it
     if (cudaFuncSetAttribute(softmax_xent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) !=
         cudaSuccess)
