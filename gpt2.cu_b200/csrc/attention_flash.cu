@@ -14,9 +14,12 @@
 // All three are "score MMAs into TMEM -> 128 threads turn a TMEM row into a K-major shared-memory
 // tile (written in the 128-byte swizzle the tensor core expects) -> accumulate MMAs", so they share
 // one skeleton: warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
-// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs, warps 2-5 do the row work.
+// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs, warps 2-5 (2-9 in the backward
+// modes) do the row work.
 // The score accumulators are double-buffered in TMEM, so the score MMAs of block t+1 run while the
-// row work of block t is in progress.
+// row work of block t is in progress; BWD_Q also double-buffers its operand stages and the tile it
+// writes, FWD instead runs two CTAs per SM, and the backward modes split a step's columns between two
+// sets of row-work warps.
 //
 // Operands are fp32 read as TF32 by the tensor core; P and dS are rounded to TF32 (to nearest) before
 // they are stored, so the second contraction carries no truncation bias. The reference computes the
@@ -37,14 +40,10 @@ namespace {
 
 constexpr int FHS = 64;        // head size
 constexpr int FROWS = 128;     // rows per CTA (TMEM lanes)
-constexpr int FCOLS = 64;      // columns per step
-constexpr int F_THREADS = 192; // warp 0 producer, warp 1 MMA, warps 2-5 row work
 
 enum { F_FWD = 0, F_BWD_Q = 1, F_BWD_KV = 2 };
 
 constexpr int TILE_A = FROWS * FHS * 4;   // 32 KiB: [128][64] K-major, two 16 KiB k-blocks
-constexpr int TILE_B = FCOLS * FHS * 4;   // 16 KiB: [64][64]  K-major (two 8 KiB k-blocks) or MN-major
-constexpr int TILE_P = FROWS * FCOLS * 4; // 32 KiB: [128][64] K-major, written by the row-work warps
 
 struct FlashMaps {
   // K-major views [T rows][64] of one head (box 32 x 64) and MN-major views (box 32 x 32 x 2 chunks)
@@ -64,25 +63,38 @@ struct FlashArgs {
 };
 
 struct FlashCtrl {
-  unsigned long long fixed_full, sc_full, sc_empty, ac_full, ac_empty, s_full[2], p_ready, acc_done;
+  unsigned long long fixed_full, sc_full[2], sc_empty[2], ac_full[2], ac_empty[2], s_full[2], p_ready, acc_done[2];
   uint32_t tmem_base;
   int abort;
 };
 
 template <int MODE>
 struct Cfg {
+  static constexpr int FC = 64;                         // columns per step
   static constexpr int NA = MODE == F_FWD ? 1 : 2;      // fixed A tiles; also score MMAs per step
   static constexpr int NP = MODE == F_BWD_KV ? 2 : 1;   // tiles the row work writes; also accumulators
+  // operand stages per step and buffers per written tile: BWD_Q has the shared memory to double both;
+  // FWD runs two CTAs per SM instead (they hide each other's latencies); BWD_KV has room for neither
+  // (measured with 32-wide steps and double buffers: 310 us against 292 us per layer at B=16, T=1024)
+  static constexpr int NST = MODE == F_BWD_Q ? 2 : 1;
+  static constexpr int NPB = MODE == F_BWD_Q ? 2 : 1;
+  // sets of four row-work warps; the backward modes split a step's columns between two sets (one
+  // CTA per SM there: a single warp per scheduler cannot hide its own latencies)
+  static constexpr int NCW = MODE == F_FWD ? 1 : 2;
+  static constexpr int MINB = MODE == F_FWD ? 2 : 1;
+  static constexpr int THREADS = 64 + 128 * NCW;
+  static constexpr int TILE_B = FC * FHS * 4;           // [FC][64] K-major (two k-blocks) or MN-major (FC/32 k-blocks)
+  static constexpr int TILE_P = FROWS * FC * 4;         // [128][FC] K-major: FC/32 k-blocks of 16 KiB
   static constexpr int OFF_A = 0;
-  static constexpr int OFF_SB = OFF_A + NA * TILE_A;    // score-stage B operands (K-major)
-  static constexpr int OFF_AB = OFF_SB + NA * TILE_B;   // accumulate-stage B operands (MN-major)
-  static constexpr int OFF_P = OFF_AB + NP * TILE_B;
-  static constexpr int OFF_VEC = OFF_P + NP * TILE_P;   // BWD_KV: lse and delta of the step's 64 queries
-  static constexpr int OFF_CTRL = OFF_VEC + 4 * 2 * 128 * 4;  // per row-work warp, two buffers
-  static constexpr int SMEM = 1024 + OFF_CTRL + 128;
-  static constexpr int TMEM_COLS = MODE == F_FWD ? 256 : 512;
-  // TMEM columns: score buffers first (2 x NA x 64), then the accumulators
-  static constexpr int COL_ACC = 2 * NA * FCOLS;
+  static constexpr int OFF_SB = OFF_A + NA * TILE_A;          // score-stage B operands (K-major)
+  static constexpr int OFF_AB = OFF_SB + NST * NA * TILE_B;   // accumulate-stage B operands (MN-major)
+  static constexpr int OFF_P = OFF_AB + NST * NP * TILE_B;
+  static constexpr int OFF_VEC = OFF_P + NP * NPB * TILE_P;   // BWD_KV: lse and delta of the step's queries
+  static constexpr int OFF_CTRL = OFF_VEC + (MODE == F_BWD_KV ? 8 * 2 * 64 * 4 : 0);  // per row-work warp, two buffers of 64 floats
+  static constexpr int SMEM = 1024 + OFF_CTRL + 256;
+  // TMEM columns: score buffers first (2 x NA x FC), then the accumulators (NP x 64)
+  static constexpr int COL_ACC = 2 * NA * FC;
+  static constexpr int TMEM_COLS = COL_ACC + NP * FHS <= 256 ? 256 : 512;
 };
 
 __device__ __forceinline__ bool f_wait(uint32_t bar, uint32_t parity, FlashCtrl *ctrl, const FlashArgs &a, int site) {
@@ -122,33 +134,57 @@ __device__ __forceinline__ float f_tf32(float x) {
   return __uint_as_float(r);
 }
 
-// this thread's row (0..127) of a [128][64] K-major tile: 16 float4 chunks in the 128-byte swizzle
-__device__ __forceinline__ void store_row(uint32_t tile, int r, const float (&v)[FCOLS]) {
+// this thread's row (0..127) of a [128][FC] K-major tile: FC/4 float4 chunks in the 128-byte swizzle
+template <int FC>
+__device__ __forceinline__ void store_row(uint32_t tile, int r, const float (&v)[FC]) {
   const uint32_t row = tile + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
 #pragma unroll
-  for (int kb = 0; kb < 2; ++kb)
+  for (int kb = 0; kb < FC / 32; ++kb)
 #pragma unroll
     for (int q = 0; q < 8; ++q)
       st_shared_v4(row + kb * 16384 + ((q ^ (r & 7)) << 4), v[kb * 32 + q * 4], v[kb * 32 + q * 4 + 1],
                    v[kb * 32 + q * 4 + 2], v[kb * 32 + q * 4 + 3]);
 }
 
-__device__ __forceinline__ void load_cols64(uint32_t taddr, float (&v)[FCOLS]) {
-  uint32_t r0[32], r1[32];
-  tmem_ld_32x32(taddr, r0);
-  tmem_ld_32x32(taddr + 32, r1);
+// FC consecutive TMEM columns of this thread's lane (all loads in flight before the one wait)
+template <int FC>
+__device__ __forceinline__ void load_cols(uint32_t taddr, float (&v)[FC]) {
+  uint32_t r[FC / 32][32];
+#pragma unroll
+  for (int hf = 0; hf < FC / 32; ++hf) tmem_ld_32x32(taddr + hf * 32, r[hf]);
   tmem_ld_wait();
 #pragma unroll
-  for (int c = 0; c < 32; ++c) {
-    v[c] = __uint_as_float(r0[c]);
-    v[32 + c] = __uint_as_float(r1[c]);
+  for (int hf = 0; hf < FC / 32; ++hf)
+#pragma unroll
+    for (int c = 0; c < 32; ++c) v[hf * 32 + c] = __uint_as_float(r[hf][c]);
+}
+
+// two column ranges (score and its partner), one wait
+template <int FC>
+__device__ __forceinline__ void load_cols2(uint32_t t0, uint32_t t1, float (&v0)[FC], float (&v1)[FC]) {
+  uint32_t r0[FC / 32][32], r1[FC / 32][32];
+#pragma unroll
+  for (int hf = 0; hf < FC / 32; ++hf) {
+    tmem_ld_32x32(t0 + hf * 32, r0[hf]);
+    tmem_ld_32x32(t1 + hf * 32, r1[hf]);
   }
+  tmem_ld_wait();
+#pragma unroll
+  for (int hf = 0; hf < FC / 32; ++hf)
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      v0[hf * 32 + c] = __uint_as_float(r0[hf][c]);
+      v1[hf * 32 + c] = __uint_as_float(r1[hf][c]);
+    }
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(F_THREADS, 1)
+__global__ void __launch_bounds__(Cfg<MODE>::THREADS, Cfg<MODE>::MINB)  // FWD: 97 KiB, 256 TMEM columns: two CTAs per SM
 attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
   using K = Cfg<MODE>;
+  constexpr int FC = K::FC;
+  constexpr int TILE_B = K::TILE_B;
+  constexpr int TILE_P = K::TILE_P;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -167,20 +203,23 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
   const int b = bh / a.NH, h = bh % a.NH;
   const int row0 = rb * FROWS;
   // column blocks [cb0, cb1)
-  const int cb0 = MODE == F_BWD_KV ? 2 * rb : 0;
-  const int cb1 = MODE == F_BWD_KV ? a.T / FCOLS : 2 * rb + 2;
+  const int cb0 = MODE == F_BWD_KV ? row0 / FC : 0;
+  const int cb1 = MODE == F_BWD_KV ? a.T / FC : (row0 + FROWS) / FC;
   const int n_it = cb1 - cb0;
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ctrl->fixed_full), 1);
-    mbar_init(smem_u32(&ctrl->sc_full), 1);
-    mbar_init(smem_u32(&ctrl->sc_empty), 1);
-    mbar_init(smem_u32(&ctrl->ac_full), 1);
-    mbar_init(smem_u32(&ctrl->ac_empty), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctrl->sc_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->sc_empty[i]), 1);
+      mbar_init(smem_u32(&ctrl->ac_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->ac_empty[i]), 1);
+    }
     mbar_init(smem_u32(&ctrl->s_full[0]), 1);
     mbar_init(smem_u32(&ctrl->s_full[1]), 1);
-    mbar_init(smem_u32(&ctrl->p_ready), 128);
-    mbar_init(smem_u32(&ctrl->acc_done), 1);
+    mbar_init(smem_u32(&ctrl->p_ready), 128 * K::NCW);
+    mbar_init(smem_u32(&ctrl->acc_done[0]), 1);
+    mbar_init(smem_u32(&ctrl->acc_done[1]), 1);
     ctrl->abort = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -217,37 +256,39 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
-          for (int half = 0; half < 2; ++half)
-            tma_load_4d(base + K::OFF_A + x * TILE_A + kb * 16384 + half * 8192, m, bar, kb * 32, row0 + half * 64, h, b);
+          for (int piece = 0; piece < FROWS / FC; ++piece)
+            tma_load_4d(base + K::OFF_A + x * TILE_A + kb * 16384 + piece * FC * 128, m, bar, kb * 32, row0 + piece * FC,
+                        h, b);
       }
       bool ok = true;
       for (int it = 0; it < n_it && ok; ++it) {
-        const int c0 = (cb0 + it) * FCOLS;
-        const uint32_t par = (uint32_t)(it & 1);
-        ok = f_wait(smem_u32(&ctrl->sc_empty), par ^ 1u, ctrl, a, 1);
+        const int c0 = (cb0 + it) * FC;
+        const int st = it % K::NST;
+        const uint32_t par = (uint32_t)((it / K::NST) & 1);
+        ok = f_wait(smem_u32(&ctrl->sc_empty[st]), par ^ 1u, ctrl, a, 1);
         if (!ok) break;
         {
-          const uint32_t sb = smem_u32(&ctrl->sc_full);
+          const uint32_t sb = smem_u32(&ctrl->sc_full[st]);
           mbar_arrive_expect_tx(sb, K::NA * TILE_B);
 #pragma unroll
           for (int x = 0; x < K::NA; ++x) {
             const CUtensorMap *m = &maps.k_major[x == 0 ? SB0 : SB1];
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb)
-              tma_load_4d(base + K::OFF_SB + x * TILE_B + kb * 8192, m, sb, kb * 32, c0, h, b);
+              tma_load_4d(base + K::OFF_SB + (st * K::NA + x) * TILE_B + kb * FC * 128, m, sb, kb * 32, c0, h, b);
           }
         }
-        ok = f_wait(smem_u32(&ctrl->ac_empty), par ^ 1u, ctrl, a, 2);
+        ok = f_wait(smem_u32(&ctrl->ac_empty[st]), par ^ 1u, ctrl, a, 2);
         if (!ok) break;
         {
-          const uint32_t ab = smem_u32(&ctrl->ac_full);
+          const uint32_t ab = smem_u32(&ctrl->ac_full[st]);
           mbar_arrive_expect_tx(ab, K::NP * TILE_B);
 #pragma unroll
           for (int y = 0; y < K::NP; ++y) {
             const CUtensorMap *m = &maps.mn_major[y == 0 ? AB0 : AB1];
 #pragma unroll
-            for (int kb = 0; kb < 2; ++kb)
-              tma_load_5d(base + K::OFF_AB + y * TILE_B + kb * 8192, m, ab, 0, c0 + kb * 32, 0, h, b);
+            for (int kb = 0; kb < FC / 32; ++kb)
+              tma_load_5d(base + K::OFF_AB + (st * K::NP + y) * TILE_B + kb * 8192, m, ab, 0, c0 + kb * 32, 0, h, b);
           }
         }
       }
@@ -257,28 +298,29 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
     if (lane == 0) {
       const uint64_t hiK = smem_desc_hi(16, 1024, 2);     // K-major, 128-byte swizzle
       const uint64_t hiMN = smem_desc_hi(4096, 512, 1);   // MN-major, 32-byte swizzle atoms
-      const uint32_t idesc_sc = make_idesc_tf32(FROWS, FCOLS, 0, 0);
+      const uint32_t idesc_sc = make_idesc_tf32(FROWS, FC, 0, 0);
       const uint32_t idesc_ac = make_idesc_tf32(FROWS, FHS, 0, 1);
       bool ok = f_wait(smem_u32(&ctrl->fixed_full), 0, ctrl, a, 3);
       tc_fence_after();
       // score MMAs of step k into TMEM buffer k & 1
       auto issue_score = [&](int k) -> bool {
-        if (!f_wait(smem_u32(&ctrl->sc_full), (uint32_t)(k & 1), ctrl, a, 4)) return false;
+        const int st = k % K::NST;
+        if (!f_wait(smem_u32(&ctrl->sc_full[st]), (uint32_t)((k / K::NST) & 1), ctrl, a, 4)) return false;
         tc_fence_after();
 #pragma unroll
         for (int x = 0; x < K::NA; ++x) {
-          const uint32_t d = tmem + (uint32_t)((k & 1) * K::NA + x) * FCOLS;
+          const uint32_t d = tmem + (uint32_t)((k & 1) * K::NA + x) * FC;
           const uint32_t a_addr = base + K::OFF_A + x * TILE_A;
-          const uint32_t b_addr = base + K::OFF_SB + x * TILE_B;
+          const uint32_t b_addr = base + K::OFF_SB + (st * K::NA + x) * TILE_B;
 #pragma unroll
           for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              mma_tf32(d, smem_desc(hiK, a_addr + kb * 16384 + ks * 32), smem_desc(hiK, b_addr + kb * 8192 + ks * 32),
+              mma_tf32(d, smem_desc(hiK, a_addr + kb * 16384 + ks * 32), smem_desc(hiK, b_addr + kb * FC * 128 + ks * 32),
                        idesc_sc, (kb | ks) ? 1u : 0u);
         }
         mma_commit(smem_u32(&ctrl->s_full[k & 1]));
-        mma_commit(smem_u32(&ctrl->sc_empty));
+        mma_commit(smem_u32(&ctrl->sc_empty[st]));
         return true;
       };
       if (ok && n_it > 0) ok = issue_score(0);
@@ -287,16 +329,17 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         if (!ok) break;
         ok = f_wait(smem_u32(&ctrl->p_ready), (uint32_t)(it & 1), ctrl, a, 5);
         if (!ok) break;
-        ok = f_wait(smem_u32(&ctrl->ac_full), (uint32_t)(it & 1), ctrl, a, 6);
+        const int st = it % K::NST;
+        ok = f_wait(smem_u32(&ctrl->ac_full[st]), (uint32_t)((it / K::NST) & 1), ctrl, a, 6);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int y = 0; y < K::NP; ++y) {
           const uint32_t d = tmem + K::COL_ACC + y * FHS;
-          const uint32_t a_addr = base + K::OFF_P + y * TILE_P;
-          const uint32_t b_addr = base + K::OFF_AB + y * TILE_B;
+          const uint32_t a_addr = base + K::OFF_P + (y * K::NPB + (it % K::NPB)) * TILE_P;
+          const uint32_t b_addr = base + K::OFF_AB + (st * K::NP + y) * TILE_B;
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb)
+          for (int kb = 0; kb < FC / 32; ++kb)
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
               // FWD reads every step's product on its own (the rescaling happens in registers)
@@ -305,13 +348,14 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
                        smem_desc(hiMN, b_addr + kb * 8192 + ks * 1024), idesc_ac, acc);
             }
         }
-        mma_commit(smem_u32(&ctrl->acc_done));
-        mma_commit(smem_u32(&ctrl->ac_empty));
+        mma_commit(smem_u32(&ctrl->acc_done[it & 1]));
+        mma_commit(smem_u32(&ctrl->ac_empty[st]));
       }
     }
   } else {
     // =============================== row work ===============================
     const int q4 = warp & 3;                  // TMEM lane quarter of this warp
+    const int cset = (warp - 2) >> 2;         // which set of four row-work warps
     const int r = q4 * 32 + lane;             // row inside the block
     const int grow = row0 + r;                // position in the sequence
     const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
@@ -328,20 +372,23 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 7, lane);
         if (!ok) break;
         tc_fence_after();
-        float s[FCOLS];
-        load_cols64(tlane + (uint32_t)(it & 1) * FCOLS, s);
-        const int c0 = (cb0 + it) * FCOLS;
-        float mx = m_run;
+        float s[FC];
+        load_cols(tlane + (uint32_t)(it & 1) * FC, s);
+        const int c0 = (cb0 + it) * FC;
+        // raw scores: max first (scale > 0 commutes with max), then p = 2^(s * scale - max) in one FMA
+        if (c0 + FC - 1 > row0) {  // the block reaches past the diagonal for some row: mask
 #pragma unroll
-        for (int c = 0; c < FCOLS; ++c) {
-          s[c] = (c0 + c > grow) ? -INFINITY : s[c] * cs;
-          mx = fmaxf(mx, s[c]);
+          for (int c = 0; c < FC; ++c) s[c] = (c0 + c > grow) ? -INFINITY : s[c];
         }
+        float mraw = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < FC; ++c) mraw = fmaxf(mraw, s[c]);
+        const float mx = fmaxf(m_run, mraw * cs);
         const float alpha = ex2(m_run - mx);  // first step: 2^(-inf) = 0; mx is finite from step 0 on (key 0 <= any query)
         float sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < FCOLS; ++c) {
-          s[c] = f_tf32(ex2(s[c] - mx));
+        for (int c = 0; c < FC; ++c) {
+          s[c] = f_tf32(ex2(fmaf(s[c], cs, -mx)));
           sum += s[c];
         }
         l_run = l_run * alpha + sum;
@@ -349,13 +396,17 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         if (it > 0) {
           // the previous product is complete: fold it in (it was formed with the previous maximum),
           // and its operands in shared memory are free again
-          ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((it - 1) & 1), ctrl, a, 8, lane);
+          ok = w_wait(smem_u32(&ctrl->acc_done[(it - 1) & 1]), (uint32_t)(((it - 1) >> 1) & 1), ctrl, a, 8, lane);
           if (!ok) break;
           tc_fence_after();
-          float pv[FHS];
-          load_cols64(tlane + K::COL_ACC, pv);
 #pragma unroll
-          for (int c = 0; c < FHS; ++c) o[c] = o[c] * alpha_prev + pv[c];
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t pv[32];
+            tmem_ld_32x32(tlane + K::COL_ACC + hf * 32, pv);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[hf * 32 + c] = o[hf * 32 + c] * alpha_prev + __uint_as_float(pv[c]);
+          }
         }
         alpha_prev = alpha;
         store_row(base + K::OFF_P, r, s);
@@ -364,11 +415,11 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
       if (ok && n_it > 0) {
-        ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((n_it - 1) & 1), ctrl, a, 9, lane);
+        ok = w_wait(smem_u32(&ctrl->acc_done[(n_it - 1) & 1]), (uint32_t)(((n_it - 1) >> 1) & 1), ctrl, a, 9, lane);
         if (ok) {
           tc_fence_after();
           float pv[FHS];
-          load_cols64(tlane + K::COL_ACC, pv);
+          load_cols(tlane + K::COL_ACC, pv);
           const float inv = 1.f / l_run;
           float *dst = a.out + ((long long)b * a.T + grow) * a.C + h * FHS;
 #pragma unroll
@@ -380,89 +431,113 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         }
       }
     } else if (MODE == F_BWD_Q) {
+      // two warp sets share the rows: set k handles columns [32k, 32k + 32) of every step, which is
+      // k-block k of the dS tile, and columns [32k, 32k + 32) of dQ at the end
+      constexpr int HC = FC / K::NCW;
+      static_assert(MODE != F_BWD_Q || HC == 32, "a warp set writes one 32-column k-block");
       const float lse = a.lse[vbase + grow];
-      const float dlt = a.delta[vbase + grow];
+      const float dlt8 = a.delta[vbase + grow] * 0.125f;
       for (int it = 0; it < n_it && ok; ++it) {
         ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 10, lane);
         if (!ok) break;
         tc_fence_after();
-        float s[FCOLS], dp[FCOLS];
-        load_cols64(tlane + (uint32_t)((it & 1) * 2) * FCOLS, s);
-        load_cols64(tlane + (uint32_t)((it & 1) * 2 + 1) * FCOLS, dp);
-        const int c0 = (cb0 + it) * FCOLS;
+        float s[HC], dp[HC];
+        load_cols2(tlane + (uint32_t)((it & 1) * 2) * FC + cset * HC, tlane + (uint32_t)((it & 1) * 2 + 1) * FC + cset * HC,
+                   s, dp);
+        const int c0 = (cb0 + it) * FC + cset * HC;
+        if (c0 + HC - 1 > row0) {  // the block reaches past the diagonal for some row: mask
 #pragma unroll
-        for (int c = 0; c < FCOLS; ++c) {
-          const float p = (c0 + c > grow) ? 0.f : ex2(s[c] * cs - lse);
-          s[c] = f_tf32(p * (dp[c] - dlt) * 0.125f);
+          for (int c = 0; c < HC; ++c) {
+            const float p = (c0 + c > grow) ? 0.f : ex2(fmaf(s[c], cs, -lse));
+            s[c] = f_tf32(p * fmaf(dp[c], 0.125f, -dlt8));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < HC; ++c) s[c] = f_tf32(ex2(fmaf(s[c], cs, -lse)) * fmaf(dp[c], 0.125f, -dlt8));
         }
-        if (it > 0) {
-          ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((it - 1) & 1), ctrl, a, 11, lane);
+        if (it >= K::NPB) {  // the tile buffer was last read by the accumulate MMAs of step it - NPB
+          const int j = it - K::NPB;
+          ok = w_wait(smem_u32(&ctrl->acc_done[j & 1]), (uint32_t)((j >> 1) & 1), ctrl, a, 11, lane);
           if (!ok) break;
         }
-        store_row(base + K::OFF_P, r, s);
+        store_row(base + K::OFF_P + (it % K::NPB) * TILE_P + cset * 16384, r, s);
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
       if (ok && n_it > 0) {
-        ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((n_it - 1) & 1), ctrl, a, 12, lane);
+        ok = w_wait(smem_u32(&ctrl->acc_done[(n_it - 1) & 1]), (uint32_t)(((n_it - 1) >> 1) & 1), ctrl, a, 12, lane);
         if (ok) {
           tc_fence_after();
-          float dq[FHS];
-          load_cols64(tlane + K::COL_ACC, dq);
-          float *dst = a.dqkv + ((long long)b * a.T + grow) * 3 * a.C + h * FHS;
+          float dq[HC];
+          load_cols(tlane + K::COL_ACC + cset * HC, dq);
+          float *dst = a.dqkv + ((long long)b * a.T + grow) * 3 * a.C + h * FHS + cset * HC;
 #pragma unroll
-          for (int c = 0; c < FHS; c += 4)
+          for (int c = 0; c < HC; c += 4)
             *reinterpret_cast<float4 *>(dst + c) = make_float4(dq[c], dq[c + 1], dq[c + 2], dq[c + 3]);
         }
       }
     } else {
+      constexpr int HC = FC / K::NCW;
+      static_assert(MODE != F_BWD_KV || HC == 32, "a warp set writes one 32-column k-block");
+      // lse and delta of the warp's 32 queries of a step are fetched one step ahead (their latency would
+      // otherwise sit at the head of every step) and shared through a per-warp copy in shared memory,
+      // double-buffered by step parity: only warp-level synchronisation is involved
+      float nl = a.lse[vbase + cb0 * FC + cset * HC + lane];
+      float nd = a.delta[vbase + cb0 * FC + cset * HC + lane];
       for (int it = 0; it < n_it && ok; ++it) {
-        const int c0 = (cb0 + it) * FCOLS;
-        // lse and delta of the step's 64 queries: every warp keeps its own copy (double-buffered by
-        // step parity), so only warp-level synchronisation is involved
-        float *vv = vec + ((warp - 2) * 2 + (it & 1)) * 128;
-        vv[lane] = a.lse[vbase + c0 + lane];
-        vv[32 + lane] = a.lse[vbase + c0 + 32 + lane];
-        vv[64 + lane] = a.delta[vbase + c0 + lane];
-        vv[96 + lane] = a.delta[vbase + c0 + 32 + lane];
+        const int c0 = (cb0 + it) * FC + cset * HC;
+        float *vv = vec + ((warp - 2) * 2 + (it & 1)) * 64;
+        vv[lane] = nl;
+        vv[32 + lane] = nd * 0.125f;
+        if (it + 1 < n_it) {
+          nl = a.lse[vbase + c0 + FC + lane];
+          nd = a.delta[vbase + c0 + FC + lane];
+        }
         __syncwarp();
         ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 13, lane);
         if (!ok) break;
         tc_fence_after();
-        float s[FCOLS], dp[FCOLS];
-        load_cols64(tlane + (uint32_t)((it & 1) * 2) * FCOLS, s);
-        load_cols64(tlane + (uint32_t)((it & 1) * 2 + 1) * FCOLS, dp);
+        float s[HC], dp[HC];
+        load_cols2(tlane + (uint32_t)((it & 1) * 2) * FC + cset * HC, tlane + (uint32_t)((it & 1) * 2 + 1) * FC + cset * HC,
+                   s, dp);
+        if (row0 + FROWS - 1 > c0) {  // some key of the block comes after some query of the step: mask
 #pragma unroll
-        for (int c = 0; c < FCOLS; ++c) {
-          const float p = (grow > c0 + c) ? 0.f : ex2(s[c] * cs - vv[c]);  // key after the query: masked
-          s[c] = f_tf32(p);
-          dp[c] = f_tf32(p * (dp[c] - vv[64 + c]) * 0.125f);
+          for (int c = 0; c < HC; ++c) {
+            const float p = (grow > c0 + c) ? 0.f : ex2(fmaf(s[c], cs, -vv[c]));
+            s[c] = f_tf32(p);
+            dp[c] = f_tf32(p * fmaf(dp[c], 0.125f, -vv[32 + c]));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < HC; ++c) {
+            const float p = ex2(fmaf(s[c], cs, -vv[c]));
+            s[c] = f_tf32(p);
+            dp[c] = f_tf32(p * fmaf(dp[c], 0.125f, -vv[32 + c]));
+          }
         }
-        if (it > 0) {
-          ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((it - 1) & 1), ctrl, a, 14, lane);
+        if (it >= K::NPB) {
+          const int j = it - K::NPB;
+          ok = w_wait(smem_u32(&ctrl->acc_done[j & 1]), (uint32_t)((j >> 1) & 1), ctrl, a, 14, lane);
           if (!ok) break;
         }
-        store_row(base + K::OFF_P, r, s);
-        store_row(base + K::OFF_P + TILE_P, r, dp);
+        store_row(base + K::OFF_P + (it % K::NPB) * TILE_P + cset * 16384, r, s);
+        store_row(base + K::OFF_P + (K::NPB + it % K::NPB) * TILE_P + cset * 16384, r, dp);
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
       if (ok && n_it > 0) {
-        ok = w_wait(smem_u32(&ctrl->acc_done), (uint32_t)((n_it - 1) & 1), ctrl, a, 15, lane);
+        ok = w_wait(smem_u32(&ctrl->acc_done[(n_it - 1) & 1]), (uint32_t)(((n_it - 1) >> 1) & 1), ctrl, a, 15, lane);
         if (ok) {
           tc_fence_after();
+          // set 0 stores dV (accumulated with P^T), set 1 stores dK (with dS^T)
           float g[FHS];
-          float *dst = a.dqkv + ((long long)b * a.T + grow) * 3 * a.C + h * FHS;
-          load_cols64(tlane + K::COL_ACC, g);  // dV (with P^T)
+          load_cols(tlane + K::COL_ACC + cset * FHS, g);
+          float *dst = a.dqkv + ((long long)b * a.T + grow) * 3 * a.C + h * FHS + (cset == 0 ? 2 * a.C : a.C);
 #pragma unroll
           for (int c = 0; c < FHS; c += 4)
-            *reinterpret_cast<float4 *>(dst + 2 * a.C + c) = make_float4(g[c], g[c + 1], g[c + 2], g[c + 3]);
-          load_cols64(tlane + K::COL_ACC + FHS, g);  // dK (with dS^T)
-#pragma unroll
-          for (int c = 0; c < FHS; c += 4)
-            *reinterpret_cast<float4 *>(dst + a.C + c) = make_float4(g[c], g[c + 1], g[c + 2], g[c + 3]);
+            *reinterpret_cast<float4 *>(dst + c) = make_float4(g[c], g[c + 1], g[c + 2], g[c + 3]);
         }
       }
     }
@@ -491,12 +566,12 @@ int *flash_status_ptr() {
   return p;
 }
 
-int build_maps(FlashMaps *m, const float *qkv, const float *dout, int B, int T, int C, int NH) {
+int build_maps(FlashMaps *m, const float *qkv, const float *dout, int B, int T, int C, int NH, int box_rows) {
   const float *src[4] = {qkv, qkv + C, qkv + 2 * C, dout};
   const long long ld[4] = {3LL * C, 3LL * C, 3LL * C, (long long)C};
   for (int x = 0; x < 4; ++x) {
     if (!src[x]) continue;
-    int e = encode_map_batched_k(&m->k_major[x], src[x], FHS, T, ld[x], NH, FHS, B, (long long)T * ld[x], FCOLS);
+    int e = encode_map_batched_k(&m->k_major[x], src[x], FHS, T, ld[x], NH, FHS, B, (long long)T * ld[x], (uint32_t)box_rows);
     if (e) return e;
     e = encode_map_batched_mn(&m->mn_major[x], src[x], FHS, T, ld[x], NH, FHS, B, (long long)T * ld[x], 2);
     if (e) return e;
@@ -514,7 +589,7 @@ int launch(const FlashMaps &maps, const FlashArgs &args, cudaStream_t st) {
     attr_set = true;
   }
   const int grid = args.B * args.NH * (args.T / FROWS);
-  attn_flash_kernel<MODE><<<grid, F_THREADS, Cfg<MODE>::SMEM, st>>>(maps, args);
+  attn_flash_kernel<MODE><<<grid, Cfg<MODE>::THREADS, Cfg<MODE>::SMEM, st>>>(maps, args);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }
@@ -533,7 +608,7 @@ int attention_flash_status() {
 int attention_flash_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t st) {
   if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
   FlashMaps maps;
-  int e = build_maps(&maps, qkv, nullptr, B, T, C, NH);
+  int e = build_maps(&maps, qkv, nullptr, B, T, C, NH, Cfg<F_FWD>::FC);
   if (e) return e;
   FlashArgs a = {};
   a.B = B; a.T = T; a.C = C; a.NH = NH;
@@ -550,8 +625,10 @@ int attention_flash_backward(float *dqkv, float *delta, const float *dout, const
   if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
   int e = attention_row_dot(delta, dout, out, B, T, C, NH, st);
   if (e) return e;
-  FlashMaps maps;
-  e = build_maps(&maps, qkv, dout, B, T, C, NH);
+  FlashMaps maps, maps_kv;  // the two kernels step by different widths: different K-major boxes
+  e = build_maps(&maps, qkv, dout, B, T, C, NH, Cfg<F_BWD_Q>::FC);
+  if (e) return e;
+  e = build_maps(&maps_kv, qkv, dout, B, T, C, NH, Cfg<F_BWD_KV>::FC);
   if (e) return e;
   FlashArgs a = {};
   a.B = B; a.T = T; a.C = C; a.NH = NH;
@@ -559,7 +636,7 @@ int attention_flash_backward(float *dqkv, float *delta, const float *dout, const
   a.status = flash_status_ptr();
   a.wait_limit_ns = 2000000000LL;
   if (!a.status) return GPT2L_ERR_CUDA;
-  e = launch<F_BWD_KV>(maps, a, st);
+  e = launch<F_BWD_KV>(maps_kv, a, st);
   if (e) return e;
   return launch<F_BWD_Q>(maps, a, st);
 }
