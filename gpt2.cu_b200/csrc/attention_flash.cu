@@ -11,18 +11,21 @@
 //          S^T = K_j Q_i^T, dP^T = V_j dO_i^T -> P^T, dS^T -> dV += P^T dO_i, dK += dS^T Q_i
 //
 // with P = 2^(S * log2(e)/8 - lse) recomputed in the backward modes and delta = rowsum(dO o O).
-// All three are "score MMAs into TMEM -> 128 threads turn a TMEM row into a K-major shared-memory
-// tile (written in the 128-byte swizzle the tensor core expects) -> accumulate MMAs", so they share
-// one skeleton: warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
+// All three are "score MMAs into TMEM -> the row-work threads read their TMEM row, turn it into P / dS
+// and write it back over the scores (tcgen05.st) -> accumulate MMAs that take that tile as their A
+// operand straight from TMEM", so they share one skeleton; P and dS never touch shared memory (an
+// MMA's operand fetch from shared memory is what bounds these small-N products: about 105 bytes per
+// ns per SM measured, so a 128 x 64 x 8 MMA with both operands in shared memory costs ~55 ns and one
+// with A in TMEM a third of the bytes): warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
 // tensor maps, nothing is copied or transposed), warp 1 issues the MMAs, warps 2-5 (2-9 in the backward
 // modes) do the row work.
-// The score accumulators are double-buffered in TMEM, so the score MMAs of block t+1 run while the
-// row work of block t is in progress; BWD_Q also double-buffers its operand stages and the tile it
-// writes, FWD instead runs two CTAs per SM, and the backward modes split a step's columns between two
-// sets of row-work warps.
+// Score buffers rotate through three TMEM slots (the score MMAs of block t+1 run while the row work
+// of block t is in progress and the accumulate MMAs of block t-1 may still be reading their slot),
+// operand stages are double-buffered, FWD runs two CTAs per SM, and the backward modes split a step's
+// columns between two sets of row-work warps.
 //
 // Operands are fp32 read as TF32 by the tensor core; P and dS are rounded to TF32 (to nearest) before
-// they are stored, so the second contraction carries no truncation bias. The reference computes the
+// they are written back, so the second contraction carries no truncation bias. The reference computes the
 // same attention with one CTA per query row and materialised T x T tensors
 // (src/layers/attention.cu:43-363); buffers and layouts (qkv in, atty out) are the same.
 #include <cuda_runtime.h>
@@ -63,7 +66,7 @@ struct FlashArgs {
 };
 
 struct FlashCtrl {
-  unsigned long long fixed_full, sc_full[2], sc_empty[2], ac_full[2], ac_empty[2], s_full[2], p_ready, acc_done[2];
+  unsigned long long fixed_full, sc_full[2], sc_empty[2], ac_full[2], ac_empty[2], s_full[3], p_ready, acc_done[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -72,28 +75,22 @@ template <int MODE>
 struct Cfg {
   static constexpr int FC = 64;                         // columns per step
   static constexpr int NA = MODE == F_FWD ? 1 : 2;      // fixed A tiles; also score MMAs per step
-  static constexpr int NP = MODE == F_BWD_KV ? 2 : 1;   // tiles the row work writes; also accumulators
-  // operand stages per step and buffers per written tile: BWD_Q has the shared memory to double both;
-  // FWD runs two CTAs per SM instead (they hide each other's latencies); BWD_KV has room for neither
-  // (measured with 32-wide steps and double buffers: 310 us against 292 us per layer at B=16, T=1024)
-  static constexpr int NST = MODE == F_BWD_Q ? 2 : 1;
-  static constexpr int NPB = MODE == F_BWD_Q ? 2 : 1;
-  // sets of four row-work warps; the backward modes split a step's columns between two sets (one
-  // CTA per SM there: a single warp per scheduler cannot hide its own latencies)
+  static constexpr int NP = MODE == F_BWD_KV ? 2 : 1;   // accumulators (and A tiles written back per step)
+  static constexpr int NST = 2;                         // operand stages
+  static constexpr int NSB = 3;                         // score slots in TMEM
+  // sets of four row-work warps; the backward modes split a step's columns between two sets
   static constexpr int NCW = MODE == F_FWD ? 1 : 2;
-  static constexpr int MINB = MODE == F_FWD ? 2 : 1;
+  static constexpr int MINB = MODE == F_FWD ? 2 : 1;    // FWD: 97 KiB, 256 TMEM columns: two CTAs per SM
   static constexpr int THREADS = 64 + 128 * NCW;
   static constexpr int TILE_B = FC * FHS * 4;           // [FC][64] K-major (two k-blocks) or MN-major (FC/32 k-blocks)
-  static constexpr int TILE_P = FROWS * FC * 4;         // [128][FC] K-major: FC/32 k-blocks of 16 KiB
   static constexpr int OFF_A = 0;
   static constexpr int OFF_SB = OFF_A + NA * TILE_A;          // score-stage B operands (K-major)
   static constexpr int OFF_AB = OFF_SB + NST * NA * TILE_B;   // accumulate-stage B operands (MN-major)
-  static constexpr int OFF_P = OFF_AB + NST * NP * TILE_B;
-  static constexpr int OFF_VEC = OFF_P + NP * NPB * TILE_P;   // BWD_KV: lse and delta of the step's queries
+  static constexpr int OFF_VEC = OFF_AB + NST * NP * TILE_B;  // BWD_KV: lse and delta of the step's queries
   static constexpr int OFF_CTRL = OFF_VEC + (MODE == F_BWD_KV ? 8 * 2 * 64 * 4 : 0);  // per row-work warp, two buffers of 64 floats
   static constexpr int SMEM = 1024 + OFF_CTRL + 256;
-  // TMEM columns: score buffers first (2 x NA x FC), then the accumulators (NP x 64)
-  static constexpr int COL_ACC = 2 * NA * FC;
+  // TMEM columns: NSB score slots of NA x FC columns, then the accumulators (NP x 64)
+  static constexpr int COL_ACC = NSB * NA * FC;
   static constexpr int TMEM_COLS = COL_ACC + NP * FHS <= 256 ? 256 : 512;
 };
 
@@ -134,16 +131,16 @@ __device__ __forceinline__ float f_tf32(float x) {
   return __uint_as_float(r);
 }
 
-// this thread's row (0..127) of a [128][FC] K-major tile: FC/4 float4 chunks in the 128-byte swizzle
-template <int FC>
-__device__ __forceinline__ void store_row(uint32_t tile, int r, const float (&v)[FC]) {
-  const uint32_t row = tile + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+// N consecutive TMEM columns of this thread's lane, written back (the A tile of the accumulate MMAs)
+template <int N>
+__device__ __forceinline__ void store_cols(uint32_t taddr, const float (&v)[N]) {
 #pragma unroll
-  for (int kb = 0; kb < FC / 32; ++kb)
+  for (int hf = 0; hf < N / 32; ++hf) {
+    uint32_t r[32];
 #pragma unroll
-    for (int q = 0; q < 8; ++q)
-      st_shared_v4(row + kb * 16384 + ((q ^ (r & 7)) << 4), v[kb * 32 + q * 4], v[kb * 32 + q * 4 + 1],
-                   v[kb * 32 + q * 4 + 2], v[kb * 32 + q * 4 + 3]);
+    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(v[hf * 32 + c]);
+    tmem_st_32x32(taddr + hf * 32, r);
+  }
 }
 
 // FC consecutive TMEM columns of this thread's lane (all loads in flight before the one wait)
@@ -184,7 +181,6 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
   using K = Cfg<MODE>;
   constexpr int FC = K::FC;
   constexpr int TILE_B = K::TILE_B;
-  constexpr int TILE_P = K::TILE_P;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -215,8 +211,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       mbar_init(smem_u32(&ctrl->ac_full[i]), 1);
       mbar_init(smem_u32(&ctrl->ac_empty[i]), 1);
     }
-    mbar_init(smem_u32(&ctrl->s_full[0]), 1);
-    mbar_init(smem_u32(&ctrl->s_full[1]), 1);
+    for (int i = 0; i < K::NSB; ++i) mbar_init(smem_u32(&ctrl->s_full[i]), 1);
     mbar_init(smem_u32(&ctrl->p_ready), 128 * K::NCW);
     mbar_init(smem_u32(&ctrl->acc_done[0]), 1);
     mbar_init(smem_u32(&ctrl->acc_done[1]), 1);
@@ -295,6 +290,8 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
+    // One lane does everything, waits included. (A variant in which the whole warp ran the control
+    // flow and built the descriptors, with one lane only issuing, was 10-20 % slower.)
     if (lane == 0) {
       const uint64_t hiK = smem_desc_hi(16, 1024, 2);     // K-major, 128-byte swizzle
       const uint64_t hiMN = smem_desc_hi(4096, 512, 1);   // MN-major, 32-byte swizzle atoms
@@ -302,14 +299,19 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       const uint32_t idesc_ac = make_idesc_tf32(FROWS, FHS, 0, 1);
       bool ok = f_wait(smem_u32(&ctrl->fixed_full), 0, ctrl, a, 3);
       tc_fence_after();
-      // score MMAs of step k into TMEM buffer k & 1
+      // score MMAs of step k into TMEM slot k % NSB
       auto issue_score = [&](int k) -> bool {
         const int st = k % K::NST;
         if (!f_wait(smem_u32(&ctrl->sc_full[st]), (uint32_t)((k / K::NST) & 1), ctrl, a, 4)) return false;
+        if (k >= K::NSB) {
+          // the slot still holds the A tile of step k - NSB: its accumulate MMAs must have retired
+          const int j = k - K::NSB;
+          if (!f_wait(smem_u32(&ctrl->acc_done[j & 1]), (uint32_t)((j >> 1) & 1), ctrl, a, 16)) return false;
+        }
         tc_fence_after();
 #pragma unroll
         for (int x = 0; x < K::NA; ++x) {
-          const uint32_t d = tmem + (uint32_t)((k & 1) * K::NA + x) * FC;
+          const uint32_t d = tmem + (uint32_t)((k % K::NSB) * K::NA + x) * FC;
           const uint32_t a_addr = base + K::OFF_A + x * TILE_A;
           const uint32_t b_addr = base + K::OFF_SB + (st * K::NA + x) * TILE_B;
 #pragma unroll
@@ -319,7 +321,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
               mma_tf32(d, smem_desc(hiK, a_addr + kb * 16384 + ks * 32), smem_desc(hiK, b_addr + kb * FC * 128 + ks * 32),
                        idesc_sc, (kb | ks) ? 1u : 0u);
         }
-        mma_commit(smem_u32(&ctrl->s_full[k & 1]));
+        mma_commit(smem_u32(&ctrl->s_full[k % K::NSB]));
         mma_commit(smem_u32(&ctrl->sc_empty[st]));
         return true;
       };
@@ -336,7 +338,10 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
 #pragma unroll
         for (int y = 0; y < K::NP; ++y) {
           const uint32_t d = tmem + K::COL_ACC + y * FHS;
-          const uint32_t a_addr = base + K::OFF_P + (y * K::NPB + (it % K::NPB)) * TILE_P;
+          // the A tile sits where the row work wrote it back: over S (FWD), over dP (BWD_Q), over
+          // S^T for dV and over dP^T for dK (BWD_KV)
+          const int slot_x = MODE == F_FWD ? 0 : (MODE == F_BWD_Q ? 1 : y);
+          const uint32_t a_tmem = tmem + (uint32_t)((it % K::NSB) * K::NA + slot_x) * FC;
           const uint32_t b_addr = base + K::OFF_AB + (st * K::NP + y) * TILE_B;
 #pragma unroll
           for (int kb = 0; kb < FC / 32; ++kb)
@@ -344,8 +349,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
             for (int ks = 0; ks < 4; ++ks) {
               // FWD reads every step's product on its own (the rescaling happens in registers)
               const uint32_t acc = (MODE == F_FWD ? 0u : (it > 0 ? 1u : 0u)) | ((kb | ks) ? 1u : 0u);
-              mma_tf32(d, smem_desc(hiK, a_addr + kb * 16384 + ks * 32),
-                       smem_desc(hiMN, b_addr + kb * 8192 + ks * 1024), idesc_ac, acc);
+              mma_tf32_tmem_a(d, a_tmem + kb * 32 + ks * 8, smem_desc(hiMN, b_addr + kb * 8192 + ks * 1024), idesc_ac, acc);
             }
         }
         mma_commit(smem_u32(&ctrl->acc_done[it & 1]));
@@ -369,11 +373,12 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       for (int c = 0; c < FHS; ++c) o[c] = 0.f;
       float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
       for (int it = 0; it < n_it && ok; ++it) {
-        ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 7, lane);
+        ok = w_wait(smem_u32(&ctrl->s_full[it % K::NSB]), (uint32_t)((it / K::NSB) & 1), ctrl, a, 7, lane);
         if (!ok) break;
         tc_fence_after();
         float s[FC];
-        load_cols(tlane + (uint32_t)(it & 1) * FC, s);
+        const uint32_t slot = tlane + (uint32_t)((it % K::NSB) * K::NA) * FC;
+        load_cols(slot, s);
         const int c0 = (cb0 + it) * FC;
         // raw scores: max first (scale > 0 commutes with max), then p = 2^(s * scale - max) in one FMA
         if (c0 + FC - 1 > row0) {  // the block reaches past the diagonal for some row: mask
@@ -409,8 +414,8 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
           }
         }
         alpha_prev = alpha;
-        store_row(base + K::OFF_P, r, s);
-        fence_proxy_async_smem();
+        store_cols(slot, s);  // P over S: the A tile of this step's P.V
+        tmem_st_wait();
         tc_fence_before();
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
@@ -438,12 +443,12 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       const float lse = a.lse[vbase + grow];
       const float dlt8 = a.delta[vbase + grow] * 0.125f;
       for (int it = 0; it < n_it && ok; ++it) {
-        ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 10, lane);
+        ok = w_wait(smem_u32(&ctrl->s_full[it % K::NSB]), (uint32_t)((it / K::NSB) & 1), ctrl, a, 10, lane);
         if (!ok) break;
         tc_fence_after();
         float s[HC], dp[HC];
-        load_cols2(tlane + (uint32_t)((it & 1) * 2) * FC + cset * HC, tlane + (uint32_t)((it & 1) * 2 + 1) * FC + cset * HC,
-                   s, dp);
+        const uint32_t slot = tlane + (uint32_t)((it % K::NSB) * K::NA) * FC + cset * HC;
+        load_cols2(slot, slot + FC, s, dp);
         const int c0 = (cb0 + it) * FC + cset * HC;
         if (c0 + HC - 1 > row0) {  // the block reaches past the diagonal for some row: mask
 #pragma unroll
@@ -455,13 +460,8 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
 #pragma unroll
           for (int c = 0; c < HC; ++c) s[c] = f_tf32(ex2(fmaf(s[c], cs, -lse)) * fmaf(dp[c], 0.125f, -dlt8));
         }
-        if (it >= K::NPB) {  // the tile buffer was last read by the accumulate MMAs of step it - NPB
-          const int j = it - K::NPB;
-          ok = w_wait(smem_u32(&ctrl->acc_done[j & 1]), (uint32_t)((j >> 1) & 1), ctrl, a, 11, lane);
-          if (!ok) break;
-        }
-        store_row(base + K::OFF_P + (it % K::NPB) * TILE_P + cset * 16384, r, s);
-        fence_proxy_async_smem();
+        store_cols(slot + FC, s);  // dS over dP: the A tile of this step's dS.K
+        tmem_st_wait();
         tc_fence_before();
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
@@ -495,12 +495,12 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
           nd = a.delta[vbase + c0 + FC + lane];
         }
         __syncwarp();
-        ok = w_wait(smem_u32(&ctrl->s_full[it & 1]), (uint32_t)((it >> 1) & 1), ctrl, a, 13, lane);
+        ok = w_wait(smem_u32(&ctrl->s_full[it % K::NSB]), (uint32_t)((it / K::NSB) & 1), ctrl, a, 13, lane);
         if (!ok) break;
         tc_fence_after();
         float s[HC], dp[HC];
-        load_cols2(tlane + (uint32_t)((it & 1) * 2) * FC + cset * HC, tlane + (uint32_t)((it & 1) * 2 + 1) * FC + cset * HC,
-                   s, dp);
+        const uint32_t slot = tlane + (uint32_t)((it % K::NSB) * K::NA) * FC + cset * HC;
+        load_cols2(slot, slot + FC, s, dp);
         if (row0 + FROWS - 1 > c0) {  // some key of the block comes after some query of the step: mask
 #pragma unroll
           for (int c = 0; c < HC; ++c) {
@@ -516,14 +516,9 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
             dp[c] = f_tf32(p * fmaf(dp[c], 0.125f, -vv[32 + c]));
           }
         }
-        if (it >= K::NPB) {
-          const int j = it - K::NPB;
-          ok = w_wait(smem_u32(&ctrl->acc_done[j & 1]), (uint32_t)((j >> 1) & 1), ctrl, a, 14, lane);
-          if (!ok) break;
-        }
-        store_row(base + K::OFF_P + (it % K::NPB) * TILE_P + cset * 16384, r, s);
-        store_row(base + K::OFF_P + (K::NPB + it % K::NPB) * TILE_P + cset * 16384, r, dp);
-        fence_proxy_async_smem();
+        store_cols(slot, s);        // P^T over S^T: A tile of dV += P^T dO
+        store_cols(slot + FC, dp);  // dS^T over dP^T: A tile of dK += dS^T Q
+        tmem_st_wait();
         tc_fence_before();
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
