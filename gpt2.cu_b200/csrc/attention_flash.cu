@@ -17,8 +17,8 @@
 // MMA's operand fetch from shared memory is what bounds these small-N products: about 105 bytes per
 // ns per SM measured, so a 128 x 64 x 8 MMA with both operands in shared memory costs ~55 ns and one
 // with A in TMEM a third of the bytes): warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
-// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs, warps 2-5 (2-9 in the backward
-// modes) do the row work.
+// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs (the backward modes: warp 1 the
+// score MMAs, warp 2 the accumulate MMAs), the remaining 4 (backward: 8) warps do the row work.
 // Score buffers rotate through three TMEM slots (the score MMAs of block t+1 run while the row work
 // of block t is in progress and the accumulate MMAs of block t-1 may still be reading their slot),
 // operand stages are double-buffered, FWD runs two CTAs per SM, and the backward modes split a step's
@@ -66,7 +66,7 @@ struct FlashArgs {
 };
 
 struct FlashCtrl {
-  unsigned long long fixed_full, sc_full[2], sc_empty[2], ac_full[2], ac_empty[2], s_full[3], p_ready, acc_done[2];
+  unsigned long long fixed_full, sc_full[2], sc_empty[2], ac_full[2], ac_empty[2], s_full[3], p_ready[3], slot_free[3], acc_done[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -81,7 +81,8 @@ struct Cfg {
   // sets of four row-work warps; the backward modes split a step's columns between two sets
   static constexpr int NCW = MODE == F_FWD ? 1 : 2;
   static constexpr int MINB = MODE == F_FWD ? 2 : 1;    // FWD: 97 KiB, 256 TMEM columns: two CTAs per SM
-  static constexpr int THREADS = 64 + 128 * NCW;
+  static constexpr int NMW = MODE == F_FWD ? 1 : 2;     // MMA-issuing warps
+  static constexpr int THREADS = 32 * (1 + NMW) + 128 * NCW;  // producer, MMA issuers, row-work warps
   static constexpr int TILE_B = FC * FHS * 4;           // [FC][64] K-major (two k-blocks) or MN-major (FC/32 k-blocks)
   static constexpr int OFF_A = 0;
   static constexpr int OFF_SB = OFF_A + NA * TILE_A;          // score-stage B operands (K-major)
@@ -211,8 +212,14 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       mbar_init(smem_u32(&ctrl->ac_full[i]), 1);
       mbar_init(smem_u32(&ctrl->ac_empty[i]), 1);
     }
-    for (int i = 0; i < K::NSB; ++i) mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-    mbar_init(smem_u32(&ctrl->p_ready), 128 * K::NCW);
+    // one barrier per TMEM score slot for each hand-over (scores ready, tile written back, tile
+    // consumed): with two independent MMA issuers a single barrier could run two phases ahead of a
+    // waiter, which a parity wait cannot tell from zero
+    for (int i = 0; i < K::NSB; ++i) {
+      mbar_init(smem_u32(&ctrl->s_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->p_ready[i]), 128 * K::NCW);
+      mbar_init(smem_u32(&ctrl->slot_free[i]), 1);
+    }
     mbar_init(smem_u32(&ctrl->acc_done[0]), 1);
     mbar_init(smem_u32(&ctrl->acc_done[1]), 1);
     ctrl->abort = 0;
@@ -288,25 +295,24 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         }
       }
     }
-  } else if (warp == 1) {
-    // =============================== MMA issuer ===============================
-    // One lane does everything, waits included. (A variant in which the whole warp ran the control
-    // flow and built the descriptors, with one lane only issuing, was 10-20 % slower.)
+  } else if (warp <= K::NMW) {
+    // =============================== MMA issuers ===============================
+    // One thread issuing all of a step's 16-32 small MMAs needs ~35-45 ns per instruction (measured
+    // with %globaltimer) and was what the row work waited for, so the backward modes use two issuing
+    // warps: warp 1 the score products, warp 2 the accumulate products. FWD (16 MMAs per step, two CTAs
+    // per SM, register-bound) keeps both in warp 1.
     if (lane == 0) {
       const uint64_t hiK = smem_desc_hi(16, 1024, 2);     // K-major, 128-byte swizzle
       const uint64_t hiMN = smem_desc_hi(4096, 512, 1);   // MN-major, 32-byte swizzle atoms
       const uint32_t idesc_sc = make_idesc_tf32(FROWS, FC, 0, 0);
       const uint32_t idesc_ac = make_idesc_tf32(FROWS, FHS, 0, 1);
-      bool ok = f_wait(smem_u32(&ctrl->fixed_full), 0, ctrl, a, 3);
-      tc_fence_after();
       // score MMAs of step k into TMEM slot k % NSB
       auto issue_score = [&](int k) -> bool {
         const int st = k % K::NST;
         if (!f_wait(smem_u32(&ctrl->sc_full[st]), (uint32_t)((k / K::NST) & 1), ctrl, a, 4)) return false;
         if (k >= K::NSB) {
           // the slot still holds the A tile of step k - NSB: its accumulate MMAs must have retired
-          const int j = k - K::NSB;
-          if (!f_wait(smem_u32(&ctrl->acc_done[j & 1]), (uint32_t)((j >> 1) & 1), ctrl, a, 16)) return false;
+          if (!f_wait(smem_u32(&ctrl->slot_free[k % K::NSB]), (uint32_t)((k / K::NSB - 1) & 1), ctrl, a, 16)) return false;
         }
         tc_fence_after();
 #pragma unroll
@@ -325,21 +331,16 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         mma_commit(smem_u32(&ctrl->sc_empty[st]));
         return true;
       };
-      if (ok && n_it > 0) ok = issue_score(0);
-      for (int it = 0; it < n_it && ok; ++it) {
-        if (it + 1 < n_it) ok = issue_score(it + 1);
-        if (!ok) break;
-        ok = f_wait(smem_u32(&ctrl->p_ready), (uint32_t)(it & 1), ctrl, a, 5);
-        if (!ok) break;
+      // accumulate MMAs of step it: A = the tile the row work wrote back into slot it % NSB
+      auto issue_acc = [&](int it) -> bool {
+        if (!f_wait(smem_u32(&ctrl->p_ready[it % K::NSB]), (uint32_t)((it / K::NSB) & 1), ctrl, a, 5)) return false;
         const int st = it % K::NST;
-        ok = f_wait(smem_u32(&ctrl->ac_full[st]), (uint32_t)((it / K::NST) & 1), ctrl, a, 6);
-        if (!ok) break;
+        if (!f_wait(smem_u32(&ctrl->ac_full[st]), (uint32_t)((it / K::NST) & 1), ctrl, a, 6)) return false;
         tc_fence_after();
 #pragma unroll
         for (int y = 0; y < K::NP; ++y) {
           const uint32_t d = tmem + K::COL_ACC + y * FHS;
-          // the A tile sits where the row work wrote it back: over S (FWD), over dP (BWD_Q), over
-          // S^T for dV and over dP^T for dK (BWD_KV)
+          // the tile sits over S (FWD), over dP (BWD_Q), over S^T for dV and over dP^T for dK (BWD_KV)
           const int slot_x = MODE == F_FWD ? 0 : (MODE == F_BWD_Q ? 1 : y);
           const uint32_t a_tmem = tmem + (uint32_t)((it % K::NSB) * K::NA + slot_x) * FC;
           const uint32_t b_addr = base + K::OFF_AB + (st * K::NP + y) * TILE_B;
@@ -354,12 +355,30 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         }
         mma_commit(smem_u32(&ctrl->acc_done[it & 1]));
         mma_commit(smem_u32(&ctrl->ac_empty[st]));
+        mma_commit(smem_u32(&ctrl->slot_free[it % K::NSB]));
+        return true;
+      };
+      bool ok = true;
+      if (warp == 1) {
+        ok = f_wait(smem_u32(&ctrl->fixed_full), 0, ctrl, a, 3);
+        tc_fence_after();
+      }
+      if (K::NMW == 1) {
+        if (ok && n_it > 0) ok = issue_score(0);
+        for (int it = 0; it < n_it && ok; ++it) {
+          if (it + 1 < n_it) ok = issue_score(it + 1);
+          if (ok) ok = issue_acc(it);
+        }
+      } else if (warp == 1) {
+        for (int k = 0; k < n_it && ok; ++k) ok = issue_score(k);
+      } else {
+        for (int it = 0; it < n_it && ok; ++it) ok = issue_acc(it);
       }
     }
   } else {
     // =============================== row work ===============================
     const int q4 = warp & 3;                  // TMEM lane quarter of this warp
-    const int cset = (warp - 2) >> 2;         // which set of four row-work warps
+    const int cset = (warp - 1 - K::NMW) >> 2;  // which set of four row-work warps
     const int r = q4 * 32 + lane;             // row inside the block
     const int grow = row0 + r;                // position in the sequence
     const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
@@ -417,7 +436,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         store_cols(slot, s);  // P over S: the A tile of this step's P.V
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(smem_u32(&ctrl->p_ready));
+        mbar_arrive(smem_u32(&ctrl->p_ready[it % K::NSB]));
       }
       if (ok && n_it > 0) {
         ok = w_wait(smem_u32(&ctrl->acc_done[(n_it - 1) & 1]), (uint32_t)(((n_it - 1) >> 1) & 1), ctrl, a, 9, lane);
@@ -463,7 +482,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         store_cols(slot + FC, s);  // dS over dP: the A tile of this step's dS.K
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(smem_u32(&ctrl->p_ready));
+        mbar_arrive(smem_u32(&ctrl->p_ready[it % K::NSB]));
       }
       if (ok && n_it > 0) {
         ok = w_wait(smem_u32(&ctrl->acc_done[(n_it - 1) & 1]), (uint32_t)(((n_it - 1) >> 1) & 1), ctrl, a, 12, lane);
@@ -487,7 +506,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       float nd = a.delta[vbase + cb0 * FC + cset * HC + lane];
       for (int it = 0; it < n_it && ok; ++it) {
         const int c0 = (cb0 + it) * FC + cset * HC;
-        float *vv = vec + ((warp - 2) * 2 + (it & 1)) * 64;
+        float *vv = vec + ((warp - 1 - K::NMW) * 2 + (it & 1)) * 64;
         vv[lane] = nl;
         vv[32 + lane] = nd * 0.125f;
         if (it + 1 < n_it) {
@@ -520,7 +539,7 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         store_cols(slot + FC, dp);  // dS^T over dP^T: A tile of dK += dS^T Q
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(smem_u32(&ctrl->p_ready));
+        mbar_arrive(smem_u32(&ctrl->p_ready[it % K::NSB]));
       }
       if (ok && n_it > 0) {
         ok = w_wait(smem_u32(&ctrl->acc_done[(n_it - 1) & 1]), (uint32_t)(((n_it - 1) >> 1) & 1), ctrl, a, 15, lane);

@@ -345,6 +345,8 @@ float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream) {
   if (cudaMemcpyAsync(m->h_losses, m->losses, (size_t)M * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess)
     return NAN;
   if (cudaStreamSynchronize(st) != cudaSuccess) return NAN;
+  // a bounded wait that gave up inside an attention kernel leaves garbage behind: report it
+  if (m->attn_flash && attention_flash_status() != 0) return NAN;
   double s = 0.0;
   for (long long i = 0; i < M; ++i) s += m->h_losses[i];
   return (float)(s / (double)M);

@@ -28,7 +28,7 @@ def rel(a, b):
 
 CASES = [
     # impl, mode, T, forward tol, backward tol
-    ("flash", 0, 128, 2e-3, 3e-3), ("flash", 0, 256, 2e-3, 3e-3), ("flash", 0, 640, 2e-3, 3e-3),
+    ("flash", 0, 128, 2e-3, 3e-3), ("flash", 0, 256, 2e-3, 3e-3), ("flash", 0, 640, 2e-3, 3e-3), ("flash", 0, 1024, 2e-3, 3e-3),
     ("gemm", 0, 256, 2e-3, 3e-3), ("gemm", 1, 160, 2e-5, 2e-5), ("gemm", 1, 256, 2e-5, 2e-5),
     ("simt", 0, 200, 2e-5, 2e-5),
 ]
