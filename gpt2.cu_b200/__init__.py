@@ -45,6 +45,8 @@ EXPORTS = [
     "gpt2_linear_forward", "gpt2_linear_backward_input", "gpt2_linear_backward_weight",
     "gpt2_linear_forward_host", "gpt2_linear_backward_input_host", "gpt2_linear_backward_weight_host",
     "gpt2_linear_backward_weight_noalloc",
+    "gpt2_linear_forward_host_async", "gpt2_linear_backward_input_host_async",
+    "gpt2_linear_backward_weight_host_async", "gpt2_linear_host_synchronize",
     "gpt2_schedule_create", "gpt2_schedule_destroy", "gpt2_schedule_validate", "gpt2_schedule_describe",
     "gpt2_megakernel_run", "gpt2_megakernel_status", "gpt2_schedule_debug_set_expected",
 ]
@@ -142,6 +144,14 @@ def _load():
         f = getattr(lib, name)
         f.argtypes = [P, P, P, P, I, I, I, I, OP, V]
         f.restype = I
+    lib.gpt2_linear_forward_host_async.argtypes = [P, P, P, P, I, I, I, I, OP]
+    lib.gpt2_linear_forward_host_async.restype = I
+    lib.gpt2_linear_backward_input_host_async.argtypes = [P, P, P, I, I, I, I, OP]
+    lib.gpt2_linear_backward_input_host_async.restype = I
+    lib.gpt2_linear_backward_weight_host_async.argtypes = [P, P, P, P, I, I, I, I, OP]
+    lib.gpt2_linear_backward_weight_host_async.restype = I
+    lib.gpt2_linear_host_synchronize.argtypes = []
+    lib.gpt2_linear_host_synchronize.restype = I
     lib.gpt2_schedule_create.argtypes = [ctypes.POINTER(Op), I, ctypes.POINTER(I)]
     lib.gpt2_schedule_create.restype = V
     lib.gpt2_schedule_destroy.argtypes = [V]
@@ -253,6 +263,25 @@ def backward_input(g_in, g_out, w, B, S, K, N, opts=None, stream=None, host=Fals
 def backward_weight(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=None, host=False):
     fn = lib.gpt2_linear_backward_weight_host if host else lib.gpt2_linear_backward_weight
     return fn(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def forward_host_async(out, x, w, b, B, S, K, N, opts=None):
+    return lib.gpt2_linear_forward_host_async(_p(out), _p(x), _p(w), _p(b), B, S, K, N,
+                                              ctypes.byref(opts) if opts else None)
+
+
+def backward_input_host_async(g_in, g_out, w, B, S, K, N, opts=None):
+    return lib.gpt2_linear_backward_input_host_async(_p(g_in), _p(g_out), _p(w), B, S, K, N,
+                                                     ctypes.byref(opts) if opts else None)
+
+
+def backward_weight_host_async(g_w, g_b, g_out, x, B, S, K, N, opts=None):
+    return lib.gpt2_linear_backward_weight_host_async(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N,
+                                                      ctypes.byref(opts) if opts else None)
+
+
+def host_synchronize():
+    return lib.gpt2_linear_host_synchronize()
 
 
 def attention_forward(out, lse, probs, qkv, B, T, NH, C, impl=ATT_FLASH, mode=MODE_TF32, stream=None):

@@ -15,6 +15,56 @@ constexpr int MAX_DEVICES = 16;
 static DeviceCtx g_ctx[MAX_DEVICES];
 static std::mutex g_mu;        // context table and the shared split-K workspace
 static std::mutex g_stage_mu;  // host-call staging buffers (held for a whole *_host call)
+
+// ---------------------------------------------------------------------------------------
+// Pipelined host-buffer calls: three streams (copy in, compute, copy out) and two sets of staging
+// buffers, so that the host->device copies of call n+1 run while call n computes and copies its
+// results out (PCIe is full duplex). A set is reused by every second call, behind the event that
+// marks its previous results as copied out.
+// ---------------------------------------------------------------------------------------
+struct HostPipe {
+  cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+  struct Set {
+    float *buf[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t bytes[4] = {0, 0, 0, 0};
+    cudaEvent_t ev_in = nullptr, ev_run = nullptr, ev_free = nullptr;
+    bool used = false;
+  } set[2];
+  unsigned long long calls = 0;
+};
+
+static void destroy_pipe(HostPipe *p) {
+  if (!p) return;
+  for (auto &s : p->set) {
+    for (float *b : s.buf)
+      if (b) cudaFree(b);
+    if (s.ev_in) cudaEventDestroy(s.ev_in);
+    if (s.ev_run) cudaEventDestroy(s.ev_run);
+    if (s.ev_free) cudaEventDestroy(s.ev_free);
+  }
+  if (p->s_in) cudaStreamDestroy(p->s_in);
+  if (p->s_run) cudaStreamDestroy(p->s_run);
+  if (p->s_out) cudaStreamDestroy(p->s_out);
+  delete p;
+}
+
+static HostPipe *get_pipe(DeviceCtx *ctx) {
+  if (ctx->pipe) return ctx->pipe;
+  HostPipe *p = new HostPipe();
+  bool ok = cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&p->s_run, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking) == cudaSuccess;
+  for (auto &s : p->set)
+    ok = ok && cudaEventCreateWithFlags(&s.ev_in, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&s.ev_run, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&s.ev_free, cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
+    destroy_pipe(p);
+    return nullptr;
+  }
+  ctx->pipe = p;
+  return p;
+}
 constexpr size_t SEM_COUNT = 1u << 20;  // split-K arrival counters (one per output tile and lane quarter)
 
 DeviceCtx *ctx_current(int *err) {
@@ -187,6 +237,7 @@ void gpt2_linear_shutdown(void) {
     if (c.xt) cudaFree(c.xt);
     for (int i = 0; i < 4; ++i)
       if (c.stage[i]) cudaFree(c.stage[i]);
+    destroy_pipe(c.pipe);
     c = DeviceCtx();
   }
   if (cur >= 0) cudaSetDevice(cur);
@@ -326,6 +377,152 @@ int gpt2_linear_backward_weight_host(float *g_w, float *g_b, const float *g_out,
                  cudaSuccess)
     return GPT2L_ERR_CUDA;
   return finish_host(ctx, st);
+}
+
+
+// ---- pipelined flavours: return once everything is enqueued; results are in the host buffers after
+// gpt2_linear_host_synchronize()
+namespace {
+struct AsyncCall {
+  HostPipe *p;
+  HostPipe::Set *s;
+};
+
+// takes the next staging set and makes the copy-in stream wait until its previous user is done
+int async_begin(DeviceCtx *ctx, AsyncCall *c) {
+  HostPipe *p = get_pipe(ctx);
+  if (!p) return GPT2L_ERR_CUDA;
+  HostPipe::Set *s = &p->set[p->calls++ & 1];
+  if (s->used && cudaStreamWaitEvent(p->s_in, s->ev_free, 0) != cudaSuccess) return GPT2L_ERR_CUDA;
+  c->p = p;
+  c->s = s;
+  return GPT2L_OK;
+}
+
+// room for `count` floats in slot `slot`; copies `host` in when given
+int async_stage(AsyncCall &c, int slot, const float *host, size_t count) {
+  HostPipe::Set *s = c.s;
+  if (count * sizeof(float) > s->bytes[slot]) {
+    // growing frees the old buffer: its last user must be done
+    if (s->used && cudaEventSynchronize(s->ev_free) != cudaSuccess) return GPT2L_ERR_CUDA;
+    int e = ensure_bytes(&s->buf[slot], &s->bytes[slot], count * sizeof(float));
+    if (e) return e;
+  }
+  if (host && cudaMemcpyAsync(s->buf[slot], host, count * sizeof(float), cudaMemcpyHostToDevice, c.p->s_in) !=
+                  cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  return GPT2L_OK;
+}
+
+int async_inputs_done(AsyncCall &c) {
+  if (cudaEventRecord(c.s->ev_in, c.p->s_in) != cudaSuccess) return GPT2L_ERR_CUDA;
+  return cudaStreamWaitEvent(c.p->s_run, c.s->ev_in, 0) == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+int async_compute_done(AsyncCall &c) {
+  if (cudaEventRecord(c.s->ev_run, c.p->s_run) != cudaSuccess) return GPT2L_ERR_CUDA;
+  return cudaStreamWaitEvent(c.p->s_out, c.s->ev_run, 0) == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+int async_out(AsyncCall &c, float *host, int slot, size_t count) {
+  return cudaMemcpyAsync(host, c.s->buf[slot], count * sizeof(float), cudaMemcpyDeviceToHost, c.p->s_out) ==
+                 cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+
+int async_end(AsyncCall &c) {
+  c.s->used = true;
+  return cudaEventRecord(c.s->ev_free, c.p->s_out) == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
+}
+}  // namespace
+
+#define AK(call)                   \
+  do {                             \
+    int _e = (call);               \
+    if (_e != GPT2L_OK) return _e; \
+  } while (0)
+
+int gpt2_linear_forward_host_async(float *out, const float *in, const float *w, const float *b, int B, int S, int K,
+                                   int N, const gpt2_linear_opts *opts) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (!out || !in || !w || B <= 0 || S <= 0 || K <= 0 || N <= 0) return GPT2L_ERR_BAD_ARG;
+  if (opts && ((opts->flags & GPT2L_EPI_GELU_DUAL) || opts->aux_op)) return GPT2L_ERR_BAD_ARG;
+  const size_t M = (size_t)B * S;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  AsyncCall c;
+  AK(async_begin(ctx, &c));
+  AK(async_stage(c, 0, in, M * K));
+  AK(async_stage(c, 1, w, (size_t)K * N));
+  AK(async_stage(c, 2, nullptr, M * N));
+  if (b) AK(async_stage(c, 3, b, (size_t)N));
+  AK(async_inputs_done(c));
+  AK(gpt2_linear_forward(c.s->buf[2], c.s->buf[0], c.s->buf[1], b ? c.s->buf[3] : nullptr, B, S, K, N, opts,
+                         c.p->s_run));
+  AK(async_compute_done(c));
+  AK(async_out(c, out, 2, M * N));
+  return async_end(c);
+}
+
+int gpt2_linear_backward_input_host_async(float *g_in, const float *g_out, const float *w, int B, int S, int K, int N,
+                                          const gpt2_linear_opts *opts) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (!g_in || !g_out || !w || B <= 0 || S <= 0 || K <= 0 || N <= 0) return GPT2L_ERR_BAD_ARG;
+  if (opts && opts->aux_op) return GPT2L_ERR_BAD_ARG;
+  const size_t M = (size_t)B * S;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  AsyncCall c;
+  AK(async_begin(ctx, &c));
+  AK(async_stage(c, 0, g_out, M * N));
+  AK(async_stage(c, 1, w, (size_t)K * N));
+  AK(async_stage(c, 2, nullptr, M * K));
+  AK(async_inputs_done(c));
+  AK(gpt2_linear_backward_input(c.s->buf[2], c.s->buf[0], c.s->buf[1], B, S, K, N, opts, c.p->s_run));
+  AK(async_compute_done(c));
+  AK(async_out(c, g_in, 2, M * K));
+  return async_end(c);
+}
+
+int gpt2_linear_backward_weight_host_async(float *g_w, float *g_b, const float *g_out, const float *in, int B, int S,
+                                           int K, int N, const gpt2_linear_opts *opts) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  if (!g_w || !g_out || !in || B <= 0 || S <= 0 || K <= 0 || N <= 0) return GPT2L_ERR_BAD_ARG;
+  const size_t M = (size_t)B * S;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  AsyncCall c;
+  AK(async_begin(ctx, &c));
+  AK(async_stage(c, 0, in, M * K));
+  AK(async_stage(c, 1, g_out, M * N));
+  AK(async_stage(c, 2, nullptr, (size_t)K * N));
+  if (g_b) AK(async_stage(c, 3, nullptr, (size_t)N));
+  AK(async_inputs_done(c));
+  AK(gpt2_linear_backward_weight(c.s->buf[2], g_b ? c.s->buf[3] : nullptr, c.s->buf[1], c.s->buf[0], B, S, K, N,
+                                 opts, c.p->s_run));
+  AK(async_compute_done(c));
+  AK(async_out(c, g_w, 2, (size_t)K * N));
+  if (g_b) AK(async_out(c, g_b, 3, (size_t)N));
+  return async_end(c);
+}
+
+int gpt2_linear_host_synchronize(void) {
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  std::lock_guard<std::mutex> lk(g_stage_mu);
+  HostPipe *p = ctx->pipe;
+  if (p) {
+    if (cudaStreamSynchronize(p->s_in) != cudaSuccess || cudaStreamSynchronize(p->s_run) != cudaSuccess ||
+        cudaStreamSynchronize(p->s_out) != cudaSuccess)
+      return GPT2L_ERR_CUDA;
+  }
+  Status s;
+  int e = read_status(ctx, &s, true);
+  if (e) return e;
+  return s.status;
 }
 
 }  // extern "C"

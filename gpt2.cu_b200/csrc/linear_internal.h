@@ -179,6 +179,7 @@ struct DeviceCtx {
   // host-call staging
   float *stage[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t stage_bytes[4] = {0, 0, 0, 0};
+  struct HostPipe *pipe = nullptr;  // streams, events and staging sets of the *_host_async calls (api.cu)
 };
 
 DeviceCtx *ctx_current(int *err);

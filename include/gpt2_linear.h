@@ -134,6 +134,26 @@ int gpt2_linear_backward_weight_host(float *g_w, float *g_b, const float *g_out,
                                      const gpt2_linear_opts *opts, gpt2l_stream_t stream);
 
 /*
+ * Pipelined host-buffer calls, for a sequence of operations on host tensors. Each call only enqueues
+ * its work — copies in on one internal stream, the kernel on a second, copies out on a third, two sets
+ * of staging buffers in rotation — and returns; the host->device copies of the next call then overlap
+ * this call's kernel and its device->host copies (PCIe carries both directions at once). Output
+ * buffers hold their results, and input buffers may be changed, only after
+ * gpt2_linear_host_synchronize(), which waits for everything enqueued on the current device and
+ * returns the device status like the *_host calls. Use pinned host memory (pageable memory makes the
+ * copies synchronous). Epilogue operands (opts->aux, GELU dual store) are device pointers and are
+ * not supported here. The reference has no host-buffer path at all.
+ */
+int gpt2_linear_forward_host_async(float *out, const float *in, const float *w, const float *b,
+                                   int B, int S, int K, int N, const gpt2_linear_opts *opts);
+int gpt2_linear_backward_input_host_async(float *g_in, const float *g_out, const float *w,
+                                          int B, int S, int K, int N, const gpt2_linear_opts *opts);
+int gpt2_linear_backward_weight_host_async(float *g_w, float *g_b, const float *g_out,
+                                           const float *in, int B, int S, int K, int N,
+                                           const gpt2_linear_opts *opts);
+int gpt2_linear_host_synchronize(void);
+
+/*
  * Weight gradient for callers that may not allocate device memory. (No counterpart in the
  * reference, which allocates everything up front and has no split-K.)
  *

@@ -246,6 +246,33 @@ def test_host_buffer_entry_points(gpu, orc):
     check_all(orc, (y, dx, dw, db), x, w, b, dy, TIGHT[1])
 
 
+def test_pipelined_host_calls_match_the_blocking_ones(gpu, orc):
+    """six calls in flight over two staging sets (the third and later calls reuse a set; shapes grow so
+    that a set is re-allocated while the pipeline is busy), results read only after the synchronise"""
+    import torch as _t
+
+    o = gpu.make_opts(mode=1, deterministic=1)
+    jobs = []
+    for i, (M, K, N) in enumerate([(256, 64, 96), (384, 96, 160), (512, 128, 192)]):
+        x, w, b, dy = seeded(M, K, N, seed=40 + i)
+        pin = lambda a: _t.from_numpy(a).pin_memory()
+        hx, hw, hb, hdy = pin(x), pin(w), pin(b), pin(dy)
+        hy = _t.empty((M, N)).pin_memory()
+        hdx = _t.empty((M, K)).pin_memory()
+        hdw = _t.empty((K, N)).pin_memory()
+        hdb = _t.empty((N,)).pin_memory()
+        assert gpu.forward_host_async(hy, hx, hw, hb, 1, M, K, N, o) == 0
+        assert gpu.backward_input_host_async(hdx, hdy, hw, 1, M, K, N, o) == 0
+        assert gpu.backward_weight_host_async(hdw, hdb, hdy, hx, 1, M, K, N, o) == 0
+        jobs.append((x, w, b, dy, hy, hdx, hdw, hdb))
+    assert gpu.host_synchronize() == 0
+    for x, w, b, dy, hy, hdx, hdw, hdb in jobs:
+        check_all(orc, (hy.numpy(), hdx.numpy(), hdw.numpy(), hdb.numpy()), x, w, b, dy, TIGHT[1])
+    assert gpu.host_synchronize() == 0  # nothing pending: returns at once
+    bad = gpu.make_opts(mode=1, aux=1 << 20, aux_op=gpu.AUX_ADD)
+    assert gpu.forward_host_async(hy, hx, hw, hb, 1, 512, 128, 192, bad) == gpu.ERR_BAD_ARG
+
+
 def test_linearity_at_full_size(gpu):
     """Size-independent property at the benchmark's QKV shape (M = 8192): the forward is linear
     in x, so f(x1) + f(x2) - f(0) == f(x1 + x2) up to TF32 rounding; 3xTF32 makes it tight."""
