@@ -192,6 +192,37 @@ def reference_gpu_baseline(torch, steps=3):
             "per_gemm_ms": per}
 
 
+def reference_train_baseline(torch, steps=10, warmup=2):
+    """The reference's own training step (src/train.cu + its layer kernels, compiled unmodified) at the
+    shape it ships, B=4, T=64, GPT-2 small, seeded weights, on this GPU. Its loop reads the loss back
+    every step (tests/test_train.cu:283-301 of the reference), so that is inside the timing too."""
+    import __graft_entry__ as ge
+
+    L = ge.load_oracle().ref_train_lib()
+    if L is None or not torch.cuda.is_available():
+        return None
+    B, T = 4, 64
+    rc = L.ref_train_create(B, T, 1234)
+    if rc != 0:
+        return {"unavailable": f"ref_train_create returned {rc}"}
+    gen = torch.Generator(device="cuda").manual_seed(100)
+    tok = torch.randint(0, 50257, (B * T,), dtype=torch.int32, device="cuda", generator=gen)
+    tgt = torch.randint(0, 50257, (B * T,), dtype=torch.int32, device="cuda", generator=gen)
+    loss = None
+    for _ in range(warmup):
+        loss = L.ref_train_step(tok.data_ptr(), tgt.data_ptr())
+    L.ref_train_sync()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loss = L.ref_train_step(tok.data_ptr(), tgt.data_ptr())
+    L.ref_train_sync()
+    sec = time.perf_counter() - t0
+    return {"tokens_per_s": B * T * steps / sec, "ms_per_step": sec / steps * 1e3, "steps": steps, "B": B, "T": T,
+            "loss_last": float(loss),
+            "what": "reference src/train.cu step (forward, cross_entropy, backward, gpt2_update: separate kernel "
+                    "launches, fp32 CUDA cores) recompiled for sm_100a, same GPU"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -225,6 +256,12 @@ def run_reference(args):
             line["reference_gpu"] = ref_gpu
     except Exception as exc:  # the CPU number above stands on its own
         line["reference_gpu"] = {"unavailable": str(exc)[:200]}
+    try:
+        ref_train = reference_train_baseline(torch)
+        if ref_train:
+            line["reference_train"] = ref_train
+    except Exception as exc:
+        line["reference_train"] = {"unavailable": str(exc)[:200]}
     print(json.dumps(line), flush=True)
     return 0
 
@@ -382,6 +419,10 @@ def run_ours(args):
     # ---- the GEMM path inside a whole training step (GPT-2 small, B=16 per GPU, T=1024)
     train = None if args.no_train else measure_train(g, dp, torch, local_rank, rank, world, barrier,
                                                       dist if world > 1 else None, mode)
+    # ---- and at the shape the reference ships (B=4, T=64), where its own step can run beside it
+    train_small = None if args.no_train else measure_train(g, dp, torch, local_rank, rank, world, barrier,
+                                                            dist if world > 1 else None, mode, B=4, T=64,
+                                                            steps=20, warmup=3)
 
     if rank != 0:
         if world > 1:
@@ -414,6 +455,8 @@ def run_ours(args):
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if train:
         line["train"] = train
+    if train_small is not None:
+        line["train_small"] = train_small
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -422,7 +465,7 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over the
 # 15 launches of one step, from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 483.4e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 485.5e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
 
 
 def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=16, T=1024, steps=5, warmup=2):
@@ -468,7 +511,7 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
     out = {"tokens_per_s": B * T * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps,
            "config": f"GPT-2 small (12 layers, 768 wide, vocabulary 50257 padded to 50304), B={B} per GPU, T={T}, "
                      f"AdamW lr 3e-4 betas 0.9/0.95 wd 0.1, fp32 master weights, {'3xTF32' if mode else 'TF32'} GEMMs, "
-                     + ("attention as batched causal GEMMs on the linear-layer kernel" if mode else
+                     + ("attention as batched causal GEMMs on the linear-layer kernel" if (mode or T % 128) else
                         "fused causal attention on the tensor cores (no T x T tensors)")
                      + "; residual adds and GELU backward in GEMM epilogues", "loss_after": loss,
            "gradient_exchange": "none (1 GPU)" if world == 1 else "NCCL average, one bucket per block, overlapped"}

@@ -10,6 +10,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle_linear.so")
 REF_SO = os.path.join(HERE, "_ref", "libref_mlp.so")
+REF_TRAIN_SO = os.path.join(HERE, "_ref", "libref_train.so")
 
 
 def build(reference_root="/root/reference"):
@@ -153,3 +154,24 @@ def ref_lib():
         L.ref_mlp_backward_weight.argtypes = [P, P, P, P, I, I, I, I, P]
         _ref = L
     return _ref
+
+
+_ref_train = None
+
+
+def ref_train_lib():
+    """The reference's own training step (src/train.cu and its layer kernels, unmodified, behind
+    oracle/ref_train_shim.cu), or None when it was not built. One model per process."""
+    global _ref_train
+    if _ref_train is None and os.path.exists(REF_TRAIN_SO):
+        L = ctypes.CDLL(REF_TRAIN_SO)
+        L.ref_train_create.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_uint]
+        L.ref_train_create.restype = ctypes.c_int
+        L.ref_train_num_params.restype = ctypes.c_longlong
+        L.ref_train_set_params.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
+        L.ref_train_set_params.restype = ctypes.c_int
+        L.ref_train_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        L.ref_train_step.restype = ctypes.c_float
+        L.ref_train_sync.restype = ctypes.c_int
+        _ref_train = L
+    return _ref_train
