@@ -302,8 +302,9 @@ def run_ours(args):
                 dist.barrier()
             torch.cuda.synchronize()
         mode0 = g.MODE_TF32X3 if args.mode == "tf32x3" else g.MODE_TF32
+        tb, tt = (int(v) for v in args.train_shape.lower().split("x"))
         train = measure_train(g, dp, torch, local_rank, rank, world, barrier0, dist if world > 1 else None, mode0,
-                              steps=args.steps, warmup=args.warmup)
+                              B=tb, T=tt, steps=args.steps, warmup=args.warmup)
         if rank == 0:
             print(json.dumps({"partial": True, "train": train}), flush=True)
         if world > 1:
@@ -486,7 +487,7 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
     gen = torch.Generator(device="cuda").manual_seed(100 + rank)
     tok = torch.randint(0, V, (B * T,), dtype=torch.int32, device="cuda", generator=gen)
     tgt = torch.randint(0, V, (B * T,), dtype=torch.int32, device="cuda", generator=gen)
-    step = dp.DataParallelStep(model, torch.device("cuda", local_rank))
+    step = dp.DataParallelStep(model, torch.device("cuda", local_rank), use_graph=(world == 1))
     stream = torch.cuda.current_stream().cuda_stream
     hyper = (3e-4, 0.9, 0.95, 1e-8, 0.1)
     t = 0
@@ -514,7 +515,8 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
                      + ("attention as batched causal GEMMs on the linear-layer kernel" if (mode or T % 128) else
                         "fused causal attention on the tensor cores (no T x T tensors)")
                      + "; residual adds and GELU backward in GEMM epilogues", "loss_after": loss,
-           "gradient_exchange": "none (1 GPU)" if world == 1 else "NCCL average, one bucket per block, overlapped"}
+           "gradient_exchange": "none (1 GPU; forward + backward replayed from a CUDA graph)" if world == 1
+           else "NCCL average, one bucket per block, overlapped"}
     model.close()
     return out
 
@@ -581,6 +583,8 @@ def main():
     ap.add_argument("--only", default="", help="comma list like lm_head.fwd,qkv.wgrad (profiling aid)")
     ap.add_argument("--no-e2e", dest="no_e2e", action="store_true", help="kernel-only run (profiling aid)")
     ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the whole-training-step leg")
+    ap.add_argument("--train-shape", dest="train_shape", default="16x1024",
+                    help="BxT of the --only-train leg (profiling aid; default 16x1024)")
     ap.add_argument("--only-train", dest="only_train", action="store_true",
                     help="run only the whole-training-step leg (profiling aid)")
     args = ap.parse_args()

@@ -61,7 +61,7 @@ MODEL_EXPORTS = [
     "gpt2_model_forward", "gpt2_model_backward", "gpt2_model_update", "gpt2_model_mean_loss",
     "gpt2_model_backward_head", "gpt2_model_backward_layer", "gpt2_model_backward_embedding",
     "gpt2_model_device_bytes", "gpt2_model_update_range", "gpt2_model_load_weights", "gpt2_model_dump_weights",
-    "gpt2_model_save_checkpoint", "gpt2_model_load_checkpoint",
+    "gpt2_model_save_checkpoint", "gpt2_model_load_checkpoint", "gpt2_model_forward_backward_graph",
 ]
 
 
@@ -201,6 +201,8 @@ def _load():
     lib.gpt2_model_update.restype = I
     lib.gpt2_model_mean_loss.argtypes = [V, V]
     lib.gpt2_model_mean_loss.restype = F
+    lib.gpt2_model_forward_backward_graph.argtypes = [V, P, P, V]
+    lib.gpt2_model_forward_backward_graph.restype = I
     lib.gpt2_model_update_range.argtypes = [V, LL, LL, F, F, F, F, F, I, V]
     lib.gpt2_model_update_range.restype = I
     for name in ("gpt2_model_load_weights", "gpt2_model_dump_weights"):
@@ -405,6 +407,9 @@ class Model:
 
     def backward(self, stream=None):
         return lib.gpt2_model_backward(self.handle, stream)
+
+    def forward_backward_graph(self, tokens, targets, stream=None):
+        return lib.gpt2_model_forward_backward_graph(self.handle, _p(tokens), _p(targets), stream)
 
     def backward_head(self, stream=None):
         return lib.gpt2_model_backward_head(self.handle, stream)

@@ -49,6 +49,12 @@ struct gpt2_model {
   bool attn_flash = false;   // attention as one fused tensor-core kernel per pass
   std::vector<LayerActs> la;
   const int *tokens = nullptr;  // of the last forward
+  // forward + backward as a CUDA graph (gpt2_model_forward_backward_graph)
+  bool eager_done = false;            // one eager pass has made every lazy allocation
+  cudaStream_t cap_stream = nullptr;  // capture happens here (the legacy default stream cannot capture)
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  const int *g_tokens = nullptr, *g_targets = nullptr;
   float *h_losses = nullptr;    // pinned
   long long device_bytes = 0;
 };
@@ -186,6 +192,9 @@ void gpt2_model_destroy(gpt2_model *m) {
   if (m->m2) cudaFree(m->m2);
   if (m->acts) cudaFree(m->acts);
   if (m->h_losses) cudaFreeHost(m->h_losses);
+  if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  if (m->graph) cudaGraphDestroy(m->graph);
+  if (m->cap_stream) cudaStreamDestroy(m->cap_stream);
   delete m;
 }
 
@@ -321,6 +330,45 @@ int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream) {
   CK(gpt2_model_backward_head(m, stream));
   for (int l = m->cfg.n_layer - 1; l >= 0; --l) CK(gpt2_model_backward_layer(m, l, stream));
   return gpt2_model_backward_embedding(m, stream);
+}
+
+// Forward + backward replayed from a CUDA graph: at small shapes (the reference's B=4, T=64) the step is
+// ~250 short launches plus the host-side tensor-map encoding of 147 GEMM calls, and the GPU waits for
+// the host; a graph replays the whole step with one call. Kernel parameters (tensor maps, pointers,
+// tilings) are frozen at capture, so the graph is rebuilt when the token / target pointers change.
+int gpt2_model_forward_backward_graph(gpt2_model *m, const int *tokens, const int *targets, gpt2l_stream_t stream) {
+  if (!m || !tokens || !targets) return GPT2L_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!m->eager_done) {
+    // workspaces, scratch and function attributes are set up lazily by the first calls: not under capture
+    CK(gpt2_model_forward(m, tokens, targets, stream));
+    CK(gpt2_model_backward(m, stream));
+    m->eager_done = true;
+    return GPT2L_OK;
+  }
+  if (!m->graph_exec || tokens != m->g_tokens || targets != m->g_targets) {
+    if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+    if (m->graph) cudaGraphDestroy(m->graph);
+    m->graph_exec = nullptr;
+    m->graph = nullptr;
+    if (!m->cap_stream && cudaStreamCreateWithFlags(&m->cap_stream, cudaStreamNonBlocking) != cudaSuccess)
+      return GPT2L_ERR_CUDA;
+    if (cudaStreamBeginCapture(m->cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return GPT2L_ERR_CUDA;
+    int e = gpt2_model_forward(m, tokens, targets, m->cap_stream);
+    if (e == GPT2L_OK) e = gpt2_model_backward(m, m->cap_stream);
+    const cudaError_t ce = cudaStreamEndCapture(m->cap_stream, &m->graph);
+    if (e != GPT2L_OK || ce != cudaSuccess) {
+      if (m->graph) cudaGraphDestroy(m->graph);
+      m->graph = nullptr;
+      (void)cudaGetLastError();
+      return e != GPT2L_OK ? e : GPT2L_ERR_CUDA;
+    }
+    if (cudaGraphInstantiate(&m->graph_exec, m->graph, 0) != cudaSuccess) return GPT2L_ERR_CUDA;
+    m->g_tokens = tokens;
+    m->g_targets = targets;
+  }
+  m->tokens = tokens;
+  return cudaGraphLaunch(m->graph_exec, st) == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }
 
 int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,

@@ -200,11 +200,15 @@ class DataParallelStep:
     backward_weight GEMMs of block l-1 hide the exchange of block l). AdamW runs replicated after the
     last bucket has landed. With one rank the exchange is a no-op.
 
+    use_graph=True (single rank only): forward + backward are replayed from a CUDA graph
+    (gpt2_model_forward_backward_graph), which pays at small shapes where launches dominate.
+
     shard_optimizer=True swaps the all-reduce for ShardedExchange: reduce-scatter per bucket, AdamW on
     this rank's slices only (gpt2_model_update_range), all-gather of the parameters."""
 
-    def __init__(self, model, device, group=None, shard_optimizer=False):
+    def __init__(self, model, device, group=None, shard_optimizer=False, use_graph=False):
         self.model = model
+        self.use_graph = use_graph
         self.exchange = GradientExchange(group)
         self.sharded = None
         if shard_optimizer:
@@ -225,6 +229,10 @@ class DataParallelStep:
         m = self.model
         if self.sharded is not None:
             return self._sharded_step(tokens, targets, lr, beta1, beta2, eps, weight_decay, t, stream)
+        if self.exchange.world == 1 and self.use_graph:
+            # nothing to overlap with: replay forward + backward from a CUDA graph
+            rc = m.forward_backward_graph(tokens, targets, stream)
+            return rc | m.update(lr, beta1, beta2, eps, weight_decay, t, stream)
         rc = m.forward(tokens, targets, stream)
         rc |= m.backward_head(stream)
         for l in range(self.L - 1, -1, -1):

@@ -62,6 +62,13 @@ int gpt2_model_backward(gpt2_model *m, gpt2l_stream_t stream);
 int gpt2_model_backward_head(gpt2_model *m, gpt2l_stream_t stream);
 int gpt2_model_backward_layer(gpt2_model *m, int l, gpt2l_stream_t stream);
 int gpt2_model_backward_embedding(gpt2_model *m, gpt2l_stream_t stream);
+/* gpt2_model_forward + gpt2_model_backward of one step replayed from a CUDA graph (the reference
+ * launches every kernel of its step separately, src/train.cu:334-448; at its shipped shape B=4, T=64 the
+ * launches and the host-side set-up of 147 GEMM calls outweigh the kernels). The first call runs eagerly
+ * (lazy allocations), the second captures, later calls replay; the graph is rebuilt when `tokens` or
+ * `targets` point elsewhere. Kernel parameters are frozen at capture: buffer contents may change, buffers
+ * may not move. */
+int gpt2_model_forward_backward_graph(gpt2_model *m, const int *tokens, const int *targets, gpt2l_stream_t stream);
 /* AdamW over the flat parameter buffer, step count t >= 1 (gpt2_update, src/train.cu:450-481). */
 int gpt2_model_update(gpt2_model *m, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
                       gpt2l_stream_t stream);
