@@ -2,7 +2,7 @@
 
     python tests/golden/make_golden.py [/path/to/reference]
 
-Imports scripts/llm.py of vnnm404/gpt2.cu (default location /root/reference), builds two tiny
+Imports scripts/llm.py of vnnm404/gpt2.cu (from the tree given on the command line), builds two tiny
 GPT models with the reference's seeded init, runs one fp32 forward + backward on CPU with seeded
 tokens, and records, for each of the five linear layers of the hot path (QKV, attention output
 projection, MLP fc, MLP fc-proj of block 0, and the tied lm_head), what went in and what the
