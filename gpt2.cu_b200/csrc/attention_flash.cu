@@ -569,15 +569,23 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
   }
 }
 
-// status word shared by the three modes (device memory, one per process and device would be
-// cleaner; attention runs on one device per process here)
+// one status word per device, shared by the three modes (0, or the site of a wait that gave up)
+constexpr int F_MAX_DEVICES = 16;
+int current_device() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= F_MAX_DEVICES) return -1;
+  return d;
+}
+
 int *flash_status_ptr() {
-  static int *p = nullptr;
-  if (!p) {
-    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
+  static int *p[F_MAX_DEVICES] = {};
+  const int d = current_device();
+  if (d < 0) return nullptr;
+  if (!p[d]) {
+    if (cudaMalloc(&p[d], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p[d], 0, sizeof(int));
   }
-  return p;
+  return p[d];
 }
 
 int build_maps(FlashMaps *m, const float *qkv, const float *dout, int B, int T, int C, int NH, int box_rows) {
@@ -595,7 +603,10 @@ int build_maps(FlashMaps *m, const float *qkv, const float *dout, int B, int T, 
 
 template <int MODE>
 int launch(const FlashMaps &maps, const FlashArgs &args, cudaStream_t st) {
-  static bool attr_set = false;  // per process; one device per process
+  static bool attr_set_on[F_MAX_DEVICES] = {};  // the attribute is per device
+  const int dev = current_device();
+  if (dev < 0) return GPT2L_ERR_CUDA;
+  bool &attr_set = attr_set_on[dev];
   if (!attr_set) {
     if (cudaFuncSetAttribute(attn_flash_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MODE>::SMEM) !=
         cudaSuccess)
