@@ -6,6 +6,7 @@
 // softmax and cross-entropy are one pass that leaves dlogits in place of the logits, and layernorm
 // works a row per warp. All fp32 CUDA-core code; the GEMMs around them are the tcgen05 path.
 #include <cuda_runtime.h>
+#include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
 #include <math.h>
@@ -66,6 +67,49 @@ layernorm_forward_kernel(float *out, float *mean, float *rstd, const float *in, 
   const float rs = rsqrtf(warp_sum(v) / C + 1e-5f);
   float *o = out + (long long)row * C;
   for (int c = lane; c < C; c += 32) o[c] = (x[c] - mu) * rs * w[c] + b[c];
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
+// the same with the row held in registers (K4 float4 per lane): one read of x, one write of out
+template <int K4>  // C <= 128 * K4, C a multiple of 4
+__global__ void __launch_bounds__(256)
+layernorm_forward_vec_kernel(float *out, float *mean, float *rstd, const float *in, const float *w, const float *b,
+                             int M, int C) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float *x = in + (long long)row * C;
+  float4 v[K4];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < K4; ++k) {
+    const int c = 4 * (lane + 32 * k);
+    v[k] = c < C ? *reinterpret_cast<const float4 *>(x + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += v[k].x + v[k].y + v[k].z + v[k].w;
+  }
+  const float mu = warp_sum(s) / C;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < K4; ++k) {
+    const int c = 4 * (lane + 32 * k);
+    if (c < C) {
+      const float dx = v[k].x - mu, dy = v[k].y - mu, dz = v[k].z - mu, dw = v[k].w - mu;
+      q += dx * dx + dy * dy + dz * dz + dw * dw;
+    }
+  }
+  const float rs = rsqrtf(warp_sum(q) / C + 1e-5f);
+  float *o = out + (long long)row * C;
+#pragma unroll
+  for (int k = 0; k < K4; ++k) {
+    const int c = 4 * (lane + 32 * k);
+    if (c < C) {
+      const float4 wv = __ldg(reinterpret_cast<const float4 *>(w + c));
+      const float4 bv = __ldg(reinterpret_cast<const float4 *>(b + c));
+      *reinterpret_cast<float4 *>(o + c) =
+          make_float4((v[k].x - mu) * rs * wv.x + bv.x, (v[k].y - mu) * rs * wv.y + bv.y,
+                      (v[k].z - mu) * rs * wv.z + bv.z, (v[k].w - mu) * rs * wv.w + bv.w);
+    }
+  }
   if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
 }
 
@@ -571,17 +615,40 @@ attention_backward_dkv_kernel(float *dqkv, const float *dout, const float *qkv, 
 // ------------------------------------------------------------------------------------
 // AdamW over the flat parameter buffer; decay on every element, bias-corrected (adamw.cu:11-48)
 // ------------------------------------------------------------------------------------
-__global__ void adamw_kernel(float *p, float *m, float *v, const float *g, long long n, float lr, float b1, float b2,
-                             float eps, float wd, float bc1, float bc2) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const float gi = g[i];
-  const float mi = b1 * m[i] + (1.f - b1) * gi;
-  const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
-  m[i] = mi;
-  v[i] = vi;
+__device__ __forceinline__ void adamw_one(float &p, float &m, float &v, float gi, float lr, float b1, float b2, float eps,
+                                          float wd, float bc1, float bc2) {
+  const float mi = b1 * m + (1.f - b1) * gi;
+  const float vi = b2 * v + (1.f - b2) * gi * gi;
+  m = mi;
+  v = vi;
   const float mh = mi / bc1, vh = vi / bc2;
-  p[i] -= lr * (mh / (sqrtf(vh) + eps) + wd * p[i]);
+  p -= lr * (mh / (sqrtf(vh) + eps) + wd * p);
+}
+
+// `head` scalar elements bring the pointers to a 16-byte boundary, then float4 elements, then a scalar
+// tail (a range of the flat buffer may start anywhere); every element sees the same arithmetic.
+__global__ void adamw_kernel(float *p, float *m, float *v, const float *g, long long n, long long head, long long n4,
+                             float lr, float b1, float b2, float eps, float wd, float bc1, float bc2) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n4) {
+    const long long o = head + 4 * i;
+    float4 pp = *reinterpret_cast<float4 *>(p + o), mm = *reinterpret_cast<float4 *>(m + o),
+           vv = *reinterpret_cast<float4 *>(v + o);
+    const float4 gg = *reinterpret_cast<const float4 *>(g + o);
+    adamw_one(pp.x, mm.x, vv.x, gg.x, lr, b1, b2, eps, wd, bc1, bc2);
+    adamw_one(pp.y, mm.y, vv.y, gg.y, lr, b1, b2, eps, wd, bc1, bc2);
+    adamw_one(pp.z, mm.z, vv.z, gg.z, lr, b1, b2, eps, wd, bc1, bc2);
+    adamw_one(pp.w, mm.w, vv.w, gg.w, lr, b1, b2, eps, wd, bc1, bc2);
+    *reinterpret_cast<float4 *>(p + o) = pp;
+    *reinterpret_cast<float4 *>(m + o) = mm;
+    *reinterpret_cast<float4 *>(v + o) = vv;
+  } else {
+    // the few elements before and after the aligned body
+    const long long j = i - n4;
+    const long long tail0 = head + 4 * n4;
+    const long long o = j < head ? j : tail0 + (j - head);
+    if (o < n) adamw_one(p[o], m[o], v[o], g[o], lr, b1, b2, eps, wd, bc1, bc2);
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -603,7 +670,17 @@ int embedding_backward(float *g_wte, float *g_wpe, const float *g, const int *to
 }
 int layernorm_forward(float *out, float *mean, float *rstd, const float *in, const float *w, const float *b, int M,
                       int C, cudaStream_t s) {
-  layernorm_forward_kernel<<<cdiv(M, 8), 256, 0, s>>>(out, mean, rstd, in, w, b, M, C);
+#define LN_FWD(K4) layernorm_forward_vec_kernel<K4><<<cdiv(M, 8), 256, 0, s>>>(out, mean, rstd, in, w, b, M, C)
+  if (C & 3) layernorm_forward_kernel<<<cdiv(M, 8), 256, 0, s>>>(out, mean, rstd, in, w, b, M, C);
+  else if (C <= 128) LN_FWD(1);
+  else if (C <= 256) LN_FWD(2);
+  else if (C <= 512) LN_FWD(4);
+  else if (C <= 768) LN_FWD(6);
+  else if (C <= 1024) LN_FWD(8);
+  else if (C <= 1280) LN_FWD(10);
+  else if (C <= 2048) LN_FWD(16);
+  else layernorm_forward_kernel<<<cdiv(M, 8), 256, 0, s>>>(out, mean, rstd, in, w, b, M, C);
+#undef LN_FWD
   return LAUNCH_OK();
 }
 int layernorm_backward(float *g_in, float *g_w, float *g_b, const float *g_out, const float *in, const float *w,
@@ -669,7 +746,12 @@ int attention_backward(float *dqkv, float *delta, const float *dout, const float
 int adamw_update(float *p, float *m, float *v, const float *g, long long n, float lr, float b1, float b2, float eps,
                  float wd, int t, cudaStream_t s) {
   const float bc1 = 1.f - powf(b1, (float)t), bc2 = 1.f - powf(b2, (float)t);
-  adamw_kernel<<<cdiv(n, 256), 256, 0, s>>>(p, m, v, g, n, lr, b1, b2, eps, wd, bc1, bc2);
+  // all four buffers are offset alike from 256-byte aligned allocations, so p decides the alignment
+  long long head = (long long)((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / 4;
+  if (head > n) head = n;
+  const long long n4 = (n - head) / 4;
+  const long long extra = n - 4 * n4;  // head + tail, at most 6
+  adamw_kernel<<<cdiv(n4 + extra, 256), 256, 0, s>>>(p, m, v, g, n, head, n4, lr, b1, b2, eps, wd, bc1, bc2);
   return LAUNCH_OK();
 }
 
