@@ -269,6 +269,18 @@ def test_pipelined_host_calls_match_the_blocking_ones(gpu, orc):
     for x, w, b, dy, hy, hdx, hdw, hdb in jobs:
         check_all(orc, (hy.numpy(), hdx.numpy(), hdw.numpy(), hdb.numpy()), x, w, b, dy, TIGHT[1])
     assert gpu.host_synchronize() == 0  # nothing pending: returns at once
+    # no bias / no bias gradient (the lm_head case), through a staging set that has held larger operands
+    x, w, b, dy = seeded(130, 36, 68, seed=77)
+    pin = lambda a: _t.from_numpy(a).pin_memory()
+    hx, hw, hdy = pin(x), pin(w), pin(dy)
+    hy, hdw = _t.empty((130, 68)).pin_memory(), _t.empty((36, 68)).pin_memory()
+    assert gpu.forward_host_async(hy, hx, hw, None, 1, 130, 36, 68, o) == 0
+    assert gpu.backward_weight_host_async(hdw, None, hdy, hx, 1, 130, 36, 68, o) == 0
+    assert gpu.host_synchronize() == 0
+    assert orc.max_rel_err(hy.numpy(), orc.forward(x, w, None, f64=True)) <= TIGHT[1]
+    assert orc.max_rel_err(hdw.numpy(), orc.backward_weight(dy, x, want_bias=False, f64=True)[0]) <= TIGHT[1]
+    hx, hw, hb = pin(seeded(512, 128, 192, seed=42)[0]), pin(seeded(512, 128, 192, seed=42)[1]), pin(seeded(512, 128, 192, seed=42)[2])
+    hy = _t.empty((512, 192)).pin_memory()
     bad = gpu.make_opts(mode=1, aux=1 << 20, aux_op=gpu.AUX_ADD)
     assert gpu.forward_host_async(hy, hx, hw, hb, 1, 512, 128, 192, bad) == gpu.ERR_BAD_ARG
 
