@@ -252,3 +252,19 @@ def test_graph_replay_equals_eager_steps(gpu):
     assert eager[0] - eager[-1] > 0.05   # the run actually trains
     m1.close()
     m2.close()
+
+
+@pytest.mark.parametrize("mode,tol", [(1, 1e-3), (0, 2e-2)])
+@pytest.mark.parametrize("fx", ["llm_train_wide1024.npz", "llm_train_wide1280.npz"])
+def test_medium_and_large_widths_track_the_reference_model(gpu, fx, mode, tol):
+    """The widths and head counts of GPT-2 medium (1024 / 16) and large (1280 / 20), two layers deep, B=2,
+    T=128, six AdamW steps: per-step loss against the reference's PyTorch model. TF32 mode runs the fused
+    attention kernels at these head counts, 3xTF32 the batched-GEMM attention."""
+    z = golden(fx)
+    m, params, tok, tgt, steps = build(gpu, z, mode)
+    losses = train(m, tok, tgt, steps, z["hyper"])
+    st, rec = gpu.last_status()
+    assert st == 0, rec
+    assert gpu.lib.gpt2_attention_status() == 0
+    assert np.abs(losses - z["losses"]).max() <= tol, (losses - z["losses"])
+    m.close()
