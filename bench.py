@@ -304,7 +304,7 @@ def run_ours(args):
         mode0 = g.MODE_TF32X3 if args.mode == "tf32x3" else g.MODE_TF32
         tb, tt = (int(v) for v in args.train_shape.lower().split("x"))
         train = measure_train(g, dp, torch, local_rank, rank, world, barrier0, dist if world > 1 else None, mode0,
-                              B=tb, T=tt, steps=args.steps, warmup=args.warmup)
+                              B=tb, T=tt, steps=args.steps, warmup=args.warmup, model_name=args.train_model)
         if rank == 0:
             print(json.dumps({"partial": True, "train": train}), flush=True)
         if world > 1:
@@ -469,14 +469,19 @@ def run_ours(args):
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 485.5e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
 
 
-def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=16, T=1024, steps=5, warmup=2):
+MODELS = {"small": (768, 12, 12), "medium": (1024, 24, 16), "large": (1280, 36, 20)}  # width, layers, heads
+
+
+def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=16, T=1024, steps=5, warmup=2,
+                  model_name="small"):
     """Tokens/s of whole training steps (forward, backward, gradient all-reduce over NCCL overlapped
     with the backward pass, AdamW) of GPT-2 small at B sequences of T tokens per GPU, random-init
     weights and uniform random tokens: the configuration BASELINE.json calls the megakernel step."""
     import numpy as np
 
-    C, V, Vp, L = 768, 50257, 50304, 12
-    model = g.Model(V, Vp, L, 12, C, 1024, B, T, mode=mode)
+    C, L, NH = MODELS[model_name]
+    V, Vp = 50257, 50304
+    model = g.Model(V, Vp, L, NH, C, 1024, B, T, mode=mode)
     rng = np.random.default_rng(42)  # same weights on every rank
     params = rng.standard_normal(model.num_params, dtype=np.float32) * np.float32(0.02)
     offs = model.offsets()
@@ -510,7 +515,7 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms = tt.item()
     out = {"tokens_per_s": B * T * world * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps,
-           "config": f"GPT-2 small (12 layers, 768 wide, vocabulary 50257 padded to 50304), B={B} per GPU, T={T}, "
+           "config": f"GPT-2 {model_name} ({L} layers, {C} wide, vocabulary 50257 padded to 50304), B={B} per GPU, T={T}, "
                      f"AdamW lr 3e-4 betas 0.9/0.95 wd 0.1, fp32 master weights, {'3xTF32' if mode else 'TF32'} GEMMs, "
                      + ("attention as batched causal GEMMs on the linear-layer kernel" if (mode or T % 128) else
                         "fused causal attention on the tensor cores (no T x T tensors)")
@@ -585,6 +590,8 @@ def main():
     ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the whole-training-step leg")
     ap.add_argument("--train-shape", dest="train_shape", default="16x1024",
                     help="BxT of the --only-train leg (profiling aid; default 16x1024)")
+    ap.add_argument("--train-model", dest="train_model", default="small", choices=sorted(MODELS),
+                    help="model of the --only-train leg (profiling aid; default small = GPT-2 124M)")
     ap.add_argument("--only-train", dest="only_train", action="store_true",
                     help="run only the whole-training-step leg (profiling aid)")
     args = ap.parse_args()
