@@ -76,12 +76,14 @@ struct Cfg {
   static constexpr int FC = 64;                         // columns per step
   static constexpr int NA = MODE == F_FWD ? 1 : 2;      // fixed A tiles; also score MMAs per step
   static constexpr int NP = MODE == F_BWD_KV ? 2 : 1;   // accumulators (and A tiles written back per step)
-  static constexpr int NST = 2;                         // operand stages
-  static constexpr int NSB = 3;                         // score slots in TMEM
+  // BWD_Q trades its double buffers for a second resident CTA per SM (two CTAs overlap each other's MMA
+  // latency, which is what bounds these kernels): one operand stage, one score slot, 113 KiB, 256 TMEM columns
+  static constexpr int NST = MODE == F_BWD_Q ? 1 : 2;   // operand stages
+  static constexpr int NSB = MODE == F_BWD_Q ? 1 : 3;   // score slots in TMEM
   // sets of four row-work warps; the backward modes split a step's columns between two sets
-  static constexpr int NCW = MODE == F_FWD ? 1 : 2;
-  static constexpr int MINB = MODE == F_FWD ? 2 : 1;    // FWD: 97 KiB, 256 TMEM columns: two CTAs per SM
-  static constexpr int NMW = MODE == F_FWD ? 1 : 2;     // MMA-issuing warps
+  static constexpr int NCW = MODE == F_BWD_KV ? 2 : 1;
+  static constexpr int MINB = MODE == F_BWD_KV ? 1 : 2;  // CTAs per SM
+  static constexpr int NMW = MODE == F_BWD_KV ? 2 : 1;  // MMA-issuing warps
   static constexpr int THREADS = 32 * (1 + NMW) + 128 * NCW;  // producer, MMA issuers, row-work warps
   static constexpr int TILE_B = FC * FHS * 4;           // [FC][64] K-major (two k-blocks) or MN-major (FC/32 k-blocks)
   static constexpr int OFF_A = 0;
@@ -89,7 +91,10 @@ struct Cfg {
   static constexpr int OFF_AB = OFF_SB + NST * NA * TILE_B;   // accumulate-stage B operands (MN-major)
   static constexpr int OFF_VEC = OFF_AB + NST * NP * TILE_B;  // BWD_KV: lse and delta of the step's queries
   static constexpr int OFF_CTRL = OFF_VEC + (MODE == F_BWD_KV ? 8 * 2 * 64 * 4 : 0);  // per row-work warp, two buffers of 64 floats
-  static constexpr int SMEM = 1024 + OFF_CTRL + 256;
+  // the control block (barriers) sits in whichever end of the allocation the 1024-byte alignment of the
+  // tiles leaves free, so the request is tiles + 1024 bytes and not a byte more
+  static constexpr int CTRL_BYTES = 256;
+  static constexpr int SMEM = 1024 + OFF_CTRL;
   // TMEM columns: NSB score slots of NA x FC columns, then the accumulators (NP x 64)
   static constexpr int COL_ACC = NSB * NA * FC;
   static constexpr int TMEM_COLS = COL_ACC + NP * FHS <= 256 ? 256 : 512;
@@ -186,7 +191,9 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - raw);
-  FlashCtrl *ctrl = reinterpret_cast<FlashCtrl *>(base_ptr + K::OFF_CTRL);
+  FlashCtrl *ctrl = reinterpret_cast<FlashCtrl *>((base - raw) >= (uint32_t)K::CTRL_BYTES ? smem_raw
+                                                                                          : base_ptr + K::OFF_CTRL);
+  static_assert(sizeof(FlashCtrl) <= K::CTRL_BYTES, "control block");
   float *vec = reinterpret_cast<float *>(base_ptr + K::OFF_VEC);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -363,7 +370,13 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         ok = f_wait(smem_u32(&ctrl->fixed_full), 0, ctrl, a, 3);
         tc_fence_after();
       }
-      if (K::NMW == 1) {
+      if (K::NMW == 1 && K::NSB == 1) {
+        // one slot: the scores of step it + 1 can only follow the accumulate MMAs of step it
+        for (int it = 0; it < n_it && ok; ++it) {
+          ok = issue_score(it);
+          if (ok) ok = issue_acc(it);
+        }
+      } else if (K::NMW == 1) {
         if (ok && n_it > 0) ok = issue_score(0);
         for (int it = 0; it < n_it && ok; ++it) {
           if (it + 1 < n_it) ok = issue_score(it + 1);
@@ -455,10 +468,8 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
         }
       }
     } else if (MODE == F_BWD_Q) {
-      // two warp sets share the rows: set k handles columns [32k, 32k + 32) of every step, which is
-      // k-block k of the dS tile, and columns [32k, 32k + 32) of dQ at the end
+      // NCW warp sets share the rows: set k handles columns [HC k, HC k + HC) of every step and of dQ at the end
       constexpr int HC = FC / K::NCW;
-      static_assert(MODE != F_BWD_Q || HC == 32, "a warp set writes one 32-column k-block");
       const float lse = a.lse[vbase + grow];
       const float dlt8 = a.delta[vbase + grow] * 0.125f;
       for (int it = 0; it < n_it && ok; ++it) {
@@ -498,7 +509,6 @@ attn_flash_kernel(const __grid_constant__ FlashMaps maps, const FlashArgs a) {
       }
     } else {
       constexpr int HC = FC / K::NCW;
-      static_assert(MODE != F_BWD_KV || HC == 32, "a warp set writes one 32-column k-block");
       // lse and delta of the warp's 32 queries of a step are fetched one step ahead (their latency would
       // otherwise sit at the head of every step) and shared through a per-warp copy in shared memory,
       // double-buffered by step parity: only warp-level synchronisation is involved
