@@ -74,3 +74,48 @@ def test_attention_shape_checks(gpu):
     l = torch.zeros((2, 192), device="cuda")
     assert gpu.attention_forward(o, l, None, x, 1, 192, 2, 128, gpu.ATT_FLASH) == gpu.ERR_BAD_ARG
     assert gpu.attention_forward(o, None, None, x, 1, 192, 2, 128, gpu.ATT_SIMT) == gpu.ERR_BAD_ARG
+
+
+def test_flash_attention_properties_at_full_sequence_length(gpu):
+    """Size-independent properties at T = 1024, 12 heads (the benchmark's sequence length): with V = 1 every
+    output is 1 (the probabilities of a row sum to one); the output at position t depends on positions
+    <= t only (bitwise, after perturbing everything from t = 512 on); and the gradient with respect to a
+    position vanishes when only earlier positions receive a gradient."""
+    B, NH, T = 2, 12, 1024
+    C = NH * 64
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(B * T, 3 * C, device="cuda", generator=gen)
+    out = torch.empty(B * T, C, device="cuda")
+    lse = torch.empty(B, NH, T, device="cuda")
+
+    ones = qkv.clone()
+    ones[:, 2 * C:] = 1.0
+    assert gpu.attention_forward(out, lse, None, ones, B, T, NH, C, gpu.ATT_FLASH, 0) == 0
+    torch.cuda.synchronize()
+    assert float((out - 1.0).abs().max()) <= 1e-5
+
+    assert gpu.attention_forward(out, lse, None, qkv, B, T, NH, C, gpu.ATT_FLASH, 0) == 0
+    ref = out.clone()
+    lse_ref = lse.clone()
+    pert = qkv.clone().view(B, T, 3 * C)
+    pert[:, 512:, :] = torch.randn(B, T - 512, 3 * C, device="cuda", generator=gen)
+    out2 = torch.empty_like(out)
+    lse2 = torch.empty_like(lse)
+    assert gpu.attention_forward(out2, lse2, None, pert.view(B * T, 3 * C), B, T, NH, C, gpu.ATT_FLASH, 0) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out2.view(B, T, C)[:, :512], ref.view(B, T, C)[:, :512])
+    assert not torch.equal(out2.view(B, T, C)[:, 512:], ref.view(B, T, C)[:, 512:])
+
+    # a gradient that arrives only at positions < 512 leaves q, k, v of positions >= 512 without gradient
+    dout = torch.zeros(B, T, C, device="cuda")
+    dout[:, :512] = torch.randn(B, 512, C, device="cuda", generator=gen) * 0.1
+    g = torch.full((B * T, 3 * C), float("nan"), device="cuda")
+    row = torch.empty(B, NH, T, device="cuda")
+    assert gpu.attention_backward(g, dout.view(B * T, C), qkv, ref, lse_ref, None, row, None, B, T, C, NH,
+                                  gpu.ATT_FLASH, 0) == 0
+    torch.cuda.synchronize()
+    assert gpu.lib.gpt2_attention_status() == 0
+    g3 = g.view(B, T, 3 * C)
+    assert torch.isfinite(g3).all()
+    assert float(g3[:, 512:].abs().max()) == 0.0
+    assert float(g3[:, :512].abs().max()) > 0.0
