@@ -155,6 +155,8 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
     }
     if (op.colsum && cudaMemsetAsync(op.colsum, 0, (size_t)op.Nc * sizeof(float), st) != cudaSuccess)
       return GPT2L_ERR_CUDA;
+  } else if (op.colsum && op.colsum_spread) {
+    if (cudaMemsetAsync(op.colsum, 0, (size_t)op.Nc * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
   }
   err = launch_single(ctx, op, st);
   if (err) return err;

@@ -76,6 +76,8 @@ struct alignas(64) GemmOp {
   float aux_scale;
   const float *bias;    // [Nc] or null
   float *colsum;        // wgrad: g_b[Nc] or null (column sums of B over the reduction)
+  int colsum_spread;     // 1: every tile row sums its share of the k-blocks (kb % tiles_m == m_tile) and adds
+                         // it atomically into a zeroed colsum; 0: tile row 0 sums everything
   float *ws;            // deterministic split-K: partial tiles [n_tiles][BM*bn]
   float *ws_colsum;     // deterministic split-K: [splits][Nc]
   unsigned *ws_sem;     // deterministic split-K: per output tile arrival counter

@@ -258,7 +258,12 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
       if (tc.skip) continue;
       const int bn = op->bn;
-      const bool do_colsum = (op->colsum != nullptr) && tc.m_tile == 0 && op->b_mn;
+      // bias gradient = column sums of the B blocks. Spread over the tile rows (row m takes the
+      // k-blocks with kb % tiles_m == m) so that no CTA carries the whole extra pass: with tile row 0
+      // doing all of it those CTAs ran ~30 % longer than the rest and the launch waited for them.
+      const bool has_cs = (op->colsum != nullptr) && op->b_mn;
+      const bool spread = has_cs && op->colsum_spread != 0;
+      const bool do_colsum = has_cs && (spread || tc.m_tile == 0);
       // column-sum mapping: `groups` float4 column groups, `parts` threads share a group and
       // split the 32 k-rows of a block between them.
       const int groups = bn >> 2;
@@ -281,7 +286,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         // An MN-major B block is walked by (column group, k-row) so that the thread that sums a
         // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
         // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
-        const bool walk_b = op->b_mn && (X3 || do_colsum);
+        const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
+        const bool walk_b = op->b_mn && (X3 || cs_kb);
         if (walk_b) {
           uint8_t *bchunk = stage + A_TILE_BYTES + chunk * 4096;
 #pragma unroll 4
@@ -289,7 +295,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             const int phys32 = (q16 >> 1) ^ (r & 3);
             float4 *ptr = reinterpret_cast<float4 *>(bchunk + r * 128 + phys32 * 32 + (q16 & 1) * 16);
             const float4 v = *ptr;
-            csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w;
+            if (cs_kb) { csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w; }
             if (X3) {
               float4 h, l;
               h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
@@ -332,7 +338,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
           const float v[4] = {csum.x, csum.y, csum.z, csum.w};
           for (int j = 0; j < 4; ++j) {
             if (col + j < op->Nc) {
-              if (op->splits > 1) atomicAdd(op->colsum + col + j, v[j]);
+              if (op->splits > 1 || spread) atomicAdd(op->colsum + col + j, v[j]);
               else op->colsum[col + j] = v[j];
             }
           }
@@ -637,6 +643,7 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
     case GPT2L_OP_BACKWARD_WEIGHT:  // g_w[K][N] = in[M][K]^T . g_out[M][N]
       op->Mc = d.K; op->Nc = d.N; op->Kc = d.M; op->a_mn = 1; op->b_mn = 1;
       op->colsum = d.out_bias;
+      op->colsum_spread = (d.out_bias && d.opts.cta_pair != 2) ? 1 : 0;
       break;
     default:
       return GPT2L_ERR_BAD_ARG;

@@ -282,6 +282,8 @@ int gpt2_megakernel_run(gpt2l_schedule *s, gpt2l_stream_t stream) {
         return GPT2L_ERR_CUDA;
       if (g.colsum && cudaMemsetAsync(g.colsum, 0, (size_t)g.Nc * sizeof(float), st) != cudaSuccess)
         return GPT2L_ERR_CUDA;
+    } else if (g.colsum && g.colsum_spread) {
+      if (cudaMemsetAsync(g.colsum, 0, (size_t)g.Nc * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
     }
   }
   return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x, s->plan.any_colsum, s->plan.pair,
