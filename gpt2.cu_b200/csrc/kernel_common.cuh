@@ -199,7 +199,7 @@ __device__ __forceinline__ void load_aux(AuxRegs &r, const EpiAux &e, long long 
 
 __device__ __forceinline__ void store_chunk(const float (&v)[32], uint32_t sbuf, float *C, long long ldc,
                                             int row0, int nb, int Mc, int Nc, int lane, bool atomic,
-                                            const EpiAux &e, const AuxRegs &r, float *C2 = nullptr) {
+                                            const EpiAux &e, const AuxRegs &r) {
   __syncwarp();  // the previous chunk's reads of this box are done
 #pragma unroll
   for (int j = 0; j < 8; ++j)
@@ -239,11 +239,6 @@ __device__ __forceinline__ void store_chunk(const float (&v)[32], uint32_t sbuf,
       float *dst = C + (long long)grow * ldc + col;
       if (atomic) red_add_v4(dst, x[i].x, x[i].y, x[i].z, x[i].w);
       else *reinterpret_cast<float4 *>(dst) = x[i];
-      // GELU dual store: the second output leaves from the same coalesced registers, so the pair
-      // costs one trip through shared memory, not two
-      if (C2)
-        *reinterpret_cast<float4 *>(C2 + (long long)grow * ldc + col) =
-            make_float4(gelu_tanh(x[i].x), gelu_tanh(x[i].y), gelu_tanh(x[i].z), gelu_tanh(x[i].w));
     }
   }
 }

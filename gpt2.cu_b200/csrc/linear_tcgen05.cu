@@ -401,6 +401,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
           ea.scale = op->aux_scale;
           if (op->aux_row) ea.row = op->aux_row + ((long long)tc.bb * op->batch_inner + tc.bh) * Mc;
         }
+        const EpiAux none;
         const float drow = (ea.row && row0 + lane < Mc) ? __ldg(ea.row + row0 + lane) : 0.f;
         for (int c = c_first; c < bn / 32; c += n_epi) {
           const int nb = n0 + c * 32;
@@ -421,12 +422,15 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
             v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
           }
-          {
-            const long long boff = tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
-            // the epilogue operand is applied once per element: with split-K reduce-adds the split
-            // that also adds the bias carries it
-            store_chunk(v, sbuf, op->C + boff, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, ea, ar,
-                        dual ? op->C2 + boff : nullptr);
+          for (int pass = 0; pass < (dual ? 2 : 1); ++pass) {
+            if (pass == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+            }
+            float *cbase = (pass == 0 ? op->C : op->C2) + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
+            // the epilogue operand applies to the first output only, and once per element: with
+            // split-K reduce-adds the split that also adds the bias carries it
+            store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, pass == 0 ? ea : none, ar);
           }
         }
       } else if (!helper)  // fixed-order split-K: the quarter's own warp parks whole rows
