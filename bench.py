@@ -417,6 +417,15 @@ def run_ours(args):
     e2e = measure_e2e(g, torch, opts, stream, world, barrier, dist if world > 1 else None,
                       steps=max(1, min(args.steps, 2)))
 
+    # ---- the set as one persistent launch (rank 0 only: a single-GPU comparison)
+    mega = None
+    if rank == 0 and not args.no_train:
+        try:
+            mega = measure_megakernel(g, torch, mode)
+        except Exception as exc:  # a reported extra, never the headline
+            mega = {"unavailable": str(exc)[:200]}
+    barrier()
+
     # ---- the GEMM path inside a whole training step (GPT-2 small, B=16 per GPU, T=1024)
     train = None if args.no_train else measure_train(g, dp, torch, local_rank, rank, world, barrier,
                                                       dist if world > 1 else None, mode)
@@ -458,6 +467,8 @@ def run_ours(args):
         line["train"] = train
     if train_small is not None:
         line["train_small"] = train_small
+    if mega is not None:
+        line["megakernel"] = mega
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -524,6 +535,49 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
            else "NCCL average, one bucket per block, overlapped"}
     model.close()
     return out
+
+
+def measure_megakernel(g, torch, mode, steps=20, warmup=3):
+    """The same 15 GEMMs as ONE persistent launch (gpt2_schedule_create + gpt2_megakernel_run): tile lists of
+    all ops walked by 148 resident CTAs, outputs published on the dependency counters. The ops of the set
+    are independent, so no counter is waited for; what shows is the cost of launch boundaries."""
+    o = g.make_opts(mode=mode)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    ops, keep = [], []
+    for name, K, N in LAYERS:
+        x = torch.randn((M_ROWS, K), device="cuda", generator=gen)
+        w = torch.randn((K, N), device="cuda", generator=gen) * 0.02
+        b = None if name == "lm_head" else torch.randn((N,), device="cuda", generator=gen) * 0.02
+        dy = torch.randn((M_ROWS, N), device="cuda", generator=gen) * 0.01
+        y = torch.empty((M_ROWS, N), device="cuda")
+        dx = torch.empty((M_ROWS, K), device="cuda")
+        dw = torch.empty((K, N), device="cuda")
+        db = None if name == "lm_head" else torch.empty((N,), device="cuda")
+        ops += [g.make_op(g.OP_FORWARD, BATCH, SEQ, K, N, y, x, w, bias=b, opts=o),
+                g.make_op(g.OP_BACKWARD_INPUT, BATCH, SEQ, K, N, dx, dy, w, opts=o),
+                g.make_op(g.OP_BACKWARD_WEIGHT, BATCH, SEQ, K, N, dw, x, dy, out_bias=db, opts=o)]
+        keep.append((x, w, b, dy, y, dx, dw, db))
+    sched = g.Schedule(ops)
+    for _ in range(warmup):
+        if sched.run() != 0:
+            raise SystemExit("megakernel run failed")
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        sched.run()
+    e.record()
+    torch.cuda.synchronize()
+    st = sched.status()
+    ms = s.elapsed_time(e) / steps
+    sched.close()
+    del keep
+    if st != 0:
+        return {"unavailable": f"device status {st}"}
+    return {"value": step_flops() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+            "launches_per_step": 1,
+            "what": "the 15 GEMMs of the set as one persistent launch (gpt2_megakernel_run); lm_head weight gradient "
+                    "without the transposed-activation path of the per-call entry point"}
 
 
 def measure_e2e(g, torch, opts, stream, world, barrier, dist, steps):
