@@ -6,6 +6,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <vector>
 
 #include "linear_internal.h"
 
@@ -31,10 +32,25 @@ struct HostPipe {
     bool used = false;
   } set[2];
   unsigned long long calls = 0;
+  // Inputs uploaded since the last synchronise, by host address and size. The contract of the pipelined
+  // calls forbids changing an input before the synchronise, so a buffer passed to several calls (the
+  // weight to forward and backward_input, the activations to forward and backward_weight, ...) crosses
+  // PCIe once. The device copies go back to `pool` at the synchronise and are reused by later windows.
+  struct Input {
+    const void *host;
+    size_t bytes;
+    float *dev;
+    size_t cap;
+  };
+  std::vector<Input> inputs;
+  std::vector<Input> pool;  // host / bytes unused
+  unsigned long long uploaded_bytes = 0, reused_bytes = 0;
 };
 
 static void destroy_pipe(HostPipe *p) {
   if (!p) return;
+  for (auto &i : p->inputs) cudaFree(i.dev);
+  for (auto &i : p->pool) cudaFree(i.dev);
   for (auto &s : p->set) {
     for (float *b : s.buf)
       if (b) cudaFree(b);
@@ -416,6 +432,42 @@ int async_stage(AsyncCall &c, int slot, const float *host, size_t count) {
   return GPT2L_OK;
 }
 
+// device copy of a host input: the one uploaded earlier in this window, or a fresh upload
+int async_input(AsyncCall &c, const float *host, size_t count, float **dev) {
+  HostPipe *p = c.p;
+  const size_t bytes = count * sizeof(float);
+  for (const auto &i : p->inputs)
+    if (i.host == host && i.bytes == bytes) {
+      *dev = i.dev;
+      p->reused_bytes += bytes;
+      return GPT2L_OK;
+    }
+  HostPipe::Input in = {host, bytes, nullptr, 0};
+  int best = -1;
+  for (int k = 0; k < (int)p->pool.size(); ++k)
+    if (p->pool[k].cap >= bytes && (best < 0 || p->pool[k].cap < p->pool[best].cap)) best = k;
+  if (best >= 0) {
+    in.dev = p->pool[best].dev;
+    in.cap = p->pool[best].cap;
+    p->pool.erase(p->pool.begin() + best);
+  } else {
+    const size_t want = (bytes + ((1u << 20) - 1)) & ~(size_t)((1u << 20) - 1);  // 1 MiB granules
+    if (cudaMalloc(reinterpret_cast<void **>(&in.dev), want) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return GPT2L_ERR_CUDA;
+    }
+    in.cap = want;
+  }
+  if (cudaMemcpyAsync(in.dev, host, bytes, cudaMemcpyHostToDevice, p->s_in) != cudaSuccess) {
+    p->pool.push_back(in);
+    return GPT2L_ERR_CUDA;
+  }
+  p->uploaded_bytes += bytes;
+  p->inputs.push_back(in);
+  *dev = in.dev;
+  return GPT2L_OK;
+}
+
 int async_inputs_done(AsyncCall &c) {
   if (cudaEventRecord(c.s->ev_in, c.p->s_in) != cudaSuccess) return GPT2L_ERR_CUDA;
   return cudaStreamWaitEvent(c.p->s_run, c.s->ev_in, 0) == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
@@ -454,13 +506,13 @@ int gpt2_linear_forward_host_async(float *out, const float *in, const float *w, 
   std::lock_guard<std::mutex> lk(g_stage_mu);
   AsyncCall c;
   AK(async_begin(ctx, &c));
-  AK(async_stage(c, 0, in, M * K));
-  AK(async_stage(c, 1, w, (size_t)K * N));
+  float *d_in = nullptr, *d_w = nullptr, *d_b = nullptr;
+  AK(async_input(c, in, M * K, &d_in));
+  AK(async_input(c, w, (size_t)K * N, &d_w));
+  if (b) AK(async_input(c, b, (size_t)N, &d_b));
   AK(async_stage(c, 2, nullptr, M * N));
-  if (b) AK(async_stage(c, 3, b, (size_t)N));
   AK(async_inputs_done(c));
-  AK(gpt2_linear_forward(c.s->buf[2], c.s->buf[0], c.s->buf[1], b ? c.s->buf[3] : nullptr, B, S, K, N, opts,
-                         c.p->s_run));
+  AK(gpt2_linear_forward(c.s->buf[2], d_in, d_w, d_b, B, S, K, N, opts, c.p->s_run));
   AK(async_compute_done(c));
   AK(async_out(c, out, 2, M * N));
   return async_end(c);
@@ -477,11 +529,12 @@ int gpt2_linear_backward_input_host_async(float *g_in, const float *g_out, const
   std::lock_guard<std::mutex> lk(g_stage_mu);
   AsyncCall c;
   AK(async_begin(ctx, &c));
-  AK(async_stage(c, 0, g_out, M * N));
-  AK(async_stage(c, 1, w, (size_t)K * N));
+  float *d_go = nullptr, *d_w = nullptr;
+  AK(async_input(c, g_out, M * N, &d_go));
+  AK(async_input(c, w, (size_t)K * N, &d_w));
   AK(async_stage(c, 2, nullptr, M * K));
   AK(async_inputs_done(c));
-  AK(gpt2_linear_backward_input(c.s->buf[2], c.s->buf[0], c.s->buf[1], B, S, K, N, opts, c.p->s_run));
+  AK(gpt2_linear_backward_input(c.s->buf[2], d_go, d_w, B, S, K, N, opts, c.p->s_run));
   AK(async_compute_done(c));
   AK(async_out(c, g_in, 2, M * K));
   return async_end(c);
@@ -497,13 +550,14 @@ int gpt2_linear_backward_weight_host_async(float *g_w, float *g_b, const float *
   std::lock_guard<std::mutex> lk(g_stage_mu);
   AsyncCall c;
   AK(async_begin(ctx, &c));
-  AK(async_stage(c, 0, in, M * K));
-  AK(async_stage(c, 1, g_out, M * N));
+  float *d_in = nullptr, *d_go = nullptr;
+  AK(async_input(c, in, M * K, &d_in));
+  AK(async_input(c, g_out, M * N, &d_go));
   AK(async_stage(c, 2, nullptr, (size_t)K * N));
   if (g_b) AK(async_stage(c, 3, nullptr, (size_t)N));
   AK(async_inputs_done(c));
-  AK(gpt2_linear_backward_weight(c.s->buf[2], g_b ? c.s->buf[3] : nullptr, c.s->buf[1], c.s->buf[0], B, S, K, N,
-                                 opts, c.p->s_run));
+  AK(gpt2_linear_backward_weight(c.s->buf[2], g_b ? c.s->buf[3] : nullptr, d_go, d_in, B, S, K, N, opts,
+                                 c.p->s_run));
   AK(async_compute_done(c));
   AK(async_out(c, g_w, 2, (size_t)K * N));
   if (g_b) AK(async_out(c, g_b, 3, (size_t)N));
@@ -520,6 +574,9 @@ int gpt2_linear_host_synchronize(void) {
     if (cudaStreamSynchronize(p->s_in) != cudaSuccess || cudaStreamSynchronize(p->s_run) != cudaSuccess ||
         cudaStreamSynchronize(p->s_out) != cudaSuccess)
       return GPT2L_ERR_CUDA;
+    // the window is over: inputs may change now, so their device copies are only storage from here on
+    for (auto &i : p->inputs) p->pool.push_back(i);
+    p->inputs.clear();
   }
   Status s;
   int e = read_status(ctx, &s, true);

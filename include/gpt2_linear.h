@@ -138,9 +138,11 @@ int gpt2_linear_backward_weight_host(float *g_w, float *g_b, const float *g_out,
  * its work — copies in on one internal stream, the kernel on a second, copies out on a third, two sets
  * of staging buffers in rotation — and returns; the host->device copies of the next call then overlap
  * this call's kernel and its device->host copies (PCIe carries both directions at once). Output
- * buffers hold their results, and input buffers may be changed, only after
+ * buffers hold their results, and input buffers may be changed or freed, only after
  * gpt2_linear_host_synchronize(), which waits for everything enqueued on the current device and
- * returns the device status like the *_host calls. Use pinned host memory (pageable memory makes the
+ * returns the device status like the *_host calls. An input buffer handed to several calls between two
+ * synchronisations (same address and size: a weight used by forward and backward_input, activations used
+ * by forward and backward_weight) is copied to the device once. Use pinned host memory (pageable memory makes the
  * copies synchronous). Epilogue operands (opts->aux, GELU dual store) are device pointers and are
  * not supported here. The reference has no host-buffer path at all.
  */

@@ -264,9 +264,10 @@ def test_pipelined_host_calls_match_the_blocking_ones(gpu, orc):
         assert gpu.forward_host_async(hy, hx, hw, hb, 1, M, K, N, o) == 0
         assert gpu.backward_input_host_async(hdx, hdy, hw, 1, M, K, N, o) == 0
         assert gpu.backward_weight_host_async(hdw, hdb, hdy, hx, 1, M, K, N, o) == 0
-        jobs.append((x, w, b, dy, hy, hdx, hdw, hdb))
+        # inputs stay alive (and unchanged) until the synchronise, as the contract of the calls demands
+        jobs.append((x, w, b, dy, hy, hdx, hdw, hdb, (hx, hw, hb, hdy)))
     assert gpu.host_synchronize() == 0
-    for x, w, b, dy, hy, hdx, hdw, hdb in jobs:
+    for x, w, b, dy, hy, hdx, hdw, hdb, _inputs in jobs:
         check_all(orc, (hy.numpy(), hdx.numpy(), hdw.numpy(), hdb.numpy()), x, w, b, dy, TIGHT[1])
     assert gpu.host_synchronize() == 0  # nothing pending: returns at once
     # no bias / no bias gradient (the lm_head case), through a staging set that has held larger operands
@@ -279,6 +280,11 @@ def test_pipelined_host_calls_match_the_blocking_ones(gpu, orc):
     assert gpu.host_synchronize() == 0
     assert orc.max_rel_err(hy.numpy(), orc.forward(x, w, None, f64=True)) <= TIGHT[1]
     assert orc.max_rel_err(hdw.numpy(), orc.backward_weight(dy, x, want_bias=False, f64=True)[0]) <= TIGHT[1]
+    # an input is uploaded once per window; after the synchronise it may change, and the next window sees it
+    hx.mul_(2.0)
+    assert gpu.forward_host_async(hy, hx, hw, None, 1, 130, 36, 68, o) == 0
+    assert gpu.host_synchronize() == 0
+    assert orc.max_rel_err(hy.numpy(), orc.forward(2.0 * x, w, None, f64=True)) <= TIGHT[1]
     hx, hw, hb = pin(seeded(512, 128, 192, seed=42)[0]), pin(seeded(512, 128, 192, seed=42)[1]), pin(seeded(512, 128, 192, seed=42)[2])
     hy = _t.empty((512, 192)).pin_memory()
     bad = gpu.make_opts(mode=1, aux=1 << 20, aux_op=gpu.AUX_ADD)
