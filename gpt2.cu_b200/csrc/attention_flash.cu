@@ -17,12 +17,13 @@
 // MMA's operand fetch from shared memory is what bounds these small-N products: about 105 bytes per
 // ns per SM measured, so a 128 x 64 x 8 MMA with both operands in shared memory costs ~55 ns and one
 // with A in TMEM a third of the bytes): warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
-// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs (the backward modes: warp 1 the
-// score MMAs, warp 2 the accumulate MMAs), the remaining 4 (backward: 8) warps do the row work.
-// Score buffers rotate through three TMEM slots (the score MMAs of block t+1 run while the row work
-// of block t is in progress and the accumulate MMAs of block t-1 may still be reading their slot),
-// operand stages are double-buffered, FWD runs two CTAs per SM, and the backward modes split a step's
-// columns between two sets of row-work warps.
+// tensor maps, nothing is copied or transposed), warp 1 issues the MMAs (BWD_KV: warp 1 the score MMAs,
+// warp 2 the accumulate MMAs), the remaining 4 (BWD_KV: 8) warps do the row work.
+// In FWD and BWD_KV score buffers rotate through three TMEM slots (the score MMAs of block t+1 run while
+// the row work of block t is in progress and the accumulate MMAs of block t-1 may still be reading their
+// slot) and operand stages are double-buffered. FWD and BWD_Q run two CTAs per SM (BWD_Q with one stage
+// and one slot, so that it fits twice); BWD_KV, one CTA per SM, splits a step's columns between two sets
+// of row-work warps and issues its MMAs from two warps.
 //
 // Operands are fp32 read as TF32 by the tensor core; P and dS are rounded to TF32 (to nearest) before
 // they are written back, so the second contraction carries no truncation bias. The reference computes the
