@@ -13,10 +13,10 @@
 // with P = 2^(S * log2(e)/8 - lse) recomputed in the backward modes and delta = rowsum(dO o O).
 // All three are "score MMAs into TMEM -> the row-work threads read their TMEM row, turn it into P / dS
 // and write it back over the scores (tcgen05.st) -> accumulate MMAs that take that tile as their A
-// operand straight from TMEM", so they share one skeleton; P and dS never touch shared memory (an
-// MMA's operand fetch from shared memory is what bounds these small-N products: about 105 bytes per
-// ns per SM measured, so a 128 x 64 x 8 MMA with both operands in shared memory costs ~55 ns and one
-// with A in TMEM a third of the bytes): warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
+// operand straight from TMEM", so they share one skeleton; P and dS never touch shared memory, which
+// saves the 32 KiB tile per step, its stores and the proxy fence they would need, and leaves the room
+// for double-buffered operand stages (measured: a 128 x 64 x 8 TF32 MMA costs about 75 ns from one CTA
+// wherever its A operand lives; two resident CTAs overlap to about 38 ns each): warp 0 loads operands with TMA straight out of qkv[B*T][3C] / dout[B*T][C] (batched
 // tensor maps, nothing is copied or transposed), warp 1 issues the MMAs (BWD_KV: warp 1 the score MMAs,
 // warp 2 the accumulate MMAs), the remaining 4 (BWD_KV: 8) warps do the row work.
 // In FWD and BWD_KV score buffers rotate through three TMEM slots (the score MMAs of block t+1 run while
