@@ -44,7 +44,7 @@ EXPORTS = [
     "gpt2_linear_last_status",
     "gpt2_linear_forward", "gpt2_linear_backward_input", "gpt2_linear_backward_weight",
     "gpt2_linear_forward_host", "gpt2_linear_backward_input_host", "gpt2_linear_backward_weight_host",
-    "gpt2_linear_backward_weight_noalloc",
+    "gpt2_linear_backward_weight_noalloc", "gpt2_linear_noalloc_last_status", "gpt2_linear_noalloc_debug_set_status",
     "gpt2_linear_forward_host_async", "gpt2_linear_backward_input_host_async",
     "gpt2_linear_backward_weight_host_async", "gpt2_linear_host_synchronize",
     "gpt2_schedule_create", "gpt2_schedule_destroy", "gpt2_schedule_validate", "gpt2_schedule_describe",
@@ -144,6 +144,10 @@ def _load():
         f = getattr(lib, name)
         f.argtypes = [P, P, P, P, I, I, I, I, OP, V]
         f.restype = I
+    lib.gpt2_linear_noalloc_last_status.argtypes = [ctypes.POINTER(I * 6)]
+    lib.gpt2_linear_noalloc_last_status.restype = I
+    lib.gpt2_linear_noalloc_debug_set_status.argtypes = [ctypes.POINTER(I * 6)]
+    lib.gpt2_linear_noalloc_debug_set_status.restype = I
     lib.gpt2_linear_forward_host_async.argtypes = [P, P, P, P, I, I, I, I, OP]
     lib.gpt2_linear_forward_host_async.restype = I
     lib.gpt2_linear_backward_input_host_async.argtypes = [P, P, P, I, I, I, I, OP]
@@ -303,6 +307,18 @@ def backward_weight_noalloc(g_w, g_b, g_out, x, B, S, K, N, opts=None, stream=No
     fixed array in the library image (for callers that must not allocate device memory)."""
     return lib.gpt2_linear_backward_weight_noalloc(_p(g_w), _p(g_b), _p(g_out), _p(x), B, S, K, N,
                                                    ctypes.byref(opts) if opts else None, stream)
+
+
+def noalloc_last_status():
+    """gpt2_linear_noalloc_last_status: (status word, record) of the no-allocation path; clears a non-zero record."""
+    rec = (ctypes.c_int * 6)()
+    st = lib.gpt2_linear_noalloc_last_status(ctypes.byref(rec))
+    return st, list(rec)
+
+
+def noalloc_debug_set_status(rec):
+    arr = (ctypes.c_int * 6)(*rec)
+    return lib.gpt2_linear_noalloc_debug_set_status(ctypes.byref(arr))
 
 
 def last_status():

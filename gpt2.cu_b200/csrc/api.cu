@@ -117,6 +117,9 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   int err;
   DeviceCtx *ctx = ctx_current(&err);
   if (!ctx) return err;
+  // a kernel of an earlier call gave up on a wait: nothing more is launched (it would unwind at its
+  // first wait anyway) until gpt2_linear_last_status() has read and cleared the record
+  if (*reinterpret_cast<volatile int *>(ctx->h_flag) != 0) return GPT2L_DEV_TIMEOUT;
   if (d.M <= 0 || d.K <= 0 || d.N <= 0 || !d.out || !d.a || !d.b) return GPT2L_ERR_BAD_ARG;
   if (d.opts.mode != GPT2L_MODE_TF32 && d.opts.mode != GPT2L_MODE_TF32X3) return GPT2L_ERR_BAD_ARG;
   if ((long long)d.M * d.N >= (1ll << 40) || (long long)d.M * d.K >= (1ll << 40)) return GPT2L_ERR_TOO_LARGE;
@@ -192,7 +195,13 @@ static int read_status(DeviceCtx *ctx, Status *out, bool clear) {
   if (cudaMemcpy(ctx->h_status, ctx->d_status, sizeof(Status), cudaMemcpyDeviceToHost) != cudaSuccess)
     return GPT2L_ERR_CUDA;
   *out = *ctx->h_status;
-  if (clear && out->status != 0) cudaMemset(ctx->d_status, 0, sizeof(Status));
+  // the flag alone is set when the launch that gave up kept its record elsewhere (a schedule's own status)
+  const int flag = *reinterpret_cast<volatile int *>(ctx->h_flag);
+  if (out->status == 0 && flag != 0) out->status = flag;
+  if (clear && out->status != 0) {
+    cudaMemset(ctx->d_status, 0, sizeof(Status));
+    *reinterpret_cast<volatile int *>(ctx->h_flag) = 0;
+  }
   return GPT2L_OK;
 }
 
@@ -231,6 +240,10 @@ int gpt2_linear_init(int device) {
   if (cudaMalloc(reinterpret_cast<void **>(&c.d_status), sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;
   cudaMemset(c.d_status, 0, sizeof(Status));
   if (cudaMallocHost(reinterpret_cast<void **>(&c.h_status), sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;
+  if (cudaHostAlloc(reinterpret_cast<void **>(&c.h_flag), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+      cudaHostGetDevicePointer(reinterpret_cast<void **>(&c.d_flag), c.h_flag, 0) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  *c.h_flag = 0;
   if (cudaMalloc(reinterpret_cast<void **>(&c.ws_sem), SEM_COUNT * sizeof(unsigned)) != cudaSuccess)
     return GPT2L_ERR_CUDA;
   cudaMemset(c.ws_sem, 0, SEM_COUNT * sizeof(unsigned));
@@ -250,6 +263,7 @@ void gpt2_linear_shutdown(void) {
     cudaDeviceSynchronize();
     cudaFree(c.d_status);
     cudaFreeHost(c.h_status);
+    cudaFreeHost(c.h_flag);
     cudaFree(c.ws_sem);
     if (c.ws) cudaFree(c.ws);
     if (c.xt) cudaFree(c.xt);

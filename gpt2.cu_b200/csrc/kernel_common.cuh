@@ -82,6 +82,18 @@ static __device__ __noinline__ void raise_timeout(Ctrl *ctrl, const LaunchParams
     p.status->expected = expected;
     p.status->where = site;
     __threadfence();
+    if (p.sticky && atomicCAS(&p.sticky->status, 0, GPT2L_DEV_TIMEOUT) == 0) {
+      p.sticky->op = op;
+      p.sticky->counter = idx;
+      p.sticky->seen = seen;
+      p.sticky->expected = expected;
+      p.sticky->where = site;
+      __threadfence();
+    }
+    if (p.host_flag) {
+      *reinterpret_cast<volatile int *>(p.host_flag) = GPT2L_DEV_TIMEOUT;
+      __threadfence_system();
+    }
   }
 }
 

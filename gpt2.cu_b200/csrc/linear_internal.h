@@ -122,6 +122,13 @@ struct LaunchParams {
   unsigned *counters;
   long long wait_limit_ns;
   int xform_active;  // 0: no op needs the transform warps (TF32 mode, no fused bias gradient)
+  // Where a wait that gives up is recorded besides `status`, both optional:
+  //   sticky     a second record in device memory that launches never clear (only its reader does), so a
+  //              timeout survives the per-call reset of `status`;
+  //   host_flag  an int in mapped pinned host memory: the host sees it without a synchronisation and the
+  //              next entry-point call returns the status instead of launching.
+  Status *sticky;
+  int *host_flag;
 };
 
 // Host-side description of a batched, strided GEMM C_b[Mc][Nc] = A_b . B_b (no bias, no split).
@@ -172,6 +179,9 @@ struct DeviceCtx {
   int max_pairs = 0;                // resident CTA pairs (cluster size 2)
   Status *d_status = nullptr;       // device
   Status *h_status = nullptr;       // pinned host mirror
+  int *h_flag = nullptr;            // mapped pinned int the kernels raise on a timeout (see LaunchParams)
+  int *d_flag = nullptr;            // its device-side address
+  Status *sticky = nullptr;         // optional second record (the no-allocation path)
   float *ws = nullptr;              // split-K workspace
   size_t ws_bytes = 0;
   unsigned *ws_sem = nullptr;

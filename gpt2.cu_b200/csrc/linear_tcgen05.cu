@@ -840,6 +840,8 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.n_ops = 1;
   p.total_tiles = op.n_tiles;
   p.status = ctx->d_status;
+  p.sticky = ctx->sticky;
+  p.host_flag = ctx->d_flag;
   p.counters = nullptr;
   p.wait_limit_ns = default_wait_limit_ns();
   p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
@@ -859,13 +861,14 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
 
 int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid, bool any_3x, bool any_colsum,
                 bool pair, Status *d_status, unsigned *d_counters, long long wait_limit_ns, cudaStream_t stream) {
-  (void)ctx;
   static GemmOp dummy;  // the by-value slot is unused when a list is given
   LaunchParams p;
   p.ops = d_ops;
   p.n_ops = n_ops;
   p.total_tiles = total_tiles;
   p.status = d_status;
+  p.sticky = nullptr;
+  p.host_flag = ctx ? ctx->d_flag : nullptr;
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
   p.xform_active = (any_3x || any_colsum) ? 1 : 0;

@@ -22,11 +22,14 @@
 namespace g2l {
 namespace {
 
-constexpr size_t NA_STATUS_BYTES = 256;   // device status record of this path
+// layout of the array: [status of the call in flight | arrival counters | kept status | partial tiles]
+constexpr size_t NA_STATUS_BYTES = 256;   // status record the kernels of the current call poll; zeroed per call
 constexpr size_t NA_SEM_COUNT = 16384;    // arrival counters: 4 per output tile
 constexpr size_t NA_SEM_BYTES = NA_SEM_COUNT * sizeof(unsigned);
+constexpr size_t NA_KEPT_BYTES = 256;     // first timeout record since the last read; calls never clear it
 constexpr size_t NA_WS_BYTES = GPT2L_NOALLOC_MAX_WORKSPACE_BYTES;
-constexpr size_t NA_TOTAL_BYTES = NA_STATUS_BYTES + NA_SEM_BYTES + NA_WS_BYTES;
+constexpr size_t NA_WS_OFFSET = NA_STATUS_BYTES + NA_SEM_BYTES + NA_KEPT_BYTES;
+constexpr size_t NA_TOTAL_BYTES = NA_WS_OFFSET + NA_WS_BYTES;
 
 // The scratch itself. In HOST code this name is only a handle for cudaGetSymbolAddress — it is not
 // a device address and must never be handed to a kernel as one.
@@ -129,9 +132,11 @@ extern "C" int gpt2_linear_backward_weight_noalloc(float *g_w, float *g_b, const
 
   Status *status = reinterpret_cast<Status *>(dev->base);
   unsigned *sem = reinterpret_cast<unsigned *>(dev->base + NA_STATUS_BYTES);
-  float *ws = reinterpret_cast<float *>(dev->base + NA_STATUS_BYTES + NA_SEM_BYTES);
+  float *ws = reinterpret_cast<float *>(dev->base + NA_WS_OFFSET);
   // the array keeps whatever the previous call left: the status record and the arrival counters
-  // must start at zero (the partial tiles are fully rewritten before they are read)
+  // must start at zero (the partial tiles are fully rewritten before they are read). The kept record
+  // behind the counters is NOT cleared here: a timeout stays readable through
+  // gpt2_linear_noalloc_last_status() however many calls follow it.
   if (cudaMemsetAsync(dev->base, 0, NA_STATUS_BYTES + NA_SEM_BYTES, st) != cudaSuccess) return GPT2L_ERR_CUDA;
   if (op.splits > 1) {
     op.ws = ws;
@@ -142,8 +147,37 @@ extern "C" int gpt2_linear_backward_weight_noalloc(float *g_w, float *g_b, const
   ctx.num_sms = dev->num_sms;
   ctx.max_pairs = dev->max_pairs;
   ctx.d_status = status;
+  ctx.sticky = reinterpret_cast<Status *>(dev->base + NA_STATUS_BYTES + NA_SEM_BYTES);
   err = launch_single(&ctx, op, st);
   if (err) return err;
   if (g_b) return launch_colsum(g_b, g_out, d.M, d.N, st);
   return GPT2L_OK;
+}
+
+// Reads (and, when it is non-zero, clears) the kept status record of the current device. Synchronises the
+// device's work on the array through the copy; allocates nothing.
+extern "C" int gpt2_linear_noalloc_last_status(int out[6]) {
+  PerDevice *dev = nullptr;
+  int err = setup_current_device(&dev);
+  if (err) return err;
+  Status h;
+  unsigned char *kept = dev->base + NA_STATUS_BYTES + NA_SEM_BYTES;
+  if (cudaMemcpy(&h, kept, sizeof(Status), cudaMemcpyDeviceToHost) != cudaSuccess) return GPT2L_ERR_CUDA;
+  if (h.status != 0 && cudaMemset(kept, 0, sizeof(Status)) != cudaSuccess) return GPT2L_ERR_CUDA;
+  if (out) {
+    out[0] = h.status; out[1] = h.op; out[2] = h.counter; out[3] = h.seen; out[4] = h.expected; out[5] = h.where;
+  }
+  return h.status;
+}
+
+// Test hook: writes a record into the kept status slot from the host, so that the reader above can be
+// exercised without making any kernel give up on a wait.
+extern "C" int gpt2_linear_noalloc_debug_set_status(const int rec[6]) {
+  if (!rec) return GPT2L_ERR_BAD_ARG;
+  PerDevice *dev = nullptr;
+  int err = setup_current_device(&dev);
+  if (err) return err;
+  Status h = {rec[0], rec[1], rec[2], rec[3], rec[4], rec[5]};
+  return cudaMemcpy(dev->base + NA_STATUS_BYTES + NA_SEM_BYTES, &h, sizeof(Status), cudaMemcpyHostToDevice) ==
+                 cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }

@@ -13,6 +13,17 @@ import torch
 import torch.distributed as dist
 
 
+def compute_stream(handle=None):
+    """The torch stream object for a raw cudaStream_t handle (None / 0 = torch's current stream), so that
+    events and collectives are ordered against the stream the model's kernels are actually enqueued on."""
+    if not handle:
+        return torch.cuda.current_stream()
+    cur = torch.cuda.current_stream()
+    if cur.cuda_stream == handle:
+        return cur
+    return torch.cuda.ExternalStream(handle)
+
+
 def plan_buckets(named_sizes, bucket_bytes):
     """Groups (name, numel) pairs, kept in the given order, into buckets of at most
     `bucket_bytes` (fp32); a tensor larger than the limit gets a bucket of its own.
@@ -44,7 +55,9 @@ class GradientExchange:
         self.pending = []
         self.calls = 0
 
-    def exchange(self, tensors):
+    def exchange(self, tensors, stream=None, tag=None):
+        """`stream`: raw handle of the stream the producing kernels were enqueued on (default: torch's
+        current stream). `tag` is handed back by wait_next()."""
         if self.world == 1:
             return
         tensors = [t for t in tensors if t is not None]
@@ -55,23 +68,36 @@ class GradientExchange:
             if self.comm_stream is None:
                 self.comm_stream = torch.cuda.Stream()
             ready = torch.cuda.Event()
-            ready.record()
+            ready.record(compute_stream(stream))
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
                 for t in tensors:
                     dist.all_reduce(t, op=dist.ReduceOp.AVG, group=self.group)
                 done = torch.cuda.Event()
                 done.record()
-            self.pending.append(done)
+            self.pending.append((done, tag))
         else:
             # gloo has no AVG: sum, then scale
             for t in tensors:
                 dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
                 t.div_(self.world)
+            self.pending.append((None, tag))
 
-    def finish(self):
-        for ev in self.pending:
-            torch.cuda.current_stream().wait_event(ev)
+    def wait_next(self, stream=None):
+        """Makes the compute stream wait for the OLDEST exchange still pending and returns its tag (None when
+        nothing is pending): lets the caller consume buckets in the order they were handed over, e.g. run the
+        optimizer on bucket i while bucket i+1 is still on the links."""
+        if not self.pending:
+            return None
+        ev, tag = self.pending.pop(0)
+        if ev is not None:
+            compute_stream(stream).wait_event(ev)
+        return tag
+
+    def finish(self, stream=None):
+        for ev, _ in self.pending:
+            if ev is not None:
+                compute_stream(stream).wait_event(ev)
         self.pending = []
 
 
@@ -105,7 +131,7 @@ class ShardedExchange:
     def _mine(self, lo, per):
         return lo + self.rank * per, lo + (self.rank + 1) * per
 
-    def reduce(self, lo, hi):
+    def reduce(self, lo, hi, stream=None):
         self.ranges.append((lo, hi))
         if self.world == 1:
             return
@@ -133,7 +159,7 @@ class ShardedExchange:
             if self.comm_stream is None:
                 self.comm_stream = torch.cuda.Stream()
             ready = torch.cuda.Event()
-            ready.record()
+            ready.record(compute_stream(stream))
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(ready)
                 issue()
@@ -143,9 +169,9 @@ class ShardedExchange:
         else:
             issue()
 
-    def finish(self):
+    def finish(self, stream=None):
         for ev in self.pending:
-            torch.cuda.current_stream().wait_event(ev)
+            compute_stream(stream).wait_event(ev)
         self.pending = []
 
     def owned(self):
@@ -164,17 +190,28 @@ class ShardedExchange:
                 out.append((body_end, hi - body_end))
         return out
 
-    def gather(self):
-        """After the update of owned(): every rank receives the other ranks' parameter slices."""
+    def gather(self, stream=None):
+        """After the update of owned(): every rank receives the other ranks' parameter slices (issued on
+        the compute stream, behind the update kernels)."""
         if self.world > 1:
-            for lo, hi in self.ranges:
-                per, body_end = shard_bounds(lo, hi, self.world)
-                if not per:
-                    continue
-                a, b = self._mine(lo, per)
-                src = self.params[a:b] if self.params.is_cuda else self.params[a:b].clone()
-                dist.all_gather_into_tensor(self.params[lo:body_end], src, group=self.group)
+            ctx = torch.cuda.stream(compute_stream(stream)) if self.params.is_cuda else _NullContext()
+            with ctx:
+                for lo, hi in self.ranges:
+                    per, body_end = shard_bounds(lo, hi, self.world)
+                    if not per:
+                        continue
+                    a, b = self._mine(lo, per)
+                    src = self.params[a:b] if self.params.is_cuda else self.params[a:b].clone()
+                    dist.all_gather_into_tensor(self.params[lo:body_end], src, group=self.group)
         self.ranges = []
+
+
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
 
 
 class _DeviceView:
@@ -197,8 +234,10 @@ class DataParallelStep:
     averaged across ranks in buckets, in the order the backward pass completes them — ln_f with the
     last block, then one bucket per block going down, then wte + wpe after the embedding backward —
     each on the side stream while the next block's backward runs on the compute stream (the
-    backward_weight GEMMs of block l-1 hide the exchange of block l). AdamW runs replicated after the
-    last bucket has landed. With one rank the exchange is a no-op.
+    backward_weight GEMMs of block l-1 hide the exchange of block l). AdamW runs replicated, bucket by
+    bucket in hand-over order as each all-reduce lands (gpt2_model_update_range), so the update of the
+    earlier buckets runs while the last and largest one (wte + wpe) is still on the links. With one rank the
+    exchange is a no-op and the update is one call.
 
     use_graph=True (single rank only): forward + backward are replayed from a CUDA graph
     (gpt2_model_forward_backward_graph), which pays at small shapes where launches dominate.
@@ -235,16 +274,23 @@ class DataParallelStep:
             return rc | m.update(lr, beta1, beta2, eps, weight_decay, t, stream)
         rc = m.forward(tokens, targets, stream)
         rc |= m.backward_head(stream)
+        if self.exchange.world == 1:
+            for l in range(self.L - 1, -1, -1):
+                rc |= m.backward_layer(l, stream)
+            rc |= m.backward_embedding(stream)
+            return rc | m.update(lr, beta1, beta2, eps, weight_decay, t, stream)
         for l in range(self.L - 1, -1, -1):
             rc |= m.backward_layer(l, stream)
-            bucket = [self._slice(self.block[l])]
-            if l == self.L - 1:
-                bucket.append(self._slice(self.lnf))
-            self.exchange.exchange(bucket)
+            ranges = [self.block[l]] + ([self.lnf] if l == self.L - 1 else [])
+            self.exchange.exchange([self._slice(r) for r in ranges], stream, tag=ranges)
         rc |= m.backward_embedding(stream)
-        self.exchange.exchange([self._slice(self.embed)])
-        self.exchange.finish()
-        rc |= m.update(lr, beta1, beta2, eps, weight_decay, t, stream)
+        self.exchange.exchange([self._slice(self.embed)], stream, tag=[self.embed])
+        while True:
+            ranges = self.exchange.wait_next(stream)
+            if ranges is None:
+                break
+            for lo, hi in ranges:
+                rc |= m.update_range(lo, hi - lo, lr, beta1, beta2, eps, weight_decay, t, stream)
         return rc
 
     def _sharded_step(self, tokens, targets, lr, beta1, beta2, eps, weight_decay, t, stream):
@@ -253,13 +299,13 @@ class DataParallelStep:
         rc |= m.backward_head(stream)
         for l in range(self.L - 1, -1, -1):
             rc |= m.backward_layer(l, stream)
-            sx.reduce(*self.block[l])
+            sx.reduce(*self.block[l], stream=stream)
             if l == self.L - 1:
-                sx.reduce(*self.lnf)
+                sx.reduce(*self.lnf, stream=stream)
         rc |= m.backward_embedding(stream)
-        sx.reduce(*self.embed)
-        sx.finish()
+        sx.reduce(*self.embed, stream=stream)
+        sx.finish(stream)
         for first, count in sx.owned():
             rc |= m.update_range(first, count, lr, beta1, beta2, eps, weight_decay, t, stream)
-        sx.gather()
+        sx.gather(stream)
         return rc

@@ -86,7 +86,11 @@ int gpt2_linear_version(void);
 /* Number of kernel launches this library issued since init (all entry points). */
 long long gpt2_linear_launch_count(void);
 /* Last device status record of the current device: {status, op, counter, seen, expected,
- * where}. Returns the status word. out may be NULL. */
+ * where}. Returns the status word and clears a non-zero record. out may be NULL.
+ * A kernel that gives up on a wait also raises a flag in host-visible memory: from then on every
+ * device-pointer entry point returns GPT2L_DEV_TIMEOUT without launching anything, until this
+ * function has been called. (Callers through include/compat ignore return codes, as the
+ * reference's kernels have none; they can poll this function instead.) */
 int gpt2_linear_last_status(int out[6]);
 
 /*
@@ -159,13 +163,21 @@ int gpt2_linear_host_synchronize(void);
  * Weight gradient for callers that may not allocate device memory. (No counterpart in the
  * reference, which allocates everything up front and has no split-K.)
  *
- * Computes exactly what gpt2_linear_backward_weight computes with opts->deterministic = 1 — the
+ * Computes what gpt2_linear_backward_weight computes with opts->deterministic = 1 — the
  * reduction over M split into chunks whose partial tiles are combined in a fixed order — but keeps
  * the partial tiles in a fixed array inside the library image instead of a cudaMalloc'ed
- * workspace. Use it from code that runs after a server has given the whole GPU to its own memory
- * pool, from loops that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply,
- * or wherever a driver allocation at call time is simply forbidden. It does not need
- * gpt2_linear_init() and calls no cudaMalloc, cudaFree or other allocating routine, ever.
+ * workspace. With the same tiling and split count the two results are bit-identical; they differ
+ * in the last bits where the regular call picks another arrangement (wide weights, N >= 8192 and
+ * N >= 8 K, which it computes from a transposed copy of `in`) or where the split count had to be
+ * lowered to fit the array. Use it from code that runs after a server has given the whole GPU to
+ * its own memory pool, from loops that cannot afford the device-wide synchronisation cudaMalloc /
+ * cudaFree imply, or wherever a driver allocation at call time is simply forbidden. It does not
+ * need gpt2_linear_init() and calls no cudaMalloc, cudaFree or other allocating routine.
+ * One caveat on "allocates nothing": the array belongs to the library's CUDA module, and with
+ * CUDA's default lazy module loading the driver reserves device memory for the module when the
+ * first call on a device touches it. Make that first call (or set CUDA_MODULE_LOADING=EAGER)
+ * before the application's pool takes what is left of the device; a first call made later fails
+ * with GPT2L_ERR_CUDA if the driver cannot place the module.
  *
  * Limits and rules:
  *   - the partial tiles (splits x ceil(K/128) x ceil(N/bn) tiles of 128 x bn floats) must fit in
@@ -179,12 +191,21 @@ int gpt2_linear_host_synchronize(void);
  *     each call re-zeroes the part that must start at zero, on the caller's stream. Two calls whose
  *     kernels overlap on the GPU (different streams, or different threads) race on it: serialise
  *     them. Every GPU that loads the library holds the array until the process exits;
- *   - opts->flags and opts->out2 are ignored; opts->mode and opts->split_k are honoured.
+ *   - opts->flags and opts->out2 are ignored; opts->mode and opts->split_k are honoured;
+ *   - the kernels' status record lives in the array too. A wait that gives up (it never should) is
+ *     kept there, across later calls, until gpt2_linear_noalloc_last_status() reads it; that call
+ *     returns the status word (0 = every call since the last read completed), fills
+ *     {status, op, counter, seen, expected, where} and clears a non-zero record. It synchronises
+ *     with the device and allocates nothing.
  */
 #define GPT2L_NOALLOC_MAX_WORKSPACE_BYTES (32u << 20)
 int gpt2_linear_backward_weight_noalloc(float *g_w, float *g_b, const float *g_out, const float *in,
                                         int B, int S, int K, int N,
                                         const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+int gpt2_linear_noalloc_last_status(int out[6]);
+/* Test hook for the reader above: stores a record in the kept slot from the host (no kernel runs,
+ * no device fault is provoked). */
+int gpt2_linear_noalloc_debug_set_status(const int rec[6]);
 
 /* ------------------------------------------------------------------------------------
  * Megakernel side: one persistent launch that runs a list of GEMM ops whose tiles are

@@ -11,13 +11,18 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle_linear.so")
 REF_SO = os.path.join(HERE, "_ref", "libref_mlp.so")
 REF_TRAIN_SO = os.path.join(HERE, "_ref", "libref_train.so")
+REF_TRAIN_B200_SO = os.path.join(HERE, "_ref", "libref_train_b200.so")
 
 
-def build(reference_root="/root/reference"):
-    """make the CPU oracle; make the reference-kernel library too when the reference tree exists."""
+def build(reference_root=None):
+    """make the CPU oracle; make the reference-kernel libraries too when a reference checkout is named
+    (argument, or the environment variable GPT2CU_REFERENCE) and exists."""
     subprocess.run(["make", "-C", HERE], check=True, capture_output=True)
-    if os.path.exists(os.path.join(reference_root, "include", "gpt2", "layers", "mlp.h")):
-        subprocess.run(["make", "-C", HERE, "ref", f"REF={reference_root}"], check=True, capture_output=True)
+    reference_root = reference_root or os.environ.get("GPT2CU_REFERENCE")
+    if reference_root and os.path.exists(os.path.join(reference_root, "include", "gpt2", "layers", "mlp.h")):
+        res = subprocess.run(["make", "-C", HERE, "ref", f"REF={reference_root}"], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("make ref failed:\n" + res.stdout[-2000:] + res.stderr[-4000:])
 
 
 _lib = None
@@ -173,5 +178,40 @@ def ref_train_lib():
         L.ref_train_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         L.ref_train_step.restype = ctypes.c_float
         L.ref_train_sync.restype = ctypes.c_int
+        _bind_train(L)
         _ref_train = L
     return _ref_train
+
+
+def _bind_train(L):
+    P, I = ctypes.c_void_p, ctypes.c_int
+    L.ref_train_forward_backward.argtypes = [P, P]
+    L.ref_train_forward_backward.restype = ctypes.c_float
+    L.ref_train_get_grads.argtypes = [P, ctypes.c_longlong]
+    L.ref_train_get_grads.restype = I
+    L.ref_attention_forward.argtypes = [P, P, P, P, I, I, I, I]
+    L.ref_attention_forward.restype = I
+    L.ref_attention_backward.argtypes = [P, P, P, P, P, P, I, I, I, I]
+    L.ref_attention_backward.restype = I
+
+
+_ref_train_b200 = None
+
+
+def ref_train_b200_lib():
+    """The same training step with its 15 linear-layer launch sites rewritten to this library's launchers
+    (oracle/Makefile target _ref/libref_train_b200.so), or None when it was not built. One model per process."""
+    global _ref_train_b200
+    if _ref_train_b200 is None and os.path.exists(REF_TRAIN_B200_SO):
+        L = ctypes.CDLL(REF_TRAIN_B200_SO)
+        L.ref_train_create.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_uint]
+        L.ref_train_create.restype = ctypes.c_int
+        L.ref_train_num_params.restype = ctypes.c_longlong
+        L.ref_train_set_params.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
+        L.ref_train_set_params.restype = ctypes.c_int
+        L.ref_train_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        L.ref_train_step.restype = ctypes.c_float
+        L.ref_train_sync.restype = ctypes.c_int
+        _bind_train(L)
+        _ref_train_b200 = L
+    return _ref_train_b200

@@ -1,6 +1,6 @@
 """Generates the golden fixtures of the linear-layer GEMMs from the reference's own PyTorch model.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 Imports scripts/llm.py of vnnm404/gpt2.cu (from the tree given on the command line), builds two tiny
 GPT models with the reference's seeded init, runs one fp32 forward + backward on CPU with seeded
@@ -104,7 +104,9 @@ def capture(ref_root, name, n_embd, n_head, vocab, B, T, seed):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref = sys.argv[1]
     # every dimension a multiple of 4: the TMA + tcgen05 path
     capture(ref, "llm_tiny_aligned.npz", n_embd=64, n_head=2, vocab=96, B=2, T=24, seed=11)
     # vocabulary 101 and width 36: ragged k-blocks, and an lm_head the TMA path cannot address

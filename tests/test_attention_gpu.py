@@ -119,3 +119,40 @@ def test_flash_attention_properties_at_full_sequence_length(gpu):
     assert torch.isfinite(g3).all()
     assert float(g3[:, 512:].abs().max()) == 0.0
     assert float(g3[:, :512].abs().max()) > 0.0
+
+
+def test_flash_attention_against_the_reference_kernels(gpu, orc):
+    """The fused tensor-core attention against the reference's own attention_forward / attention_backward
+    (src/layers/attention.cu:213-218, 366-371, compiled unmodified into oracle/_ref/libref_train.so) at the
+    benchmarked sequence length: T = 1024, B = 1, 12 heads, seeded inputs. Same tolerances as against the
+    float64 restatement (the reference computes in fp32 with --use_fast_math)."""
+    L = orc.ref_train_lib()
+    if L is None:
+        pytest.skip("oracle/_ref/libref_train.so was not built (no reference tree at build time)")
+    B, T, NH = 1, 1024, 12
+    C = NH * 64
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    qkv = torch.randn((B * T, 3 * C), device="cuda", generator=gen)
+    qkv[:, :C] *= 2.0
+    dout = torch.randn((B * T, C), device="cuda", generator=gen) * 0.1
+    ref_out = torch.zeros((B * T, C), device="cuda")
+    preatt = torch.zeros((B, NH, T, T), device="cuda")
+    att = torch.zeros((B, NH, T, T), device="cuda")
+    g_ref = torch.zeros((B * T, 3 * C), device="cuda")
+    g_preatt, g_att = torch.zeros_like(preatt), torch.zeros_like(att)
+    torch.cuda.synchronize()
+    assert L.ref_attention_forward(ref_out.data_ptr(), preatt.data_ptr(), att.data_ptr(), qkv.data_ptr(), B, T, NH, C) == 0
+    assert L.ref_attention_backward(g_ref.data_ptr(), g_preatt.data_ptr(), g_att.data_ptr(), dout.data_ptr(),
+                                    qkv.data_ptr(), att.data_ptr(), B, T, C, NH) == 0
+    out = torch.full((B * T, C), float("nan"), device="cuda")
+    lse = torch.zeros((B, NH, T), device="cuda")
+    row = torch.zeros((B, NH, T), device="cuda")
+    g = torch.full((B * T, 3 * C), float("nan"), device="cuda")
+    assert gpu.attention_forward(out, lse, None, qkv, B, T, NH, C, gpu.ATT_FLASH, 0) == 0
+    assert gpu.attention_backward(g, dout, qkv, out, lse, None, row, None, B, T, C, NH, gpu.ATT_FLASH, 0) == 0
+    torch.cuda.synchronize()
+    assert gpu.lib.gpt2_attention_status() == 0
+    assert torch.isfinite(out).all() and torch.isfinite(g).all()
+    assert rel(out.cpu().numpy(), ref_out.cpu().numpy()) <= 2e-3
+    for name, sl in (("dq", slice(0, C)), ("dk", slice(C, 2 * C)), ("dv", slice(2 * C, 3 * C))):
+        assert rel(g[:, sl].cpu().numpy(), g_ref[:, sl].cpu().numpy()) <= 3e-3, name

@@ -59,9 +59,16 @@ def _worker(rank, world, port, out, shard):
         want_p = np.empty_like(params)
         full.get_params(want_p)
         eg = np.abs(grads - want_g).max() / np.abs(want_g).max()
-        ep = np.abs(after - want_p).max()
-        # AdamW's first step moves every weight by about lr * sign(g): where g is within rounding of zero
-        # the two runs may disagree on the sign, so the parameters are only required to agree within 2 * lr
+        # AdamW's first step moves a weight by lr * g / (|g| + eps) + lr * wd * p: almost independent of |g|,
+        # so wherever the gradient is clearly non-zero (above 1e-4 of the largest, ten times the bound on the
+        # gradient error itself) the two runs must land on the same parameter to 1e-6. Only where g is within
+        # rounding of zero may the runs disagree on its sign, and there the parameters are within 2 * lr.
+        gmax = np.abs(want_g).max()
+        clear = np.abs(want_g) > 1e-4 * gmax
+        ep_clear = np.abs(after - want_p)[clear].max()
+        ep_rest = np.abs(after - want_p)[~clear].max() if (~clear).any() else 0.0
+        ep = max(ep_clear, ep_rest)
+        out["clear_fraction"] = float(clear.mean())
         calls = step.sharded.calls if shard else step.exchange.calls
         if shard:
             # only this rank's slices hold averaged gradients: compare those
@@ -72,8 +79,21 @@ def _worker(rank, world, port, out, shard):
             for first, count in sx.owned():
                 mask[first:first + count] = True
             eg = np.abs(grads - want_g)[mask].max() / np.abs(want_g).max()
-        ok = bool(eg <= 1e-5 and ep <= 2 * hyper[0] and calls == n_layer + (2 if shard else 1))
-        out["err"] = (float(eg), float(ep), calls)
+        ok = bool(eg <= 1e-5 and ep_clear <= 1e-6 and ep_rest <= 2 * hyper[0] and clear.mean() > 0.5
+                  and calls == n_layer + (2 if shard else 1))
+        out["err"] = (float(eg), float(ep_clear), float(ep_rest), calls)
+    # the update really ran over every range this rank is responsible for (all of them when replicated)
+    moved = after != params
+    if shard:
+        sx = dp.ShardedExchange(torch.zeros(1), torch.zeros(1))
+        sx.world, sx.rank = world, rank
+        sx.ranges = [step.block[l] for l in range(n_layer)] + [step.lnf, step.embed]
+        mine = sx.owned()
+    else:
+        mine = [(lo, hi - lo) for lo, hi in [step.block[l] for l in range(n_layer)] + [step.lnf, step.embed]]
+    for first, count in mine:
+        if count > 0 and np.any(params[first:first + count] != 0):
+            ok = ok and bool(moved[first:first + count].any())
     # every rank holds the same parameters (and, with the all-reduce, the same averaged gradients)
     t = torch.from_numpy(after if shard else grads).cuda()
     ref = t.clone()
@@ -92,4 +112,5 @@ def test_two_gpu_step_equals_one_gpu_step_on_the_whole_batch(gpu, shard):
     mgr = mp.Manager()
     out = mgr.dict()
     mp.spawn(_worker, args=(2, 29600 + os.getpid() % 1000 + int(shard), out, shard), nprocs=2, join=True)
+    print("two-GPU step vs one-GPU step:", dict(out))
     assert out.get(0) and out.get(1), dict(out)

@@ -123,6 +123,17 @@ def test_unsatisfiable_dependency_times_out_cleanly(gpu):
     assert time.time() - t0 < 10.0
     assert sched.status() == gpu.DEV_TIMEOUT
     sched.close()
+    # the timeout raised the host-visible flag: the next device-pointer call refuses to launch and
+    # returns the status, until gpt2_linear_last_status() has read (and cleared) it
+    x = torch.randn((128, 64), device="cuda")
+    w = torch.randn((64, 64), device="cuda")
+    y = torch.empty((128, 64), device="cuda")
+    assert gpu.forward(y, x, w, None, 1, 128, 64, 64, o) == gpu.DEV_TIMEOUT
+    st, _ = gpu.last_status()
+    assert st == gpu.DEV_TIMEOUT
+    assert gpu.last_status()[0] == 0
+    assert gpu.forward(y, x, w, None, 1, 128, 64, 64, o) == 0
+    torch.cuda.synchronize()
     # the device is still usable: a fresh schedule of the same chain runs to completion
     t2, ops2, o2 = mlp_block(gpu, 2, 256, 64, 0)
     s2 = gpu.Schedule(ops2)

@@ -54,7 +54,12 @@ def test_noalloc_weight_gradient_matches_regular_entry_point(gpu, mode):
     torch.cuda.synchronize()
     free_after, _ = torch.cuda.mem_get_info()
     assert free_after == free_before, "the no-allocation entry point changed the amount of free device memory"
-    for (M, K, N, o, x, dy, want_w, want_b, got_w, got_b) in prepared:
+    st, rec = gpu.noalloc_last_status()
+    assert st == 0, rec  # no wait gave up in any of the three calls
+    for i, (M, K, N, o, x, dy, want_w, want_b, got_w, got_b) in enumerate(prepared):
+        if shapes[i][3] > 0:
+            # forced split count: same tiling, same fixed combination order as the regular call
+            assert torch.equal(got_w, want_w)
         assert torch.isfinite(got_w).all() and torch.isfinite(got_b).all()
         assert rel(got_w, want_w) <= TOL[mode]
         assert rel(got_b, want_b) <= TOL[mode]
@@ -78,3 +83,25 @@ def test_noalloc_rejects_what_does_not_fit(gpu):
     truth = x.double().t() @ dy.double()
     assert rel(gw.double(), truth) <= TOL[0]
     assert gpu.backward_weight_noalloc(None, None, dy, x, 1, M, K, N, o) == gpu.ERR_BAD_ARG
+
+
+def test_noalloc_status_record_is_kept_until_read(gpu):
+    """A timeout record of this path must survive later calls and be cleared only by its reader. The
+    record is planted from the host (no kernel is made to give up); two calls follow, then the reader
+    must still return it, and a second read must return 0."""
+    M, K, N = 512, 128, 256
+    x, dy = operands(M, K, N, seed=60)
+    gw = torch.empty((K, N), device="cuda")
+    assert gpu.backward_weight_noalloc(gw, None, dy, x, 1, M, K, N, gpu.make_opts(mode=0)) == 0
+    torch.cuda.synchronize()
+    assert gpu.noalloc_last_status()[0] == 0
+    planted = [gpu.DEV_TIMEOUT, 3, 17, 5, 8, 7]
+    assert gpu.noalloc_debug_set_status(planted) == 0
+    for _ in range(2):
+        assert gpu.backward_weight_noalloc(gw, None, dy, x, 1, M, K, N, gpu.make_opts(mode=0, split_k=2)) == 0
+    torch.cuda.synchronize()
+    truth = x.double().t() @ dy.double()
+    assert rel(gw.double(), truth) <= TOL[0]  # the planted record did not disturb the calls
+    st, rec = gpu.noalloc_last_status()
+    assert st == gpu.DEV_TIMEOUT and rec == planted
+    assert gpu.noalloc_last_status()[0] == 0
