@@ -49,11 +49,6 @@ enum { F_FWD = 0, F_BWD_Q = 1, F_BWD_KV = 2 };
 
 constexpr int TILE_A = FROWS * FHS * 4;   // 32 KiB: [128][64] K-major, two 16 KiB k-blocks
 
-struct FlashMaps {
-  // K-major views [T rows][64] of one head (box 32 x 64) and MN-major views (box 32 x 32 x 2 chunks)
-  CUtensorMap k_major[4];   // Q, K, V, dO
-  CUtensorMap mn_major[4];  // Q, K, V, dO
-};
 enum { X_Q = 0, X_K = 1, X_V = 2, X_DO = 3 };
 
 struct FlashArgs {

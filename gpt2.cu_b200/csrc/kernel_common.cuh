@@ -20,6 +20,8 @@ struct Ctrl {
   uint64_t ready[MAX_STAGES];
   uint64_t tmem_full[NUM_ACC];
   uint64_t tmem_empty[NUM_ACC];
+  uint64_t row_bar;  // step kernel: rendezvous of the eight worker warps
+  uint64_t cta_bar;  // step kernel: rendezvous of every warp of the CTA (attention tiles)
   uint32_t tmem_base;
   int abort;
 };
@@ -45,6 +47,14 @@ __device__ __forceinline__ const GemmOp *decode_tile(const GemmOp *ops, int n_op
   int local = t - op->tile_base;
   tc.bh = 0;
   tc.bb = 0;
+  if (op->op_kind != OPK_GEMM) {  // row-local op or attention: tiles are numbered linearly
+    tc.m_tile = local;
+    tc.n_tile = 0;
+    tc.split = 0;
+    tc.kb0 = tc.kb1 = 0;
+    tc.skip = 0;
+    return op;
+  }
   if (op->batch > 1) {
     const int bi = local / op->tiles_per_batch;
     local -= bi * op->tiles_per_batch;
@@ -148,6 +158,43 @@ __device__ __forceinline__ bool wait_counter(const unsigned *ctr, unsigned expec
   }
 }
 
+// Every dependency of a tile at once (one lane calls this): the counters are probed with independent
+// relaxed loads, so a tile whose producers are done pays one round trip to L2 however many
+// dependencies it has, and one acquire fence orders the tile's reads behind them. Only a counter that
+// is still short is polled (bounded). `rb` is the consumer's 128-row block.
+__device__ __forceinline__ bool wait_deps(const GemmOp *op, int rb, Ctrl *ctrl, const LaunchParams &p) {
+  bool all = true;
+#pragma unroll
+  for (int w = 0; w < MAX_WAITS; ++w) {
+    const int base = op->wait_ctr[w];
+    if (base < 0) continue;
+    const unsigned need = (unsigned)op->wait_expected[w];
+    if (op->wait_kind[w] == DEP_SEQUENCE) {
+      const int n = op->rb_per_seq, first = base + (rb / n) * n;
+      for (int i = 0; i < n; ++i) all &= ld_relaxed(p.counters + first + i) >= need;
+    } else {
+      all &= ld_relaxed(p.counters + base + (op->wait_kind[w] == GPT2L_DEP_ROWBLOCK ? rb : 0)) >= need;
+    }
+  }
+  if (!all) {
+    for (int w = 0; w < MAX_WAITS; ++w) {
+      const int base = op->wait_ctr[w];
+      if (base < 0) continue;
+      const unsigned need = (unsigned)op->wait_expected[w];
+      if (op->wait_kind[w] == DEP_SEQUENCE) {
+        const int n = op->rb_per_seq, first = base + (rb / n) * n;
+        for (int i = 0; i < n; ++i)
+          if (!wait_counter(p.counters + first + i, need, ctrl, p, op->op_index, first + i)) return false;
+      } else {
+        const int idx = base + (op->wait_kind[w] == GPT2L_DEP_ROWBLOCK ? rb : 0);
+        if (!wait_counter(p.counters + idx, need, ctrl, p, op->op_index, idx)) return false;
+      }
+    }
+  }
+  fence_acq_rel_gpu();
+  return true;
+}
+
 // tanh(u) = 1 - 2 / (1 + e^{2u}) on the special-function unit (ex2.approx, rcp.approx): absolute error
 // about 2e-7, which is what GELU needs (it uses 1 + tanh and 1 - tanh^2, never tanh alone); tanhf
 // costs several times as many instructions, and the epilogue warps evaluate 32K of these per tile.
@@ -205,7 +252,8 @@ __device__ __forceinline__ void load_aux(AuxRegs &r, const EpiAux &e, long long 
   for (int i = 0; i < 8; ++i) {
     const int grow = row0 + 4 * i + rr;
     r.a[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (grow < Mc && col < Nc) r.a[i] = __ldg(reinterpret_cast<const float4 *>(e.aux + (long long)grow * ldc + col));
+    // a plain load: inside a schedule the operand may have been written earlier in the same launch
+    if (grow < Mc && col < Nc) r.a[i] = *reinterpret_cast<const float4 *>(e.aux + (long long)grow * ldc + col);
   }
 }
 

@@ -36,7 +36,46 @@ constexpr int EPI_BUF_BYTES = 32 * 32 * 4;                       // one 32 x 32 
 constexpr int EPI_BYTES = NUM_EPI_WARPS * 2 * EPI_BUF_BYTES;    // two boxes per epilogue warp
 constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + RING_BYTES + EPI_BYTES + SMEM_CTRL_BYTES;
 
-constexpr int MAX_WAITS = GPT2L_MAX_DEPS;
+constexpr int MAX_WAITS = 8;  // dependencies per op inside the library (the public gpt2l_op carries GPT2L_MAX_DEPS)
+static_assert(MAX_WAITS >= GPT2L_MAX_DEPS, "public dependency count");
+
+// The persistent step kernel (a whole training step in one launch) runs with one more warp than the
+// GEMM-only kernel: the key/value pass of the attention backward needs two MMA issuers and eight
+// row-work warps besides the producer.
+constexpr int STEP_THREADS = 352;
+constexpr int NUM_WORKER_WARPS = NUM_XFORM_WARPS + NUM_EPI_WARPS;  // warps 2..9: row-local ops run on these
+
+// What an entry of a schedule is. Everything but OPK_GEMM exists only inside the persistent step kernel:
+// the layers between the GEMMs of a training step (src/mk.cu:1155-1810 of the reference lists the same
+// ops as cases of its interpreter), executed as tiles of `rows_per_tile` rows by the eight worker warps.
+enum OpKind : int {
+  OPK_GEMM = 0,
+  OPK_EMBED_FWD = 1,    // out[m][:] = wte[:, tok[m]] + wpe[m % T][:]
+  OPK_LN_FWD = 2,       // out, mean, rstd = layernorm(in) * w + b
+  OPK_XENT = 3,         // losses[m], logits[m][:] <- dlogits (softmax + cross-entropy, in place)
+  OPK_LN_BWD = 4,       // g_in[m][:] += layernorm backward; g_w, g_b += column sums
+  OPK_ROWDOT = 5,       // delta[b][h][t] = sum_d dout[m][h*64+d] * out[m][h*64+d]
+  OPK_EMBED_BWD = 6,    // g_wte[:, tok[m]] += g[m][:]; g_wpe[m % T][:] += g[m][:]
+  OPK_ADAMW = 7,        // AdamW over a range of the flat buffers
+  OPK_ATTN_FWD = 8,     // fused causal attention, forward (tile = 128 query rows of one head)
+  OPK_ATTN_BWD_KV = 9,  //   dK, dV
+  OPK_ATTN_BWD_Q = 10,  //   dQ
+  OPK_TRANSPOSE = 11    // out[c][m] = in[m][c] (K-major copy of activations for wide weight gradients)
+};
+
+// Operands of a non-GEMM op (meaning per kind: see the builder in step_schedule.cu)
+struct RowArgs {
+  const float *in0, *in1, *in2, *in3, *in4;
+  float *out0, *out1, *out2;
+  const int *idx0, *idx1;  // tokens / targets
+  long long n0, n1;        // AdamW: first element and element count of the range
+  int i0, i1, i2, i3, i4;  // M, C, T, V, Vp ... per kind
+  float f0;
+};
+
+// what a dependency waits for, beyond the two public kinds: every 128-row block of the consumer tile's
+// sequence (attention: a query block needs the keys of its whole sequence, a key block every later query)
+constexpr int DEP_SEQUENCE = 3;
 
 // where a bounded wait gave up (status record field `where`)
 enum WaitSite {
@@ -47,7 +86,10 @@ enum WaitSite {
   SITE_SMEM_READY = 4,
   SITE_TMEM_EMPTY = 5,
   SITE_TMEM_FULL = 6,
-  SITE_SPLITK_TURNSTILE = 7
+  SITE_SPLITK_TURNSTILE = 7,
+  SITE_ROW_SYNC = 8,   // rendezvous of the worker warps inside a row-local op
+  SITE_CTA_SYNC = 9,   // rendezvous of the whole CTA around an attention tile
+  SITE_ATTENTION = 16  // + the wait number inside the attention tile code
 };
 
 // Device status record: one per device (single-op calls) or per schedule.
@@ -112,6 +154,19 @@ struct alignas(64) GemmOp {
   unsigned idesc;       // tcgen05 instruction descriptor
   int op_index;
   int layer;
+  // ---- non-GEMM ops of the step kernel ----
+  int op_kind;          // OpKind; 0 = GEMM
+  int rows_per_tile;    // rows one tile covers (divides 128, or a multiple of it); GEMM: 128
+  int rb_per_seq;       // DEP_SEQUENCE: 128-row blocks per sequence (T / 128)
+  int xform;            // this op needs the operand-transform warps (3xTF32 split or fused column sums)
+  RowArgs ra;
+};
+
+// tensor maps of one fused-attention pass (attention_flash.cu): K-major views [T rows][64] of one head
+// (box 32 x 64) and MN-major views (box 32 x 32 x 2 chunks) of Q, K, V (inside qkv) and dO
+struct FlashMaps {
+  CUtensorMap k_major[4];   // Q, K, V, dO
+  CUtensorMap mn_major[4];  // Q, K, V, dO
 };
 
 struct LaunchParams {
@@ -129,6 +184,11 @@ struct LaunchParams {
   //              next entry-point call returns the status instead of launching.
   Status *sticky;
   int *host_flag;
+  // step kernel only: AdamW hyper-parameters of this launch {lr, beta1, beta2, eps, weight_decay,
+  // 1 - beta1^t, 1 - beta2^t}, the tensor maps of the attention ops, and the profile buffer
+  float adam[7];
+  const FlashMaps *fmaps;
+  unsigned long long *prof;  // [total_tiles][2] = {%globaltimer at tile start, SM id << 32 | duration} or null
 };
 
 // Host-side description of a batched, strided GEMM C_b[Mc][Nc] = A_b . B_b (no bias, no split).
@@ -229,7 +289,7 @@ int pair_max_pairs(int num_sms);  // how many CTA pairs can be resident at once
 int pair_launch(const GemmOp *op_by_value, const LaunchParams &p, int n_pairs, bool x3, cudaStream_t stream);
 int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid,
                 bool any_3x, bool any_colsum, bool pair, Status *d_status, unsigned *d_counters, long long wait_limit_ns,
-                cudaStream_t stream);
+                const float *adam, const FlashMaps *fmaps, unsigned long long *prof, cudaStream_t stream);
 int set_kernel_attributes();
 void count_launch(int n = 1);
 

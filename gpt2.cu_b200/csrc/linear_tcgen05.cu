@@ -39,21 +39,334 @@
 #include "linear_internal.h"
 #include "ptx_sm100.cuh"
 #include "kernel_common.cuh"
+#include "step_rowops.cuh"
 
 namespace g2l {
 
 using namespace ptx;
 
 // ------------------------------------------------------------------------------------
-// the kernel
+// per-tile bodies of the operand-transform and epilogue roles (shared by the GEMM kernel and the
+// step kernel, which runs them for GEMM tiles between its other ops)
 // ------------------------------------------------------------------------------------
 template <bool X3>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+struct RingCfg {
+  static constexpr int NST = X3 ? STAGES_3X : STAGES_1X;
+  static constexpr int STAGE_STRIDE = X3 ? 2 * STAGE_BYTES : STAGE_BYTES;
+  static constexpr int LO_OFFSET = STAGE_BYTES;  // 3x: lo copies sit behind the hi copies of a stage
+};
+
+// Operand transform of one tile: 3xTF32 hi/lo split of every landed stage and / or the bias-gradient
+// column sums of the B blocks. `x` = thread index among the 128 transform threads. Advances `it`.
+template <bool X3>
+__device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uint8_t *ring_ptr, Ctrl *ctrl,
+                                           const LaunchParams &p, uint32_t &it, int x, int lane) {
+  using R = RingCfg<X3>;
+  bool ok = true;
+  const int bn = op->bn;
+  // bias gradient = column sums of the B blocks. Spread over the tile rows (row m takes the
+  // k-blocks with kb % tiles_m == m) so that no CTA carries the whole extra pass: with tile row 0
+  // doing all of it those CTAs ran ~30 % longer than the rest and the launch waited for them.
+  const bool has_cs = (op->colsum != nullptr) && op->b_mn;
+  const bool spread = has_cs && op->colsum_spread != 0;
+  const bool do_colsum = has_cs && (spread || tc.m_tile == 0);
+  // column-sum mapping: `groups` float4 column groups, `parts` threads share a group and
+  // split the 32 k-rows of a block between them.
+  const int groups = bn >> 2;
+  const int parts = 128 / groups;
+  const int rows_per_part = 32 / parts;
+  const int grp = x / parts, part = x % parts;
+  const int chunk = grp >> 3, q16 = grp & 7;
+  float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int stage_f4 = (A_TILE_BYTES + bn * BK * 4) >> 4;
+
+  for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
+    const int s = it % R::NST;
+    const uint32_t ph = (it / R::NST) & 1u;
+    int okl = 1;
+    if (lane == 0)
+      okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s, X3 ? 0 : 64);
+    ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
+    if (!ok) break;
+    uint8_t *stage = ring_ptr + s * R::STAGE_STRIDE;
+    // An MN-major B block is walked by (column group, k-row) so that the thread that sums a
+    // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
+    // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
+    const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
+    const bool walk_b = op->b_mn && (X3 || cs_kb);
+    if (walk_b) {
+      uint8_t *bchunk = stage + A_TILE_BYTES + chunk * 4096;
+#pragma unroll 4
+      for (int r = part * rows_per_part; r < (part + 1) * rows_per_part; ++r) {
+        const int phys32 = (q16 >> 1) ^ (r & 3);
+        float4 *ptr = reinterpret_cast<float4 *>(bchunk + r * 128 + phys32 * 32 + (q16 & 1) * 16);
+        const float4 v = *ptr;
+        if (cs_kb) { csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w; }
+        if (X3) {
+          float4 h, l;
+          h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
+          l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+          *ptr = h;
+          *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(ptr) + R::LO_OFFSET) = l;
+        }
+      }
+    }
+    if (X3) {
+      float4 *hi = reinterpret_cast<float4 *>(stage);
+      float4 *lo = reinterpret_cast<float4 *>(stage + R::LO_OFFSET);
+      const int lin_f4 = walk_b ? (A_TILE_BYTES >> 4) : stage_f4;  // A only, or A and a K-major B
+      for (int i = x; i < lin_f4; i += NUM_XFORM_WARPS * 32) {
+        const float4 v = hi[i];
+        float4 h, l;
+        h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
+        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+        hi[i] = h;
+        lo[i] = l;
+      }
+      fence_proxy_async_smem();
+    }
+    __syncwarp();
+    if (lane == 0) {
+      if (X3) mbar_arrive(smem_u32(&ctrl->ready[s]));
+      mbar_arrive(smem_u32(&ctrl->empty[s]));
+    }
+  }
+  if (!ok) return false;
+  if (do_colsum) {
+    for (int o = 1; o < parts; o <<= 1) {
+      csum.x += __shfl_xor_sync(0xffffffffu, csum.x, o);
+      csum.y += __shfl_xor_sync(0xffffffffu, csum.y, o);
+      csum.z += __shfl_xor_sync(0xffffffffu, csum.z, o);
+      csum.w += __shfl_xor_sync(0xffffffffu, csum.w, o);
+    }
+    if (part == 0) {
+      const int col = tc.n_tile * bn + grp * 4;
+      const float v[4] = {csum.x, csum.y, csum.z, csum.w};
+      for (int j = 0; j < 4; ++j) {
+        if (col + j < op->Nc) {
+          if (op->splits > 1 || spread) atomicAdd(op->colsum + col + j, v[j]);
+          else op->colsum[col + j] = v[j];
+        }
+      }
+    }
+  }
+  return true;
+}
+
+// Epilogue of one tile by one warp: waits for the accumulator `tcount & 1`, drains the 32-column chunks
+// c_first, c_first + n_epi, ... of its TMEM lane quarter, hands the accumulator back (`arrive` arrivals: a
+// warp that works without its helper twin arrives for both) and publishes the tile on the dependency
+// counters (`arrive` again).
+__device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, uint32_t tcount, bool helper, int n_epi,
+                                              int c_first, unsigned arrive, uint32_t sbuf, uint32_t tmem_base, Ctrl *ctrl,
+                                              const LaunchParams &p, int warp, int lane) {
+  const int q = warp & 3;  // TMEM lane quarter this warp may read
+  const uint32_t as = tcount & 1u;
+  const uint32_t aph = (tcount >> 1) & 1u;
+  int okl = 1;
+  if (lane == 0)
+    okl = wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128);
+  if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
+  tc_fence_after();
+
+  const int bn = op->bn;
+  const int Mc = op->Mc, Nc = op->Nc;
+  const long long ldc = op->ldc;
+  const int row = tc.m_tile * BM + q * 32 + lane;
+  const int n0 = tc.n_tile * bn;
+  const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * MAX_BN;
+  const bool det_split = (op->splits > 1) && !op->atomic_out;
+  const bool add_bias = (op->bias != nullptr) && (tc.split == 0 || det_split);
+  const bool dual = (op->flags & GPT2L_EPI_GELU_DUAL) && op->C2 != nullptr;
+  const int out_tile = tc.m_tile * op->tiles_n + tc.n_tile;
+  float *ws_tile = nullptr;
+  if (det_split)
+    ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
+              (size_t)(q * 32 + lane) * bn;
+
+  if (!det_split) {
+    // ---- registers -> swizzled 32x32 box in shared memory -> coalesced stores (or vector
+    // reductions for split-K partials); see store_chunk
+    const int row0 = tc.m_tile * BM + q * 32;
+    EpiAux ea;
+    if (op->aux_op && tc.split == 0) {
+      ea.aux = op->aux + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
+      ea.op = op->aux_op;
+      ea.scale = op->aux_scale;
+      if (op->aux_row) ea.row = op->aux_row + ((long long)tc.bb * op->batch_inner + tc.bh) * Mc;
+    }
+    const EpiAux none;
+    const float drow = (ea.row && row0 + lane < Mc) ? __ldg(ea.row + row0 + lane) : 0.f;
+    for (int c = c_first; c < bn / 32; c += n_epi) {
+      const int nb = n0 + c * 32;
+      if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
+      AuxRegs ar;
+      ar.drow = drow;
+      load_aux(ar, ea, ldc, row0, nb, Mc, Nc, lane);  // in flight while the accumulator is read
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * 32, r);
+      tmem_ld_wait();
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (add_bias && nb + 4 * j < Nc) bv = __ldg(reinterpret_cast<const float4 *>(op->bias + nb) + j);
+        v[4 * j + 0] = __uint_as_float(r[4 * j + 0]) + bv.x;
+        v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + bv.y;
+        v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
+        v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
+      }
+      for (int pass = 0; pass < (dual ? 2 : 1); ++pass) {
+        if (pass == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        }
+        float *cbase = (pass == 0 ? op->C : op->C2) + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
+        // the epilogue operand applies to the first output only, and once per element: with
+        // split-K reduce-adds the split that also adds the bias carries it
+        store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, pass == 0 ? ea : none, ar);
+      }
+    }
+  } else if (!helper)  // fixed-order split-K: the quarter's own warp parks whole rows
+  for (int c = 0; c < bn / 32; ++c) {
+    const int nb = n0 + c * 32;
+    if (nb >= Nc) break;  // warp-uniform
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * 32, r);
+    tmem_ld_wait();
+    {
+      float4 *dst = reinterpret_cast<float4 *>(ws_tile + c * 32);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+    }
+  }
+  // the accumulator is in registers / memory now: hand the TMEM buffer back
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive_cnt(smem_u32(&ctrl->tmem_empty[as]), arrive);
+
+  if (det_split && !helper) {
+    // Deterministic split-K: every split parks its partial rows in the workspace; the
+    // warp that arrives last for this (output tile, lane quarter) adds the partials in
+    // split order and writes C. No ordering between splits is ever waited for.
+    __threadfence();
+    __syncwarp();
+    unsigned old = 0;
+    unsigned *sem = op->ws_sem + (size_t)out_tile * 4 + q;
+    if (lane == 0) old = atom_acq_rel_add(sem, 1u);
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old == (unsigned)(op->splits - 1)) {
+      __threadfence();
+      if (lane == 0) *sem = 0;  // ready for the next launch
+      const size_t split_stride = (size_t)op->tiles_m * op->tiles_n * (size_t)(BM * bn);
+      const float *p0 = op->ws + (size_t)out_tile * (size_t)(BM * bn) + (size_t)(q * 32 + lane) * bn;
+      if (row < Mc) {
+        for (int c4 = 0; c4 < bn / 4; ++c4) {
+          const int col = n0 + c4 * 4;
+          if (col >= Nc) break;
+          // L2 reads: the partials were written by other SMs during this launch
+          float4 acc = __ldcg(reinterpret_cast<const float4 *>(p0 + c4 * 4));
+          for (int sp = 1; sp < op->splits; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + sp * split_stride + c4 * 4));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+          float *dst = op->C + (long long)row * ldc + col;
+          if (col + 4 <= Nc) {
+            if (add_bias) {
+              const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + col));
+              vals[0] += bv.x; vals[1] += bv.y; vals[2] += bv.z; vals[3] += bv.w;
+            }
+            *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+            if (dual)
+              *reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + col) =
+                  make_float4(gelu_tanh(vals[0]), gelu_tanh(vals[1]), gelu_tanh(vals[2]), gelu_tanh(vals[3]));
+          } else {
+            for (int j = 0; j < 4; ++j)
+              if (col + j < Nc) {
+                float v = vals[j] + (add_bias ? __ldg(op->bias + col + j) : 0.f);
+                dst[j] = v;
+                if (dual) op->C2[(long long)row * ldc + col + j] = gelu_tanh(v);
+              }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- publish: everything this warp stored is visible before the counters move (helpers
+  // publish too, so a tile counts NUM_EPI_WARPS or 2 * NUM_EPI_WARPS arrivals: epi_arrivals())
+  if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+      if (op->pub_rb_base >= 0) red_release_add(p.counters + op->pub_rb_base + tc.m_tile, arrive);
+      if (op->pub_op_ctr >= 0) red_release_add(p.counters + op->pub_op_ctr, arrive);
+    }
+  }
+  return true;
+}
+
+// A non-GEMM tile of the step kernel, executed by one of the eight worker warps (w8 = 0..7). `scratch` is
+// the 32 KiB of epilogue boxes, free while all eight warps are inside the same tile.
+__device__ __forceinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, int w8, int lane, float *scratch,
+                                            RowSync &rs, Ctrl *ctrl, const LaunchParams &p) {
+  const int tile = tc.m_tile;
+  const int rpt = op->rows_per_tile;
+  // dependencies are counted per 128-row block; every warp makes its own acquire before it reads
+  const int rb = op->op_kind == OPK_ADAMW ? 0 : (int)(((long long)tile * rpt) >> 7);
+  int okl = 1;
+  if (lane == 0) okl = wait_deps(op, rb, ctrl, p) ? 1 : 0;
+  if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
+  const int wtid = w8 * 32 + lane;
+  bool ok = true;
+  switch (op->op_kind) {
+    case OPK_EMBED_FWD: row_embed_fwd(op, tile, wtid); break;
+    case OPK_EMBED_BWD: row_embed_bwd(op, tile, wtid); break;
+    case OPK_LN_FWD:
+      if (op->ra.i1 <= 256) row_ln_fwd<2>(op, tile, w8, lane);
+      else if (op->ra.i1 <= 768) row_ln_fwd<6>(op, tile, w8, lane);
+      else row_ln_fwd<10>(op, tile, w8, lane);
+      break;
+    case OPK_LN_BWD:
+      if (op->ra.i1 <= 256) ok = row_ln_bwd<2>(op, tile, w8, lane, scratch, rs, p);
+      else if (op->ra.i1 <= 768) ok = row_ln_bwd<6>(op, tile, w8, lane, scratch, rs, p);
+      else ok = row_ln_bwd<10>(op, tile, w8, lane, scratch, rs, p);
+      break;
+    case OPK_XENT: ok = row_xent(op, tile, w8, lane, scratch, rs, p); break;
+    case OPK_ROWDOT: row_rowdot(op, tile, wtid); break;
+    case OPK_ADAMW: row_adamw(op, tile, wtid, p); break;
+    case OPK_TRANSPOSE: row_transpose(op, tile, w8, lane, scratch + w8 * 1024); break;
+    default: break;
+  }
+  if (!ok) return false;
+  // publish: one arrival per worker warp and tile
+  if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+      if (op->pub_rb_base >= 0) red_release_add(p.counters + op->pub_rb_base + rb, 1u);
+      if (op->pub_op_ctr >= 0) red_release_add(p.counters + op->pub_op_ctr, 1u);
+    }
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------
+// the kernel. MEGA = false: one GEMM (or a list of GEMMs whose transform needs are the same for the
+// whole launch). MEGA = true: the step kernel: GEMM ops with a per-op decision on the transform warps,
+// row-local ops on the worker warps, one more warp, profile stamps.
+// ------------------------------------------------------------------------------------
+template <bool X3, bool MEGA>
+__global__ void __launch_bounds__(MEGA ? STEP_THREADS : NUM_THREADS, 1)
 gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParams p) {
   extern __shared__ uint8_t smem_raw[];
-  constexpr int NST = X3 ? STAGES_3X : STAGES_1X;
-  constexpr int STAGE_STRIDE = X3 ? 2 * STAGE_BYTES : STAGE_BYTES;
-  constexpr int LO_OFFSET = STAGE_BYTES;  // 3x: lo copies sit behind the hi copies of a stage
+  using R = RingCfg<X3>;
+  constexpr int NST = R::NST;
+  constexpr int STAGE_STRIDE = R::STAGE_STRIDE;
+  constexpr int LO_OFFSET = R::LO_OFFSET;
 
   const GemmOp *ops = p.ops ? p.ops : &op0;
   const int n_ops = p.ops ? p.n_ops : 1;
@@ -66,17 +379,21 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  // MEGA: barrier counts are fixed at their maximum; a party with nothing to do in an op is stood in for
+  const bool xf_all = MEGA ? true : (p.xform_active != 0);
 
   if (tid == 0) {
     for (int s = 0; s < STAGES_1X; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), 1);
-      mbar_init(smem_u32(&ctrl->empty[s]), 1 + (p.xform_active ? NUM_XFORM_WARPS : 0));
+      mbar_init(smem_u32(&ctrl->empty[s]), 1 + (xf_all ? NUM_XFORM_WARPS : 0));
       mbar_init(smem_u32(&ctrl->ready[s]), NUM_XFORM_WARPS);
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[a]), NUM_EPI_WARPS * (p.xform_active ? 1 : 2));
+      mbar_init(smem_u32(&ctrl->tmem_empty[a]), NUM_EPI_WARPS * ((MEGA || !p.xform_active) ? 2 : 1));
     }
+    mbar_init(smem_u32(&ctrl->row_bar), NUM_WORKER_WARPS);
+    mbar_init(smem_u32(&ctrl->cta_bar), STEP_THREADS / 32);
     ctrl->abort = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -98,23 +415,16 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      if (MEGA && op->op_kind != OPK_GEMM) continue;  // the worker warps run these
       if (tc.skip) continue;  // every role skips the same tiles, so no barrier phase is consumed
       // ---- dependency counters: do not touch the operands before their producers are done
-      bool waited = false;
-#pragma unroll
-      for (int w = 0; w < MAX_WAITS; ++w) {
-        const int base = op->wait_ctr[w];
-        if (base < 0) continue;
-        const int idx = base + (op->wait_kind[w] == GPT2L_DEP_ROWBLOCK ? tc.m_tile : 0);
+      if (op->wait_ctr[0] >= 0) {  // dependencies fill the slots from 0 up
         int okl = 1;
-        if (lane == 0)
-          okl = wait_counter(p.counters + idx, (unsigned)op->wait_expected[w], ctrl, p, op->op_index, idx);
+        if (lane == 0) okl = wait_deps(op, tc.m_tile, ctrl, p) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-        waited = true;
         if (!ok) break;
+        fence_proxy_async_all();  // producers wrote with plain stores; TMA reads next
       }
-      if (!ok) break;
-      if (waited) fence_proxy_async_all();  // producers wrote with plain stores; TMA reads next
 
       const int m0 = tc.m_tile * BM;
       const int n0 = tc.n_tile * op->bn;
@@ -179,7 +489,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       Tile tc_next = tc;
       const GemmOp *op_next = op;
       if (have_next) op_next = decode_tile(ops, n_ops, t_next, cursor, tc_next);
-      if (tc.skip) {
+      if (tc.skip || (MEGA && op->op_kind != OPK_GEMM)) {
         t = t_next; tc = tc_next; op = op_next; have = have_next;
         continue;
       }
@@ -202,6 +512,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const uint64_t hiB = op->b_mn ? smem_desc_hi(4096, 512, 1) : smem_desc_hi(16, 1024, 2);
       const uint32_t stepA = op->a_mn ? 1024u : 32u;
       const uint32_t stepB = op->b_mn ? 1024u : 32u;
+      // MEGA: an op that needs no operand transform leaves the transform warps' share of empty[s] to us
+      const bool stand_in = MEGA && !op->xform;
 
       for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const int s = it % NST;
@@ -233,6 +545,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             }
           }
           mma_commit(smem_u32(&ctrl->empty[s]));  // frees the stage once these MMAs have read it
+          if (stand_in) mbar_arrive_cnt(smem_u32(&ctrl->empty[s]), NUM_XFORM_WARPS);
         }
         __syncwarp();
       }
@@ -245,10 +558,9 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       have = have_next;
       ++tcount;
     }
-  } else if (warp < EPI_WARP0 && p.xform_active) {
+  } else if (!MEGA && warp < EPI_WARP0 && p.xform_active) {
     // =============================== operand transform ===============================
     // (in launches where no op needs a split or a column sum these warps join the epilogue instead)
-    {
     const int x = tid - XFORM_WARP0 * 32;  // 0..127
     int cursor = 0;
     uint32_t it = 0;
@@ -257,102 +569,14 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
       if (tc.skip) continue;
-      const int bn = op->bn;
-      // bias gradient = column sums of the B blocks. Spread over the tile rows (row m takes the
-      // k-blocks with kb % tiles_m == m) so that no CTA carries the whole extra pass: with tile row 0
-      // doing all of it those CTAs ran ~30 % longer than the rest and the launch waited for them.
-      const bool has_cs = (op->colsum != nullptr) && op->b_mn;
-      const bool spread = has_cs && op->colsum_spread != 0;
-      const bool do_colsum = has_cs && (spread || tc.m_tile == 0);
-      // column-sum mapping: `groups` float4 column groups, `parts` threads share a group and
-      // split the 32 k-rows of a block between them.
-      const int groups = bn >> 2;
-      const int parts = 128 / groups;
-      const int rows_per_part = 32 / parts;
-      const int grp = x / parts, part = x % parts;
-      const int chunk = grp >> 3, q16 = grp & 7;
-      float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
-      const int stage_f4 = (A_TILE_BYTES + bn * BK * 4) >> 4;
-
-      for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
-        const int s = it % NST;
-        const uint32_t ph = (it / NST) & 1u;
-        int okl = 1;
-        if (lane == 0)
-          okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s, X3 ? 0 : 64);
-        ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-        if (!ok) break;
-        uint8_t *stage = ring_ptr + s * STAGE_STRIDE;
-        // An MN-major B block is walked by (column group, k-row) so that the thread that sums a
-        // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
-        // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
-        const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
-        const bool walk_b = op->b_mn && (X3 || cs_kb);
-        if (walk_b) {
-          uint8_t *bchunk = stage + A_TILE_BYTES + chunk * 4096;
-#pragma unroll 4
-          for (int r = part * rows_per_part; r < (part + 1) * rows_per_part; ++r) {
-            const int phys32 = (q16 >> 1) ^ (r & 3);
-            float4 *ptr = reinterpret_cast<float4 *>(bchunk + r * 128 + phys32 * 32 + (q16 & 1) * 16);
-            const float4 v = *ptr;
-            if (cs_kb) { csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w; }
-            if (X3) {
-              float4 h, l;
-              h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
-              l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-              *ptr = h;
-              *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(ptr) + LO_OFFSET) = l;
-            }
-          }
-        }
-        if (X3) {
-          float4 *hi = reinterpret_cast<float4 *>(stage);
-          float4 *lo = reinterpret_cast<float4 *>(stage + LO_OFFSET);
-          const int lin_f4 = walk_b ? (A_TILE_BYTES >> 4) : stage_f4;  // A only, or A and a K-major B
-          for (int i = x; i < lin_f4; i += NUM_XFORM_WARPS * 32) {
-            const float4 v = hi[i];
-            float4 h, l;
-            h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
-            l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-            hi[i] = h;
-            lo[i] = l;
-          }
-          fence_proxy_async_smem();
-        }
-        __syncwarp();
-        if (lane == 0) {
-          if (X3) mbar_arrive(smem_u32(&ctrl->ready[s]));
-          mbar_arrive(smem_u32(&ctrl->empty[s]));
-        }
-      }
-      if (!ok) break;
-      if (do_colsum) {
-        for (int o = 1; o < parts; o <<= 1) {
-          csum.x += __shfl_xor_sync(0xffffffffu, csum.x, o);
-          csum.y += __shfl_xor_sync(0xffffffffu, csum.y, o);
-          csum.z += __shfl_xor_sync(0xffffffffu, csum.z, o);
-          csum.w += __shfl_xor_sync(0xffffffffu, csum.w, o);
-        }
-        if (part == 0) {
-          const int col = tc.n_tile * bn + grp * 4;
-          const float v[4] = {csum.x, csum.y, csum.z, csum.w};
-          for (int j = 0; j < 4; ++j) {
-            if (col + j < op->Nc) {
-              if (op->splits > 1 || spread) atomicAdd(op->colsum + col + j, v[j]);
-              else op->colsum[col + j] = v[j];
-            }
-          }
-        }
-      }
+      ok = xform_tile<X3>(op, tc, ring_ptr, ctrl, p, it, x, lane);
     }
-    }
-  } else {
+  } else if (!MEGA) {
     // =============================== epilogue ===============================
     // Warps 6-9 always work here. When the transform warps 2-5 have nothing to transform they
     // help: warp w and warp w + 4 read the same TMEM lane quarter and take alternate 32-column
     // chunks of every tile, which halves the time a tile spends in the epilogue (what bounds
     // short reductions such as the attention score GEMMs, and every CTA's last tile).
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
     const bool helper = warp < EPI_WARP0;
     const int n_epi = p.xform_active ? 1 : 2;
     const int c_first = helper ? 1 : 0;
@@ -365,152 +589,50 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
       if (tc.skip) continue;
-      const uint32_t as = tcount & 1u;
-      const uint32_t aph = (tcount >> 1) & 1u;
+      ok = epilogue_tile(op, tc, tcount, helper, n_epi, c_first, 1u, sbuf, tmem_base, ctrl, p, warp, lane);
       ++tcount;
-      int okl = 1;
-      if (lane == 0)
-        okl = wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128);
-      ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-      if (!ok) break;
-      tc_fence_after();
-
-      const int bn = op->bn;
-      const int Mc = op->Mc, Nc = op->Nc;
-      const long long ldc = op->ldc;
-      const int row = tc.m_tile * BM + q * 32 + lane;
-      const int n0 = tc.n_tile * bn;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * MAX_BN;
-      const bool det_split = (op->splits > 1) && !op->atomic_out;
-      const bool add_bias = (op->bias != nullptr) && (tc.split == 0 || det_split);
-      const bool dual = (op->flags & GPT2L_EPI_GELU_DUAL) && op->C2 != nullptr;
-      const int out_tile = tc.m_tile * op->tiles_n + tc.n_tile;
-      float *ws_tile = nullptr;
-      if (det_split)
-        ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
-                  (size_t)(q * 32 + lane) * bn;
-
-      if (!det_split) {
-        // ---- registers -> swizzled 32x32 box in shared memory -> coalesced stores (or vector
-        // reductions for split-K partials); see store_chunk
-        const int row0 = tc.m_tile * BM + q * 32;
-        EpiAux ea;
-        if (op->aux_op && tc.split == 0) {
-          ea.aux = op->aux + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
-          ea.op = op->aux_op;
-          ea.scale = op->aux_scale;
-          if (op->aux_row) ea.row = op->aux_row + ((long long)tc.bb * op->batch_inner + tc.bh) * Mc;
-        }
-        const EpiAux none;
-        const float drow = (ea.row && row0 + lane < Mc) ? __ldg(ea.row + row0 + lane) : 0.f;
-        for (int c = c_first; c < bn / 32; c += n_epi) {
-          const int nb = n0 + c * 32;
-          if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
-          AuxRegs ar;
-          ar.drow = drow;
-          load_aux(ar, ea, ldc, row0, nb, Mc, Nc, lane);  // in flight while the accumulator is read
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (add_bias && nb + 4 * j < Nc) bv = __ldg(reinterpret_cast<const float4 *>(op->bias + nb) + j);
-            v[4 * j + 0] = __uint_as_float(r[4 * j + 0]) + bv.x;
-            v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + bv.y;
-            v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
-            v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
-          }
-          for (int pass = 0; pass < (dual ? 2 : 1); ++pass) {
-            if (pass == 1) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-            }
-            float *cbase = (pass == 0 ? op->C : op->C2) + tc.bb * op->c_bs_outer + tc.bh * op->c_bs_inner;
-            // the epilogue operand applies to the first output only, and once per element: with
-            // split-K reduce-adds the split that also adds the bias carries it
-            store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, pass == 0 ? ea : none, ar);
-          }
-        }
-      } else if (!helper)  // fixed-order split-K: the quarter's own warp parks whole rows
-      for (int c = 0; c < bn / 32; ++c) {
-        const int nb = n0 + c * 32;
-        if (nb >= Nc) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        {
-          float4 *dst = reinterpret_cast<float4 *>(ws_tile + c * 32);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-        }
+    }
+  } else if (warp < EPI_WARP0 + NUM_EPI_WARPS) {
+    // =============================== step kernel: worker warps 2-9 ===============================
+    // GEMM tile of an op that needs the transform: warps 2-5 transform, warps 6-9 drain the accumulator
+    // alone (and arrive twice). GEMM tile of any other op: all eight drain it, alternate chunks. Any other
+    // tile: all eight run the row-local op.
+    const bool helper = warp < EPI_WARP0;
+    const int w8 = warp - XFORM_WARP0;
+    const int x = tid - XFORM_WARP0 * 32;
+    const uint32_t sbuf = ring + RING_BYTES +
+                          (uint32_t)(helper ? (warp - XFORM_WARP0) * 2 + 1 : (warp - EPI_WARP0) * 2) * EPI_BUF_BYTES;
+    float *scratch = reinterpret_cast<float *>(ring_ptr + RING_BYTES);
+    RowSync rs = {smem_u32(&ctrl->row_bar), 0u, ctrl};
+    int cursor = 0;
+    uint32_t it = 0, tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      Tile tc;
+      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      long long t0 = 0;
+      if (p.prof && tid == EPI_WARP0 * 32) t0 = globaltimer_ns();
+      if (op->op_kind != OPK_GEMM) {
+        if (op->op_kind < OPK_ATTN_FWD || op->op_kind > OPK_ATTN_BWD_Q)
+          ok = row_op_tile(op, tc, w8, lane, scratch, rs, ctrl, p);
+      } else if (tc.skip) {
+        continue;
+      } else if (op->xform) {
+        if (helper) ok = xform_tile<X3>(op, tc, ring_ptr, ctrl, p, it, x, lane);
+        else ok = epilogue_tile(op, tc, tcount, false, 1, 0, 2u, sbuf, tmem_base, ctrl, p, warp, lane);
+        if (!helper) it += (uint32_t)(tc.kb1 - tc.kb0);
+        ++tcount;
+      } else {
+        ok = epilogue_tile(op, tc, tcount, helper, 2, helper ? 1 : 0, 1u, sbuf, tmem_base, ctrl, p, warp, lane);
+        it += (uint32_t)(tc.kb1 - tc.kb0);
+        ++tcount;
       }
-      // the accumulator is in registers / memory now: hand the TMEM buffer back
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[as]));
-
-      if (det_split && !helper) {
-        // Deterministic split-K: every split parks its partial rows in the workspace; the
-        // warp that arrives last for this (output tile, lane quarter) adds the partials in
-        // split order and writes C. No ordering between splits is ever waited for.
-        __threadfence();
-        __syncwarp();
-        unsigned old = 0;
-        unsigned *sem = op->ws_sem + (size_t)out_tile * 4 + q;
-        if (lane == 0) old = atom_acq_rel_add(sem, 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == (unsigned)(op->splits - 1)) {
-          __threadfence();
-          if (lane == 0) *sem = 0;  // ready for the next launch
-          const size_t split_stride = (size_t)op->tiles_m * op->tiles_n * (size_t)(BM * bn);
-          const float *p0 = op->ws + (size_t)out_tile * (size_t)(BM * bn) + (size_t)(q * 32 + lane) * bn;
-          if (row < Mc) {
-            for (int c4 = 0; c4 < bn / 4; ++c4) {
-              const int col = n0 + c4 * 4;
-              if (col >= Nc) break;
-              // L2 reads: the partials were written by other SMs during this launch
-              float4 acc = __ldcg(reinterpret_cast<const float4 *>(p0 + c4 * 4));
-              for (int sp = 1; sp < op->splits; ++sp) {
-                const float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + sp * split_stride + c4 * 4));
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-              }
-              float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-              float *dst = op->C + (long long)row * ldc + col;
-              if (col + 4 <= Nc) {
-                if (add_bias) {
-                  const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + col));
-                  vals[0] += bv.x; vals[1] += bv.y; vals[2] += bv.z; vals[3] += bv.w;
-                }
-                *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
-                if (dual)
-                  *reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + col) =
-                      make_float4(gelu_tanh(vals[0]), gelu_tanh(vals[1]), gelu_tanh(vals[2]), gelu_tanh(vals[3]));
-              } else {
-                for (int j = 0; j < 4; ++j)
-                  if (col + j < Nc) {
-                    float v = vals[j] + (add_bias ? __ldg(op->bias + col + j) : 0.f);
-                    dst[j] = v;
-                    if (dual) op->C2[(long long)row * ldc + col + j] = gelu_tanh(v);
-                  }
-              }
-            }
-          }
-        }
-      }
-
-      // ---- publish: everything this warp stored is visible before the counters move (helpers
-      // publish too, so a tile counts NUM_EPI_WARPS or 2 * NUM_EPI_WARPS arrivals: epi_arrivals())
-      if (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0) {
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-          if (op->pub_rb_base >= 0) red_release_add(p.counters + op->pub_rb_base + tc.m_tile, 1u);
-          if (op->pub_op_ctr >= 0) red_release_add(p.counters + op->pub_op_ctr, 1u);
-        }
+      if (p.prof && tid == EPI_WARP0 * 32) {
+        // per-tile profile stamp (the reference keeps such arrays per instruction, src/mk.cu:966-971):
+        // start time, and SM id with the time this warp spent in the tile
+        const long long t1 = globaltimer_ns();
+        p.prof[2 * (size_t)t] = (unsigned long long)t0;
+        p.prof[2 * (size_t)t + 1] = ((unsigned long long)smid() << 48) | (unsigned long long)(t1 - t0);
       }
     }
   }
@@ -822,10 +944,16 @@ size_t op_workspace_bytes(const GemmOp &op) {
 }
 
 int set_kernel_attributes() {
-  cudaError_t e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<false>,
+  cudaError_t e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<false, false>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return GPT2L_ERR_CUDA;
-  e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           SMEM_BYTES);
+  if (e != cudaSuccess) return GPT2L_ERR_CUDA;
+  e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           SMEM_BYTES);
+  if (e != cudaSuccess) return GPT2L_ERR_CUDA;
+  e = cudaFuncSetAttribute(gpt2_linear_tcgen05_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            SMEM_BYTES);
   return e == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }
@@ -843,6 +971,9 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.sticky = ctx->sticky;
   p.host_flag = ctx->d_flag;
   p.counters = nullptr;
+  p.fmaps = nullptr;
+  p.prof = nullptr;
+  for (float &f : p.adam) f = 0.f;
   p.wait_limit_ns = default_wait_limit_ns();
   p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
   if (op.pair) {
@@ -852,15 +983,18 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   }
   const int grid = op.n_tiles < ctx->num_sms ? op.n_tiles : ctx->num_sms;
   if (op.mode == GPT2L_MODE_TF32X3)
-    gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
+    gpt2_linear_tcgen05_kernel<true, false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
   else
-    gpt2_linear_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
+    gpt2_linear_tcgen05_kernel<false, false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(op, p);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }
 
+// One launch over a device array of ops. GEMM-only lists on CTA pairs keep the pair kernel; everything
+// else runs the step kernel (per-op transform decision, row-local ops, STEP_THREADS threads).
 int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles, int grid, bool any_3x, bool any_colsum,
-                bool pair, Status *d_status, unsigned *d_counters, long long wait_limit_ns, cudaStream_t stream) {
+                bool pair, Status *d_status, unsigned *d_counters, long long wait_limit_ns, const float *adam,
+                const FlashMaps *fmaps, unsigned long long *prof, cudaStream_t stream) {
   static GemmOp dummy;  // the by-value slot is unused when a list is given
   LaunchParams p;
   p.ops = d_ops;
@@ -872,11 +1006,14 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
   p.xform_active = (any_3x || any_colsum) ? 1 : 0;
+  for (int i = 0; i < 7; ++i) p.adam[i] = adam ? adam[i] : 0.f;
+  p.fmaps = fmaps;
+  p.prof = prof;
   if (pair) return pair_launch(nullptr, p, grid, any_3x, stream);
   if (any_3x)
-    gpt2_linear_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);
+    gpt2_linear_tcgen05_kernel<true, true><<<grid, STEP_THREADS, SMEM_BYTES, stream>>>(dummy, p);
   else
-    gpt2_linear_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(dummy, p);
+    gpt2_linear_tcgen05_kernel<false, true><<<grid, STEP_THREADS, SMEM_BYTES, stream>>>(dummy, p);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? GPT2L_OK : GPT2L_ERR_CUDA;
 }

@@ -3,28 +3,18 @@
 // the schedule by replaying it on the host, and launches the kernel once per run.
 //
 // Counter layout: op i owns tiles_m(i) row-block counters followed by one op-level counter.
-// Each epilogue warp of a tile publishes once to the row-block counter of its tile row and once
-// to the op counter, so with A arrivals per tile (4 epilogue warps; 8 in one-CTA launches whose
-// transform warps help in the epilogue) a complete row block shows A * tiles_n * splits arrivals
-// and a complete op A * n_tiles.
+// A finished tile publishes A arrivals to the row-block counter of its rows and A to the op counter
+// (A = 8, the worker warps of a CTA; 4 in the CTA-pair kernel), so a complete row block of a GEMM shows
+// A * tiles_n * splits arrivals and a complete op A * n_tiles.
 #include <cuda_runtime.h>
 #include <string.h>
 
 #include <vector>
 
 #include "linear_internal.h"
+#include "schedule_internal.h"
 
 namespace g2l {
-
-struct Plan {
-  std::vector<GemmOp> ops;
-  int total_tiles = 0;
-  int n_counters = 0;
-  bool any_3x = false;
-  bool any_colsum = false;
-  bool pair = false;  // every op runs on CTA pairs (256-row tiles)
-  int arrivals = NUM_EPI_WARPS;  // counter arrivals per finished 128-row tile (see epi_arrivals)
-};
 
 static GemmDesc desc_from(const gpt2l_op &o) {
   GemmDesc d;
@@ -41,58 +31,122 @@ static GemmDesc desc_from(const gpt2l_op &o) {
   return d;
 }
 
+OpSpec spec_from(const gpt2l_op &o) {
+  OpSpec s;
+  s.kind = OPK_GEMM;
+  s.gemm = desc_from(o);
+  s.layer = o.layer;
+  for (int w = 0; w < GPT2L_MAX_DEPS; ++w)
+    if (o.deps[w].kind != GPT2L_DEP_NONE) s.deps.push_back({o.deps[w].producer, o.deps[w].kind});
+  return s;
+}
+
 // Shapes, tiling, counters and dependency wiring. No CUDA calls (used by the CPU tests).
-static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
-  if (!ops || n_ops <= 0) return GPT2L_ERR_BAD_ARG;
+// Counter arrivals: in the step kernel every finished tile, of whatever op, counts NUM_WORKER_WARPS
+// arrivals (a GEMM tile whose transform warps are busy has its four epilogue warps arrive twice); in the
+// pair kernel the four epilogue warps of each CTA arrive once.
+int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
+  const int n_ops = (int)specs.size();
+  if (n_ops <= 0) return GPT2L_ERR_BAD_ARG;
   plan->ops.resize(n_ops);
   int tile_base = 0, ctr = 0;
   // one kernel runs the whole list, so all ops use the same CTA arrangement: pairs only when
-  // every op asks for them (cta_pair == 2)
+  // every op is a GEMM that asks for them (cta_pair == 2)
   bool pair = true;
-  for (int i = 0; i < n_ops; ++i)
-    if (ops[i].opts.cta_pair != 2) pair = false;
+  for (const auto &s : specs)
+    if (s.kind != OPK_GEMM || s.gemm.opts.cta_pair != 2) pair = false;
   plan->pair = pair;
   for (int i = 0; i < n_ops; ++i) {
-    GemmDesc d = desc_from(ops[i]);
-    d.opts.cta_pair = pair ? 2 : 1;
-    // bias gradient inside a schedule is always the fused column sum
-    int e = plan_op(d, num_sms, &plan->ops[i]);
-    if (e) return e;
+    const OpSpec &s = specs[i];
     GemmOp &g = plan->ops[i];
-    if (i > 0 && g.mode != plan->ops[0].mode) return GPT2L_ERR_SCHEDULE;  // one mode per launch
+    if (s.kind == OPK_GEMM) {
+      GemmDesc d = s.gemm;
+      d.opts.cta_pair = pair ? 2 : 1;
+      // bias gradient inside a schedule is always the fused column sum
+      int e = plan_op(d, num_sms, &g);
+      if (e) return e;
+      if (g.mode != plan->ops[0].mode && plan->ops[0].op_kind == OPK_GEMM) return GPT2L_ERR_SCHEDULE;  // one mode per launch
+      if (g.mode == GPT2L_MODE_TF32X3) plan->any_3x = true;
+      if (g.colsum) plan->any_colsum = true;
+      g.rows_per_tile = BM;
+    } else {
+      if (s.rows <= 0 || s.rows_per_tile <= 0) return GPT2L_ERR_BAD_ARG;
+      memset(&g, 0, sizeof(g));
+      g.op_kind = s.kind;
+      g.ra = s.ra;
+      g.rows_per_tile = s.rows_per_tile;
+      g.rb_per_seq = s.rb_per_seq;
+      if (s.kind == OPK_ADAMW) {
+        g.tiles_m = 1;  // one counter block: consumers (none today) would wait for the whole op
+        g.n_tiles = (int)((s.ra.n1 + (long long)s.rows_per_tile * 1024 - 1) / ((long long)s.rows_per_tile * 1024));
+      } else if (s.kind >= OPK_ATTN_FWD && s.kind <= OPK_ATTN_BWD_Q) {
+        // tile = (sequence * heads + head, 128-row block of the sequence); row blocks are numbered over all rows
+        g.tiles_m = s.rows / BM;
+        g.n_tiles = g.tiles_m * s.ra.i3;  // i3 = heads
+      } else {
+        // whole 128-row blocks: tiles past the last row do nothing but still count, so that every block
+        // shows the same number of arrivals
+        if (BM % s.rows_per_tile != 0) return GPT2L_ERR_BAD_ARG;
+        g.tiles_m = (s.rows + BM - 1) / BM;
+        g.n_tiles = g.tiles_m * (BM / s.rows_per_tile);
+      }
+      g.Mc = s.rows;
+      g.tiles_n = 1;
+      g.splits = 1;
+      g.tiles_dec = g.tiles_m;
+      for (int w = 0; w < MAX_WAITS; ++w) g.wait_ctr[w] = -1;
+    }
     g.op_index = i;
-    g.layer = ops[i].layer;
+    g.layer = s.layer;
     g.tile_base = tile_base;
     tile_base += g.n_tiles;
     g.pub_rb_base = ctr;
     g.pub_op_ctr = ctr + g.tiles_m;
     ctr += g.tiles_m + 1;
-    if (g.mode == GPT2L_MODE_TF32X3) plan->any_3x = true;
-    if (g.colsum) plan->any_colsum = true;
   }
-  // the pair kernel always publishes from its four epilogue warps per CTA
-  plan->arrivals = plan->pair ? NUM_EPI_WARPS : epi_arrivals(plan->any_3x || plan->any_colsum);
-  const unsigned ARRIVALS_PER_TILE = (unsigned)plan->arrivals;
+  // transform warps: per op in the step kernel, per launch in the pair kernel
+  for (auto &g : plan->ops)
+    g.xform = (g.op_kind == OPK_GEMM && (plan->any_3x || (g.colsum != nullptr && g.b_mn))) ? 1 : 0;
+  plan->arrivals = plan->pair ? NUM_EPI_WARPS : NUM_WORKER_WARPS;
+  const unsigned A = (unsigned)plan->arrivals;
   for (int i = 0; i < n_ops; ++i) {
     GemmOp &g = plan->ops[i];
-    for (int w = 0; w < GPT2L_MAX_DEPS; ++w) {
-      const gpt2l_dep &dep = ops[i].deps[w];
+    if ((int)specs[i].deps.size() > MAX_WAITS) return GPT2L_ERR_SCHEDULE;
+    int w = 0;
+    for (const auto &dep : specs[i].deps) {
       if (dep.kind == GPT2L_DEP_NONE) continue;
       if (dep.producer < 0 || dep.producer >= i) return GPT2L_ERR_SCHEDULE;  // must point backwards
       const GemmOp &pr = plan->ops[dep.producer];
-      if (dep.kind == GPT2L_DEP_ROWBLOCK) {
+      // arrivals a complete 128-row block / the complete op shows
+      unsigned per_block, whole;
+      if (pr.op_kind == OPK_GEMM) {
+        per_block = A * pr.tiles_n * pr.splits;
+        whole = A * pr.tiles_m * pr.tiles_n * pr.splits;
+      } else if (pr.op_kind >= OPK_ATTN_FWD && pr.op_kind <= OPK_ATTN_BWD_Q) {
+        per_block = A * pr.ra.i3;
+        whole = A * pr.n_tiles;
+      } else if (pr.op_kind == OPK_ADAMW) {
+        per_block = whole = A * pr.n_tiles;
+      } else {
+        per_block = A * (BM / pr.rows_per_tile);
+        whole = A * pr.n_tiles;
+      }
+      if (dep.kind == GPT2L_DEP_ROWBLOCK || dep.kind == DEP_SEQUENCE) {
         // row block r of the consumer reads rows [128r, 128r+128) of the producer's output
-        if (pr.Mc != g.Mc || g.a_mn) return GPT2L_ERR_SCHEDULE;
+        if (g.op_kind == OPK_GEMM && (pr.Mc != g.Mc || g.a_mn)) return GPT2L_ERR_SCHEDULE;
+        if (pr.tiles_m != g.tiles_m && g.op_kind != OPK_ADAMW) return GPT2L_ERR_SCHEDULE;
+        if (dep.kind == DEP_SEQUENCE && (g.rb_per_seq <= 0 || pr.tiles_m % g.rb_per_seq != 0)) return GPT2L_ERR_SCHEDULE;
         g.wait_ctr[w] = pr.pub_rb_base;
-        g.wait_kind[w] = GPT2L_DEP_ROWBLOCK;
-        g.wait_expected[w] = (int)(ARRIVALS_PER_TILE * pr.tiles_n * pr.splits);
+        g.wait_kind[w] = dep.kind;
+        g.wait_expected[w] = (int)per_block;
       } else if (dep.kind == GPT2L_DEP_WHOLE_OP) {
         g.wait_ctr[w] = pr.pub_op_ctr;
         g.wait_kind[w] = GPT2L_DEP_WHOLE_OP;
-        g.wait_expected[w] = (int)(ARRIVALS_PER_TILE * pr.tiles_m * pr.tiles_n * pr.splits);
+        g.wait_expected[w] = (int)whole;
       } else {
         return GPT2L_ERR_SCHEDULE;
       }
+      ++w;
     }
   }
   plan->total_tiles = tile_base;
@@ -100,16 +154,39 @@ static int make_plan(const gpt2l_op *ops, int n_ops, int num_sms, Plan *plan) {
   return GPT2L_OK;
 }
 
+// 128-row blocks a tile of op g touches as a consumer / publishes as a producer
+static void tile_blocks(const GemmOp &g, int local, bool pair, int *rb, int *n_rb) {
+  if (g.op_kind == OPK_GEMM) {
+    int m_dec, n_tile, split;
+    decode_local(local, g.tiles_dec, g.tiles_n, g.band_m, m_dec, n_tile, split);
+    *rb = pair ? 2 * m_dec : m_dec;
+    *n_rb = pair ? ((2 * m_dec + 1 < g.tiles_m) ? 2 : 1) : 1;
+  } else if (g.op_kind == OPK_ADAMW) {
+    *rb = 0;
+    *n_rb = 1;
+  } else if (g.op_kind >= OPK_ATTN_FWD && g.op_kind <= OPK_ATTN_BWD_Q) {
+    // tile order: see attention_tile_coords()
+    const int per_seq = g.rb_per_seq, heads = g.ra.i3;
+    const int seq = local / (per_seq * heads), i = (local % (per_seq * heads)) / heads;
+    const int blk = g.op_kind == OPK_ATTN_BWD_KV ? i : per_seq - 1 - i;
+    *rb = seq * per_seq + blk;
+    *n_rb = 1;
+  } else {
+    *rb = (int)(((long long)local * g.rows_per_tile) / BM);
+    *n_rb = 1;
+  }
+}
+
 // Replays the schedule: CTA c owns tiles c, c+grid, ... and runs them in order; a tile may
 // run when its counters have reached the expected values. Returns OK when every tile ran.
-static int replay(const Plan &plan, int grid) {
+int replay(const Plan &plan, int grid) {
   if (grid <= 0) return GPT2L_ERR_BAD_ARG;
   std::vector<long long> counters(plan.n_counters, 0);
   std::vector<int> next(grid);
   for (int c = 0; c < grid; ++c) next[c] = c;
   int remaining = plan.total_tiles;
   std::vector<int> cursor(grid, 0);
-  const int ARRIVALS_PER_TILE = plan.arrivals;
+  const int A = plan.arrivals;
   while (remaining > 0) {
     bool progress = false;
     for (int c = 0; c < grid; ++c) {
@@ -118,27 +195,26 @@ static int replay(const Plan &plan, int grid) {
         int &cur = cursor[c];
         while (cur + 1 < (int)plan.ops.size() && t >= plan.ops[cur].tile_base + plan.ops[cur].n_tiles) ++cur;
         const GemmOp &g = plan.ops[cur];
-        int m_dec, n_tile, split;
-        decode_local(t - g.tile_base, g.tiles_dec, g.tiles_n, g.band_m, m_dec, n_tile, split);
-        // a pair tile covers two 128-row blocks, one per CTA
-        const int halves = g.pair ? 2 : 1;
+        int rb0, n_rb;
+        tile_blocks(g, t - g.tile_base, plan.pair, &rb0, &n_rb);
         bool ready = true;
-        for (int h = 0; h < halves; ++h) {
-          const int m_tile = g.pair ? 2 * m_dec + h : m_dec;
-          if (m_tile >= g.tiles_m) continue;
+        for (int h = 0; h < n_rb; ++h) {
+          const int rb = rb0 + h;
           for (int w = 0; w < MAX_WAITS; ++w) {
             if (g.wait_ctr[w] < 0) continue;
-            const int idx = g.wait_ctr[w] + (g.wait_kind[w] == GPT2L_DEP_ROWBLOCK ? m_tile : 0);
-            if (idx < 0 || idx >= plan.n_counters) return GPT2L_ERR_SCHEDULE;
-            if (counters[idx] < g.wait_expected[w]) ready = false;
+            int first = g.wait_ctr[w], count = 1;
+            if (g.wait_kind[w] == GPT2L_DEP_ROWBLOCK) first += rb;
+            else if (g.wait_kind[w] == DEP_SEQUENCE) { first += (rb / g.rb_per_seq) * g.rb_per_seq; count = g.rb_per_seq; }
+            for (int i = 0; i < count; ++i) {
+              if (first + i < 0 || first + i >= plan.n_counters) return GPT2L_ERR_SCHEDULE;
+              if (counters[first + i] < g.wait_expected[w]) ready = false;
+            }
           }
         }
         if (!ready) break;
-        for (int h = 0; h < halves; ++h) {
-          const int m_tile = g.pair ? 2 * m_dec + h : m_dec;
-          if (m_tile >= g.tiles_m) continue;
-          counters[g.pub_rb_base + m_tile] += ARRIVALS_PER_TILE;
-          counters[g.pub_op_ctr] += ARRIVALS_PER_TILE;
+        for (int h = 0; h < n_rb; ++h) {
+          counters[g.pub_rb_base + rb0 + h] += A;
+          counters[g.pub_op_ctr] += A;
         }
         next[c] += grid;
         --remaining;
@@ -154,56 +230,21 @@ static int replay(const Plan &plan, int grid) {
 
 using namespace g2l;
 
-struct gpt2l_schedule {
-  Plan plan;
-  std::vector<gpt2l_op> user_ops;
-  GemmOp *d_ops = nullptr;
-  unsigned *d_counters = nullptr;
-  Status *d_status = nullptr;
-  float *ws = nullptr;
-  unsigned *ws_sem = nullptr;
-  int grid = 0;
-  long long wait_limit_ns = 0;
-  DeviceCtx *ctx = nullptr;
-};
+namespace g2l {
 
-extern "C" {
-
-int gpt2_schedule_validate(const gpt2l_op *ops, int n_ops, int grid) {
-  Plan plan;
-  int e = make_plan(ops, n_ops, grid, &plan);
-  if (e) return e;
-  int units = plan.pair ? (grid / 2 > 0 ? grid / 2 : 1) : grid;  // CTAs, or CTA pairs
-  if (units > plan.total_tiles) units = plan.total_tiles;
-  return replay(plan, units);
-}
-
-int gpt2_schedule_describe(const gpt2l_op *ops, int n_ops, int num_sms, int counts[3]) {
-  Plan plan;
-  int e = make_plan(ops, n_ops, num_sms, &plan);
-  if (e) return e;
-  if (counts) {
-    counts[0] = plan.total_tiles;
-    counts[1] = plan.n_counters;
-    const int units = plan.pair ? (num_sms / 2 > 0 ? num_sms / 2 : 1) : num_sms;
-    counts[2] = units < plan.total_tiles ? units : plan.total_tiles;  // CTAs, or CTA pairs
-  }
-  return GPT2L_OK;
-}
-
-gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
+gpt2l_schedule *schedule_build(const std::vector<OpSpec> &specs, int grid_limit, int *err) {
   int e = GPT2L_OK;
-  int dummy;
-  if (!err) err = &dummy;
   DeviceCtx *ctx = ctx_current(&e);
   if (!ctx) { *err = e; return nullptr; }
   gpt2l_schedule *s = new gpt2l_schedule();
   s->ctx = ctx;
-  e = make_plan(ops, n_ops, ctx->num_sms, &s->plan);
+  s->specs = specs;
+  e = make_plan(specs, ctx->num_sms, &s->plan);
   if (e) { *err = e; delete s; return nullptr; }
-  s->user_ops.assign(ops, ops + n_ops);
+  const int n_ops = (int)specs.size();
   {
-    const int units = s->plan.pair ? ctx->max_pairs : ctx->num_sms;  // CTA pairs or CTAs
+    int units = s->plan.pair ? ctx->max_pairs : ctx->num_sms;  // CTA pairs or CTAs
+    if (grid_limit > 0 && grid_limit < units) units = grid_limit;
     s->grid = units < s->plan.total_tiles ? units : s->plan.total_tiles;
     if (s->grid <= 0) { *err = GPT2L_ERR_CUDA; delete s; return nullptr; }
   }
@@ -212,7 +253,8 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
   // tensor maps + workspace
   size_t ws_bytes = 0, sem_count = 0;
   for (int i = 0; i < n_ops; ++i) {
-    GemmDesc d = desc_from(ops[i]);
+    if (specs[i].kind != OPK_GEMM) continue;
+    GemmDesc d = specs[i].gemm;
     d.opts.cta_pair = s->plan.pair ? 2 : 1;
     if (!d.out || !d.a || !d.b || !tma_eligible(d)) { *err = GPT2L_ERR_BAD_ARG; delete s; return nullptr; }
     GemmOp full;
@@ -225,8 +267,17 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
     g.tmC2 = full.tmC2;
     g.a_3d = full.a_3d;
     g.b_3d = full.b_3d;
+    if (specs[i].transposed_a) {
+      // the forward form of a weight gradient: the B operand is still g_out, its column sums are g_b
+      g.colsum = specs[i].gemm.out_bias;
+      g.colsum_spread = g.colsum ? 1 : 0;
+      g.xform = (s->plan.any_3x || g.colsum) ? 1 : 0;
+    }
     ws_bytes += op_workspace_bytes(g);
     if (g.splits > 1 && !g.atomic_out) sem_count += (size_t)g.tiles_m * g.tiles_n * 4;
+    // accumulated outputs start from zero at every launch
+    if (g.splits > 1 && g.atomic_out) s->zero.push_back({g.C, (size_t)g.Mc * g.Nc * sizeof(float)});
+    if (g.colsum && (g.splits > 1 || g.colsum_spread)) s->zero.push_back({g.colsum, (size_t)g.Nc * sizeof(float)});
   }
   bool ok = true;
   if (ws_bytes) {
@@ -235,7 +286,7 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
     ok = ok && cudaMemset(s->ws_sem, 0, sem_count * sizeof(unsigned)) == cudaSuccess;
     size_t off = 0, soff = 0;
     for (auto &g : s->plan.ops) {
-      if (g.splits > 1 && !g.atomic_out) {
+      if (g.op_kind == OPK_GEMM && g.splits > 1 && !g.atomic_out) {
         g.ws = s->ws + off / sizeof(float);
         g.ws_sem = s->ws_sem + soff;
         off += op_workspace_bytes(g);
@@ -258,6 +309,46 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
   return s;
 }
 
+}  // namespace g2l
+
+static std::vector<OpSpec> specs_from(const gpt2l_op *ops, int n_ops) {
+  std::vector<OpSpec> v;
+  if (ops)
+    for (int i = 0; i < n_ops; ++i) v.push_back(spec_from(ops[i]));
+  return v;
+}
+
+extern "C" {
+
+int gpt2_schedule_validate(const gpt2l_op *ops, int n_ops, int grid) {
+  Plan plan;
+  int e = make_plan(specs_from(ops, n_ops), grid, &plan);
+  if (e) return e;
+  int units = plan.pair ? (grid / 2 > 0 ? grid / 2 : 1) : grid;  // CTAs, or CTA pairs
+  if (units > plan.total_tiles) units = plan.total_tiles;
+  return replay(plan, units);
+}
+
+int gpt2_schedule_describe(const gpt2l_op *ops, int n_ops, int num_sms, int counts[3]) {
+  Plan plan;
+  int e = make_plan(specs_from(ops, n_ops), num_sms, &plan);
+  if (e) return e;
+  if (counts) {
+    counts[0] = plan.total_tiles;
+    counts[1] = plan.n_counters;
+    const int units = plan.pair ? (num_sms / 2 > 0 ? num_sms / 2 : 1) : num_sms;
+    counts[2] = units < plan.total_tiles ? units : plan.total_tiles;  // CTAs, or CTA pairs
+  }
+  return GPT2L_OK;
+}
+
+gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
+  int dummy;
+  if (!err) err = &dummy;
+  if (!ops || n_ops <= 0) { *err = GPT2L_ERR_BAD_ARG; return nullptr; }
+  return schedule_build(specs_from(ops, n_ops), 0, err);
+}
+
 void gpt2_schedule_destroy(gpt2l_schedule *s) {
   if (!s) return;
   if (s->d_ops) cudaFree(s->d_ops);
@@ -265,29 +356,24 @@ void gpt2_schedule_destroy(gpt2l_schedule *s) {
   if (s->d_status) cudaFree(s->d_status);
   if (s->ws) cudaFree(s->ws);
   if (s->ws_sem) cudaFree(s->ws_sem);
+  if (s->d_fmaps) cudaFree(s->d_fmaps);
+  if (s->d_prof) cudaFree(s->d_prof);
   delete s;
 }
 
 int gpt2_megakernel_run(gpt2l_schedule *s, gpt2l_stream_t stream) {
   if (!s) return GPT2L_ERR_BAD_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (*reinterpret_cast<volatile int *>(s->ctx->h_flag) != 0) return GPT2L_DEV_TIMEOUT;  // see gpt2_linear_last_status
   // the reference zeroes bar[] before every launch (tests/test_train_mk.cu:285); so do we
   if (cudaMemsetAsync(s->d_counters, 0, sizeof(unsigned) * s->plan.n_counters, st) != cudaSuccess)
     return GPT2L_ERR_CUDA;
   if (cudaMemsetAsync(s->d_status, 0, sizeof(Status), st) != cudaSuccess) return GPT2L_ERR_CUDA;
-  for (const auto &g : s->plan.ops) {
-    if (g.splits > 1) {
-      if (g.atomic_out &&
-          cudaMemsetAsync(g.C, 0, (size_t)g.Mc * g.Nc * sizeof(float), st) != cudaSuccess)
-        return GPT2L_ERR_CUDA;
-      if (g.colsum && cudaMemsetAsync(g.colsum, 0, (size_t)g.Nc * sizeof(float), st) != cudaSuccess)
-        return GPT2L_ERR_CUDA;
-    } else if (g.colsum && g.colsum_spread) {
-      if (cudaMemsetAsync(g.colsum, 0, (size_t)g.Nc * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
-    }
-  }
-  return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x, s->plan.any_colsum, s->plan.pair,
-                     s->d_status, s->d_counters, s->wait_limit_ns, st);
+  for (const auto &z : s->zero)
+    if (cudaMemsetAsync(z.ptr, 0, z.bytes, st) != cudaSuccess) return GPT2L_ERR_CUDA;
+  return launch_list(s->ctx, s->d_ops, (int)s->plan.ops.size(), s->plan.total_tiles, s->grid, s->plan.any_3x,
+                     s->plan.any_colsum, s->plan.pair, s->d_status, s->d_counters, s->wait_limit_ns, s->adam, s->d_fmaps,
+                     s->d_prof, st);
 }
 
 int gpt2_megakernel_status(gpt2l_schedule *s) {
@@ -304,6 +390,44 @@ int gpt2_schedule_debug_set_expected(gpt2l_schedule *s, int op, int dep, int exp
   if (cudaMemcpy(s->d_ops + op, &s->plan.ops[op], sizeof(GemmOp), cudaMemcpyHostToDevice) != cudaSuccess)
     return GPT2L_ERR_CUDA;
   return GPT2L_OK;
+}
+
+// Per-tile profile of the next runs: {start (%globaltimer ns), SM id << 48 | ns spent} per tile, in the
+// global tile order (the reference keeps per-instruction %globaltimer arrays, src/mk.cu:966-971,
+// 1117-1138, 1814-1819). enable = 0 stops recording.
+int gpt2_schedule_profile(gpt2l_schedule *s, int enable) {
+  if (!s) return GPT2L_ERR_BAD_ARG;
+  if (enable && !s->d_prof) {
+    if (cudaMalloc(reinterpret_cast<void **>(&s->d_prof), sizeof(unsigned long long) * 2 * (size_t)s->plan.total_tiles) !=
+        cudaSuccess) {
+      (void)cudaGetLastError();
+      return GPT2L_ERR_CUDA;
+    }
+    cudaMemset(s->d_prof, 0, sizeof(unsigned long long) * 2 * (size_t)s->plan.total_tiles);
+  } else if (!enable && s->d_prof) {
+    cudaFree(s->d_prof);
+    s->d_prof = nullptr;
+  }
+  return GPT2L_OK;
+}
+
+// Copies the profile of the last run to the host: for tile i, out[4*i .. 4*i+3] = {op index, start ns,
+// duration ns, SM id}. Returns the number of tiles, or a negative error. `max_tiles` bounds the copy.
+long long gpt2_schedule_read_profile(gpt2l_schedule *s, long long *out, long long max_tiles) {
+  if (!s || !out || !s->d_prof) return GPT2L_ERR_BAD_ARG;
+  const long long n = s->plan.total_tiles < max_tiles ? s->plan.total_tiles : max_tiles;
+  std::vector<unsigned long long> h(2 * (size_t)n);
+  if (cudaMemcpy(h.data(), s->d_prof, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return GPT2L_ERR_CUDA;
+  size_t cur = 0;
+  for (long long i = 0; i < n; ++i) {
+    while (cur + 1 < s->plan.ops.size() && i >= s->plan.ops[cur].tile_base + s->plan.ops[cur].n_tiles) ++cur;
+    out[4 * i] = (long long)cur;
+    out[4 * i + 1] = (long long)h[2 * i];
+    out[4 * i + 2] = (long long)(h[2 * i + 1] & 0xffffffffffffull);
+    out[4 * i + 3] = (long long)(h[2 * i + 1] >> 48);
+  }
+  return n;
 }
 
 }  // extern "C"

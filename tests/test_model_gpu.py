@@ -289,10 +289,11 @@ def _sampled_gradient_errors(z, grads):
 # 3xTF32 mode (batched-GEMM attention) must hold the 1e-3 per-step loss bound. TF32 mode runs the fused
 # attention kernels (eight 128-row blocks per head) and the single-pass tensor-core GEMMs: its products
 # carry ~1e-3 relative error each, the loss falls by 4.6 over these six steps (an over-fit of one batch at
-# a high learning rate, so errors of one step feed the next), and the bound stated for it is 3e-2 on the
-# loss and 3e-2 of each tensor's largest gradient.
-@pytest.mark.parametrize("mode,graph,tol_loss,tol_grad", [(1, False, 1e-3, 5e-4), (0, False, 3e-2, 3e-2),
-                                                         (0, True, 3e-2, 3e-2)])
+# a high learning rate, so errors of one step feed the next), and the bound stated for it is 5e-3 on the
+# loss and 1e-2 of each tensor's largest gradient (measured on a B200: 1.4e-3 and 2.6e-3; 3xTF32: 1.5e-5
+# and 2.2e-5).
+@pytest.mark.parametrize("mode,graph,tol_loss,tol_grad", [(1, False, 1e-3, 5e-4), (0, False, 5e-3, 1e-2),
+                                                         (0, True, 5e-3, 1e-2)])
 def test_sequence_length_1024_tracks_the_reference_model(gpu, mode, graph, tol_loss, tol_grad):
     z = golden("llm_train_t1024.npz")
     m, params, tok, tgt, steps = build(gpu, z, mode)
