@@ -49,6 +49,7 @@ EXPORTS = [
     "gpt2_linear_backward_weight_host_async", "gpt2_linear_host_synchronize",
     "gpt2_schedule_create", "gpt2_schedule_destroy", "gpt2_schedule_validate", "gpt2_schedule_describe",
     "gpt2_megakernel_run", "gpt2_megakernel_status", "gpt2_schedule_debug_set_expected",
+    "gpt2_schedule_profile", "gpt2_schedule_read_profile",
 ]
 # every symbol include/gpt2_model.h declares
 ATTENTION_EXPORTS = ["gpt2_attention_supported", "gpt2_attention_forward", "gpt2_attention_backward",
@@ -62,7 +63,11 @@ MODEL_EXPORTS = [
     "gpt2_model_backward_head", "gpt2_model_backward_layer", "gpt2_model_backward_embedding",
     "gpt2_model_device_bytes", "gpt2_model_update_range", "gpt2_model_load_weights", "gpt2_model_dump_weights",
     "gpt2_model_save_checkpoint", "gpt2_model_load_checkpoint", "gpt2_model_forward_backward_graph",
+    "gpt2_schedule_instructions", "gpt2_free_schedule", "gpt2_megakernel_step", "gpt2_megakernel_step_status",
+    "gpt2_megakernel_step_info", "gpt2_megakernel_step_debug_set_expected",
 ]
+STEP_WITH_UPDATE = 1
+STEP_ATTENTION_IN_KERNEL = 2
 
 
 class Opts(ctypes.Structure):
@@ -216,6 +221,22 @@ def _load():
     lib.gpt2_model_save_checkpoint.restype = I
     lib.gpt2_model_load_checkpoint.argtypes = [V, ctypes.c_char_p, ctypes.POINTER(I)]
     lib.gpt2_model_load_checkpoint.restype = I
+    lib.gpt2_schedule_profile.argtypes = [V, I]
+    lib.gpt2_schedule_profile.restype = I
+    lib.gpt2_schedule_read_profile.argtypes = [V, P, LL]
+    lib.gpt2_schedule_read_profile.restype = LL
+    lib.gpt2_schedule_instructions.argtypes = [V, P, P, ctypes.c_uint, ctypes.POINTER(I)]
+    lib.gpt2_schedule_instructions.restype = V
+    lib.gpt2_free_schedule.argtypes = [V]
+    lib.gpt2_free_schedule.restype = None
+    lib.gpt2_megakernel_step.argtypes = [V, F, F, F, F, F, I, V]
+    lib.gpt2_megakernel_step.restype = I
+    lib.gpt2_megakernel_step_status.argtypes = [V]
+    lib.gpt2_megakernel_step_status.restype = I
+    lib.gpt2_megakernel_step_info.argtypes = [V, ctypes.POINTER(I * 3)]
+    lib.gpt2_megakernel_step_info.restype = I
+    lib.gpt2_megakernel_step_debug_set_expected.argtypes = [V, I, I, I, I, I]
+    lib.gpt2_megakernel_step_debug_set_expected.restype = I
     # ---- gpt2_attention.h ----
     lib.gpt2_attention_supported.argtypes = [I, I, I, I]
     lib.gpt2_attention_supported.restype = I
@@ -466,6 +487,44 @@ class Model:
     def close(self):
         if self.handle:
             lib.gpt2_model_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Step:
+    """Owns a gpt2l_step (include/gpt2_model.h): one training step of a Model as a schedule of the persistent
+    kernel. tokens / targets are device int32 tensors that must outlive the object."""
+
+    def __init__(self, model, tokens, targets, with_update=True, attention_in_kernel=False):
+        self.model, self.tokens, self.targets = model, tokens, targets
+        flags = (STEP_WITH_UPDATE if with_update else 0) | (STEP_ATTENTION_IN_KERNEL if attention_in_kernel else 0)
+        err = ctypes.c_int(0)
+        self.handle = lib.gpt2_schedule_instructions(model.handle, _p(tokens), _p(targets), flags, ctypes.byref(err))
+        if not self.handle:
+            raise LinearError("gpt2_schedule_instructions", err.value)
+
+    def run(self, lr=0.0, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, t=1, stream=None):
+        return lib.gpt2_megakernel_step(self.handle, lr, beta1, beta2, eps, weight_decay, t, stream)
+
+    def status(self):
+        return lib.gpt2_megakernel_step_status(self.handle)
+
+    def info(self):
+        out = (ctypes.c_int * 3)()
+        check("gpt2_megakernel_step_info", lib.gpt2_megakernel_step_info(self.handle, ctypes.byref(out)))
+        return {"ops": out[0], "launches": out[1], "tiles": out[2]}
+
+    def debug_set_expected(self, piece, op, dep, expected, wait_limit_ms=0):
+        return lib.gpt2_megakernel_step_debug_set_expected(self.handle, piece, op, dep, expected, wait_limit_ms)
+
+    def close(self):
+        if self.handle:
+            lib.gpt2_free_schedule(self.handle)
             self.handle = None
 
     def __del__(self):

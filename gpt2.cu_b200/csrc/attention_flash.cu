@@ -656,8 +656,15 @@ int attention_flash_backward(float *dqkv, float *delta, const float *dout, const
   if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
   int e = attention_row_dot(delta, dout, out, B, T, C, NH, st);
   if (e) return e;
+  return attention_flash_backward_core(dqkv, delta, dout, qkv, lse, B, T, C, NH, st);
+}
+
+// the two backward kernels alone: delta[b][h][t] = rowsum(dout o out) has been computed by the caller
+int attention_flash_backward_core(float *dqkv, const float *delta, const float *dout, const float *qkv,
+                                  const float *lse, int B, int T, int C, int NH, cudaStream_t st) {
+  if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
   FlashMaps maps, maps_kv;  // the two kernels step by different widths: different K-major boxes
-  e = build_maps(&maps, qkv, dout, B, T, C, NH, Cfg<F_BWD_Q>::FC);
+  int e = build_maps(&maps, qkv, dout, B, T, C, NH, Cfg<F_BWD_Q>::FC);
   if (e) return e;
   e = build_maps(&maps_kv, qkv, dout, B, T, C, NH, Cfg<F_BWD_KV>::FC);
   if (e) return e;

@@ -274,6 +274,14 @@ int gpt2_megakernel_status(gpt2l_schedule *s);
 int gpt2_schedule_debug_set_expected(gpt2l_schedule *s, int op, int dep, int expected,
                                      int wait_limit_ms);
 
+/* Per-tile profile of the following runs of `s` (the reference keeps %globaltimer arrays per instruction,
+ * src/mk.cu:966-971, 1117-1138, 1814-1819): enable = 1 allocates the record, 0 frees it.
+ * gpt2_schedule_read_profile copies the record of the last run: for tile i (global tile order),
+ * out[4i..4i+3] = {op index, start in ns (%globaltimer), ns the tile's epilogue / worker warp spent in it,
+ * SM id}; returns the number of tiles copied (at most max_tiles) or a negative error. */
+int gpt2_schedule_profile(gpt2l_schedule *s, int enable);
+long long gpt2_schedule_read_profile(gpt2l_schedule *s, long long *out, long long max_tiles);
+
 #ifdef __cplusplus
 }
 #endif

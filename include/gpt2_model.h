@@ -82,6 +82,41 @@ float gpt2_model_mean_loss(gpt2_model *m, gpt2l_stream_t stream);
 /* Bytes of device memory the model holds. */
 long long gpt2_model_device_bytes(const gpt2_model *m);
 
+/* ------------------------------------------------------------------------------------------------
+ * The same training step as a schedule of the persistent kernel: what schedule_instructions /
+ * free_schedule (include/gpt2/mk.h:34, src/mk.cu:281-942) and the launch of megakernel
+ * (tests/test_train_mk.cu:292-314) are in the reference. gpt2_schedule_instructions builds the op list of
+ * one step of `m` on fixed token / target buffers — embedding, the blocks, loss, the backward pass with
+ * every weight gradient, the embedding backward and (GPT2_STEP_WITH_UPDATE) AdamW — derives the tile
+ * dependencies from the buffers each op reads and writes, and uploads it; gpt2_megakernel_step runs it.
+ * Where the reference takes a config_t and returns per-SM instruction streams, this takes the model
+ * (which owns the buffers the reference passes to the kernel launch) and returns an opaque handle; the
+ * dependency counters are per 128-row block, every wait is bounded, and a step that gave up on a wait
+ * reports GPT2L_DEV_TIMEOUT through gpt2_megakernel_step_status instead of hanging.
+ * Without GPT2_STEP_ATTENTION_IN_KERNEL the attention passes are launched between the persistent pieces
+ * (one piece and one attention pass per block and direction instead of a single launch), with whichever
+ * attention implementation the model uses. Needs n_embd <= 1280, and for attention inside the launch the
+ * fused attention (T % 128 == 0, TF32 mode or GPT2_ATTENTION=flash); otherwise GPT2L_ERR_TOO_LARGE and the
+ * caller keeps using gpt2_model_forward / _backward / _update. tokens / targets must stay valid and in place.
+ * ------------------------------------------------------------------------------------------------ */
+#define GPT2_STEP_WITH_UPDATE 1u         /* AdamW inside the step (single GPU)                          */
+#define GPT2_STEP_ATTENTION_IN_KERNEL 2u /* attention tiles inside the persistent launch                */
+typedef struct gpt2l_step gpt2l_step;
+gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const int *targets, unsigned flags, int *err);
+void gpt2_free_schedule(gpt2l_step *s);
+/* One step. lr ... t are AdamW's (ignored without GPT2_STEP_WITH_UPDATE); the losses of the forward pass
+ * are left where gpt2_model_mean_loss reads them. */
+int gpt2_megakernel_step(gpt2l_step *s, float lr, float beta1, float beta2, float eps, float weight_decay, int t,
+                         gpt2l_stream_t stream);
+/* After the stream has been synchronised: 0, or GPT2L_DEV_TIMEOUT when a wait of the last step gave up. */
+int gpt2_megakernel_step_status(gpt2l_step *s);
+/* out = {ops in the step, kernel launches per step, tiles per step}. */
+int gpt2_megakernel_step_info(const gpt2l_step *s, int out[3]);
+/* Test hook for the bounded waits (host-side fault injection; no device fault is provoked): overrides the
+ * arrival count dependency `dep` of op `op` of persistent piece `piece` waits for, and that piece's wait
+ * limit in milliseconds (0 keeps the default). */
+int gpt2_megakernel_step_debug_set_expected(gpt2l_step *s, int piece, int op, int dep, int expected, int wait_limit_ms);
+
 /* ---- files (blocking; they synchronise the device) ---- */
 #define GPT2M_ERR_IO (-7)     /* open / read / write failed                                   */
 #define GPT2M_ERR_FORMAT (-8) /* size, magic or configuration does not match this model       */

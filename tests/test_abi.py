@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(g):
 
 
 def test_library_exports_every_model_symbol(g):
-    names = [n for n in header_functions("gpt2_model.h") if n.startswith("gpt2_model_")]
+    names = header_functions("gpt2_model.h")  # the model calls and the step-schedule calls
     assert sorted(names) == sorted(g.MODEL_EXPORTS)
     for n in names:
         assert hasattr(g.lib, n)
