@@ -65,6 +65,7 @@ MODEL_EXPORTS = [
     "gpt2_model_save_checkpoint", "gpt2_model_load_checkpoint", "gpt2_model_forward_backward_graph",
     "gpt2_schedule_instructions", "gpt2_free_schedule", "gpt2_megakernel_step", "gpt2_megakernel_step_status",
     "gpt2_megakernel_step_info", "gpt2_megakernel_step_debug_set_expected",
+    "gpt2_megakernel_step_profile", "gpt2_megakernel_step_read_profile",
 ]
 STEP_WITH_UPDATE = 1
 STEP_ATTENTION_IN_KERNEL = 2
@@ -235,6 +236,10 @@ def _load():
     lib.gpt2_megakernel_step_status.restype = I
     lib.gpt2_megakernel_step_info.argtypes = [V, ctypes.POINTER(I * 3)]
     lib.gpt2_megakernel_step_info.restype = I
+    lib.gpt2_megakernel_step_profile.argtypes = [V, I]
+    lib.gpt2_megakernel_step_profile.restype = I
+    lib.gpt2_megakernel_step_read_profile.argtypes = [V, I, P, LL]
+    lib.gpt2_megakernel_step_read_profile.restype = LL
     lib.gpt2_megakernel_step_debug_set_expected.argtypes = [V, I, I, I, I, I]
     lib.gpt2_megakernel_step_debug_set_expected.restype = I
     # ---- gpt2_attention.h ----
@@ -518,6 +523,23 @@ class Step:
         out = (ctypes.c_int * 3)()
         check("gpt2_megakernel_step_info", lib.gpt2_megakernel_step_info(self.handle, ctypes.byref(out)))
         return {"ops": out[0], "launches": out[1], "tiles": out[2]}
+
+    def profile(self, enable=True):
+        check("gpt2_megakernel_step_profile", lib.gpt2_megakernel_step_profile(self.handle, 1 if enable else 0))
+
+    def read_profile(self, piece, max_tiles=1 << 22):
+        """numpy int64 array [tiles][4] = (op index, op kind, start ns, duration ns, SM) -> columns op, kind, start, ns, sm"""
+        import numpy as np
+        buf = np.zeros((max_tiles, 4), np.int64)
+        n = lib.gpt2_megakernel_step_read_profile(self.handle, piece, buf.ctypes.data, max_tiles)
+        if n < 0:
+            return None
+        buf = buf[:n]
+        out = np.zeros((n, 5), np.int64)
+        out[:, 0] = buf[:, 0] & 0xffffffff
+        out[:, 1] = buf[:, 0] >> 32
+        out[:, 2:] = buf[:, 1:]
+        return out
 
     def debug_set_expected(self, piece, op, dep, expected, wait_limit_ms=0):
         return lib.gpt2_megakernel_step_debug_set_expected(self.handle, piece, op, dep, expected, wait_limit_ms)

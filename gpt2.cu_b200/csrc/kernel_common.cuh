@@ -25,7 +25,8 @@ struct Ctrl {
   uint32_t tmem_base;
   int abort;
 };
-static_assert(sizeof(Ctrl) <= SMEM_CTRL_BYTES, "control block too large");
+constexpr int CTRL_MAIN_BYTES = 256;  // the attention tiles' three barrier sets follow at this offset
+static_assert(sizeof(Ctrl) <= CTRL_MAIN_BYTES, "control block too large");
 
 struct Tile {
   int m_tile, n_tile, split;

@@ -31,7 +31,7 @@ constexpr int NUM_EPI_WARPS = 4;
 // counter arrivals one finished tile produces in the one-CTA kernel: the transform warps double as
 // epilogue warps (and publish) in launches that need no transform
 constexpr int epi_arrivals(bool xform_active) { return xform_active ? NUM_EPI_WARPS : 2 * NUM_EPI_WARPS; }
-constexpr int SMEM_CTRL_BYTES = 512;  // mbarriers + tmem pointer + abort flag
+constexpr int SMEM_CTRL_BYTES = 1024;  // mbarriers + tmem pointer + abort flag; the attention tiles' barriers behind them
 constexpr int EPI_BUF_BYTES = 32 * 32 * 4;                       // one 32 x 32 fp32 store box
 constexpr int EPI_BYTES = NUM_EPI_WARPS * 2 * EPI_BUF_BYTES;    // two boxes per epilogue warp
 constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + RING_BYTES + EPI_BYTES + SMEM_CTRL_BYTES;
@@ -292,6 +292,10 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
                 const float *adam, const FlashMaps *fmaps, unsigned long long *prof, cudaStream_t stream);
 int set_kernel_attributes();
 void count_launch(int n = 1);
+
+// --- attention_flash.cu ---
+// tensor maps of the fused attention over qkv[B*T][3C] and dout[B*T][C] (dout may be null: forward)
+int attention_flash_build_maps(FlashMaps *maps, const float *qkv, const float *dout, int B, int T, int C, int NH);
 
 // --- linear_simt.cu ---
 int launch_simt(const GemmDesc &d, cudaStream_t stream);

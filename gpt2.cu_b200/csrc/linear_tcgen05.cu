@@ -40,6 +40,7 @@
 #include "ptx_sm100.cuh"
 #include "kernel_common.cuh"
 #include "step_rowops.cuh"
+#include "attention_flash.cuh"
 
 namespace g2l {
 
@@ -311,7 +312,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
 
 // A non-GEMM tile of the step kernel, executed by one of the eight worker warps (w8 = 0..7). `scratch` is
 // the 32 KiB of epilogue boxes, free while all eight warps are inside the same tile.
-__device__ __forceinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, int w8, int lane, float *scratch,
+__device__ __noinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, int w8, int lane, float *scratch,
                                             RowSync &rs, Ctrl *ctrl, const LaunchParams &p) {
   const int tile = tc.m_tile;
   const int rpt = op->rows_per_tile;
@@ -355,6 +356,103 @@ __device__ __forceinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, in
 }
 
 // ------------------------------------------------------------------------------------
+// attention tiles inside the step kernel
+// ------------------------------------------------------------------------------------
+static_assert(CTRL_MAIN_BYTES + 3 * sizeof(flash::FlashCtrl) <= SMEM_CTRL_BYTES, "control region too small");
+static_assert(flash::Cfg<flash::F_BWD_KV>::OFF_CTRL <= RING_BYTES + EPI_BYTES, "attention tile does not fit");
+static_assert(flash::Cfg<flash::F_BWD_KV>::THREADS <= STEP_THREADS, "attention tile needs more warps");
+
+// Every warp's view of how far the CTA's attention barriers have been driven (see attn_tile_body): steps and
+// tiles per mode, and the number of CTA rendezvous so far. All warps run the same tiles, so all count alike.
+struct AttnProgress {
+  uint32_t steps[3] = {0u, 0u, 0u};
+  uint32_t tiles[3] = {0u, 0u, 0u};
+  uint32_t cta_phase = 0u;
+};
+
+// rendezvous of all STEP_THREADS / 32 warps (bounded like every other wait)
+__device__ __forceinline__ bool cta_sync(Ctrl *ctrl, const LaunchParams &p, AttnProgress &ap, int op, int lane) {
+  __syncwarp();
+  int okl = 1;
+  if (lane == 0) {
+    const uint32_t bar = smem_u32(&ctrl->cta_bar);
+    mbar_arrive(bar);
+    okl = wait_bar(bar, ap.cta_phase & 1u, ctrl, p, SITE_CTA_SYNC, op, (int)ap.cta_phase, 20) ? 1 : 0;
+  }
+  ++ap.cta_phase;
+  return __shfl_sync(0xffffffffu, okl, 0) != 0;
+}
+
+// One attention tile (128 rows of one head of one sequence) run by the whole CTA between two GEMM tiles:
+// everybody meets (the ring, the epilogue boxes and the tensor memory are idle then), the fused attention
+// code runs with its own barriers in the same shared memory and tensor memory, everybody meets again and
+// the worker warps publish the tile. Tile order inside the op: sequence, then row block (heavy ones first),
+// then head.
+// (not inlined: the attention code gets a register allocation of its own instead of sharing one with the
+// GEMM roles, whose state is dead while it runs)
+template <int MODE>
+__device__ __noinline__ bool attention_tile_mode(const GemmOp *op, int grb, int rb, int bh, uint8_t *ring_ptr, uint32_t ring,
+                                                    Ctrl *ctrl, uint32_t tmem_base, const LaunchParams &p, AttnProgress &ap,
+                                                    int warp, int lane) {
+  using namespace flash;
+  if (warp == 0) {
+    int okl = 1;
+    if (lane == 0) okl = wait_deps(op, grb, ctrl, p) ? 1 : 0;
+    if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
+    fence_proxy_async_all();  // the operands were written with plain stores; TMA reads them next
+  }
+  if (!cta_sync(ctrl, p, ap, op->op_index, lane)) return false;
+  FlashCtrl *fc = reinterpret_cast<FlashCtrl *>(reinterpret_cast<uint8_t *>(ctrl) + CTRL_MAIN_BYTES) + MODE;
+  const RowArgs &ra = op->ra;
+  FlashArgs a;
+  a.B = ra.i0; a.C = ra.i1; a.T = ra.i2; a.NH = ra.i3;
+  a.out = ra.out0;
+  a.lse = MODE == F_FWD ? ra.out1 : const_cast<float *>(ra.in2);
+  a.delta = ra.in3;
+  a.dqkv = ra.out0;
+  a.status = nullptr;
+  a.wait_limit_ns = p.wait_limit_ns;
+  a.cta_abort = &ctrl->abort;
+  a.step_status = p.status;
+  a.host_flag = p.host_flag;
+  a.op_index = op->op_index;
+  attn_tile_body<MODE>(p.fmaps[ra.i4], a, ring_ptr, ring, fc, tmem_base, warp, lane, rb, bh, ap.steps[MODE], ap.tiles[MODE]);
+  ap.steps[MODE] += (uint32_t)attn_tile_steps<MODE>(rb, a.T);
+  ap.tiles[MODE] += 1u;
+  if (*reinterpret_cast<volatile int *>(&fc->abort)) return false;
+  tc_fence_before();
+  __threadfence();  // the row-work warps' stores, before the rendezvous the publishing warps leave through
+  if (!cta_sync(ctrl, p, ap, op->op_index, lane)) return false;
+  tc_fence_after();
+  if (warp >= XFORM_WARP0 && warp < EPI_WARP0 + NUM_EPI_WARPS && lane == 0) {
+    if (op->pub_rb_base >= 0) red_release_add(p.counters + op->pub_rb_base + grb, 1u);
+    if (op->pub_op_ctr >= 0) red_release_add(p.counters + op->pub_op_ctr, 1u);
+  }
+  return true;
+}
+
+__device__ __forceinline__ bool attention_tile(const GemmOp *op, const Tile &tc, uint8_t *ring_ptr, uint32_t ring, Ctrl *ctrl,
+                                               uint32_t tmem_base, const LaunchParams &p, AttnProgress &ap, int warp, int lane) {
+  const int per_seq = op->rb_per_seq, heads = op->ra.i3;
+  const int local = tc.m_tile;
+  const int seq = local / (per_seq * heads);
+  const int i = (local % (per_seq * heads)) / heads;
+  const int h = local % heads;
+  const int rb = op->op_kind == OPK_ATTN_BWD_KV ? i : per_seq - 1 - i;
+  const int grb = seq * per_seq + rb;
+  const int bh = seq * heads + h;
+  if (op->op_kind == OPK_ATTN_FWD)
+    return attention_tile_mode<flash::F_FWD>(op, grb, rb, bh, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
+  if (op->op_kind == OPK_ATTN_BWD_KV)
+    return attention_tile_mode<flash::F_BWD_KV>(op, grb, rb, bh, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
+  return attention_tile_mode<flash::F_BWD_Q>(op, grb, rb, bh, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
+}
+
+__device__ __forceinline__ bool is_attention(const GemmOp *op) {
+  return op->op_kind >= OPK_ATTN_FWD && op->op_kind <= OPK_ATTN_BWD_Q;
+}
+
+// ------------------------------------------------------------------------------------
 // the kernel. MEGA = false: one GEMM (or a list of GEMMs whose transform needs are the same for the
 // whole launch). MEGA = true: the step kernel: GEMM ops with a per-op decision on the transform warps,
 // row-local ops on the worker warps, one more warp, profile stamps.
@@ -394,6 +492,12 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     }
     mbar_init(smem_u32(&ctrl->row_bar), NUM_WORKER_WARPS);
     mbar_init(smem_u32(&ctrl->cta_bar), STEP_THREADS / 32);
+    if (MEGA) {
+      flash::FlashCtrl *fc = reinterpret_cast<flash::FlashCtrl *>(reinterpret_cast<uint8_t *>(ctrl) + CTRL_MAIN_BYTES);
+      flash::attn_init_barriers(fc + flash::F_FWD, flash::Cfg<flash::F_FWD>::NCW);
+      flash::attn_init_barriers(fc + flash::F_BWD_Q, flash::Cfg<flash::F_BWD_Q>::NCW);
+      flash::attn_init_barriers(fc + flash::F_BWD_KV, flash::Cfg<flash::F_BWD_KV>::NCW);
+    }
     ctrl->abort = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -412,10 +516,15 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     int cursor = 0;
     uint32_t it = 0;
     bool ok = true;
+    AttnProgress ap;
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
-      if (MEGA && op->op_kind != OPK_GEMM) continue;  // the worker warps run these
+      if (MEGA && op->op_kind != OPK_GEMM) {
+        // attention tiles take the whole CTA; the row-local ops are the worker warps' alone
+        if (is_attention(op)) ok = attention_tile(op, tc, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
+        continue;
+      }
       if (tc.skip) continue;  // every role skips the same tiles, so no barrier phase is consumed
       // ---- dependency counters: do not touch the operands before their producers are done
       if (op->wait_ctr[0] >= 0) {  // dependencies fill the slots from 0 up
@@ -478,6 +587,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     int cursor = 0;
     uint32_t it = 0, tcount = 0;
     bool ok = true;
+    AttnProgress ap;
     int t = blockIdx.x;
     Tile tc;
     const GemmOp *op = nullptr;
@@ -490,6 +600,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const GemmOp *op_next = op;
       if (have_next) op_next = decode_tile(ops, n_ops, t_next, cursor, tc_next);
       if (tc.skip || (MEGA && op->op_kind != OPK_GEMM)) {
+        if (MEGA && is_attention(op)) ok = attention_tile(op, tc, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
         t = t_next; tc = tc_next; op = op_next; have = have_next;
         continue;
       }
@@ -604,6 +715,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
                           (uint32_t)(helper ? (warp - XFORM_WARP0) * 2 + 1 : (warp - EPI_WARP0) * 2) * EPI_BUF_BYTES;
     float *scratch = reinterpret_cast<float *>(ring_ptr + RING_BYTES);
     RowSync rs = {smem_u32(&ctrl->row_bar), 0u, ctrl};
+    AttnProgress ap;
     int cursor = 0;
     uint32_t it = 0, tcount = 0;
     bool ok = true;
@@ -613,8 +725,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       long long t0 = 0;
       if (p.prof && tid == EPI_WARP0 * 32) t0 = globaltimer_ns();
       if (op->op_kind != OPK_GEMM) {
-        if (op->op_kind < OPK_ATTN_FWD || op->op_kind > OPK_ATTN_BWD_Q)
-          ok = row_op_tile(op, tc, w8, lane, scratch, rs, ctrl, p);
+        if (is_attention(op)) ok = attention_tile(op, tc, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
+        else ok = row_op_tile(op, tc, w8, lane, scratch, rs, ctrl, p);
       } else if (tc.skip) {
         continue;
       } else if (op->xform) {
@@ -634,6 +746,19 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         p.prof[2 * (size_t)t] = (unsigned long long)t0;
         p.prof[2 * (size_t)t + 1] = ((unsigned long long)smid() << 48) | (unsigned long long)(t1 - t0);
       }
+    }
+  }
+
+  else if (MEGA) {
+    // =============================== step kernel: warp 10 ===============================
+    // only the key/value pass of the attention backward has work for an eleventh warp
+    AttnProgress ap;
+    int cursor = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      Tile tc;
+      const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      if (is_attention(op)) ok = attention_tile(op, tc, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
     }
   }
 

@@ -279,7 +279,24 @@ gpt2l_schedule *schedule_build(const std::vector<OpSpec> &specs, int grid_limit,
     if (g.splits > 1 && g.atomic_out) s->zero.push_back({g.C, (size_t)g.Mc * g.Nc * sizeof(float)});
     if (g.colsum && (g.splits > 1 || g.colsum_spread)) s->zero.push_back({g.colsum, (size_t)g.Nc * sizeof(float)});
   }
+  // attention ops: one set of tensor maps each, in a device array the kernel indexes with ra.i4
+  std::vector<FlashMaps> fmaps;
+  for (int i = 0; i < n_ops; ++i) {
+    const int k = specs[i].kind;
+    if (k < OPK_ATTN_FWD || k > OPK_ATTN_BWD_Q) continue;
+    const RowArgs &ra = specs[i].ra;
+    FlashMaps fm;
+    memset(&fm, 0, sizeof(fm));
+    e = attention_flash_build_maps(&fm, ra.in0, k == OPK_ATTN_FWD ? nullptr : ra.in1, ra.i0, ra.i2, ra.i1, ra.i3);
+    if (e) { *err = e; delete s; return nullptr; }
+    s->plan.ops[i].ra.i4 = (int)fmaps.size();
+    fmaps.push_back(fm);
+  }
   bool ok = true;
+  if (!fmaps.empty()) {
+    ok = ok && cudaMalloc(reinterpret_cast<void **>(&s->d_fmaps), sizeof(FlashMaps) * fmaps.size()) == cudaSuccess;
+    ok = ok && cudaMemcpy(s->d_fmaps, fmaps.data(), sizeof(FlashMaps) * fmaps.size(), cudaMemcpyHostToDevice) == cudaSuccess;
+  }
   if (ws_bytes) {
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&s->ws), ws_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&s->ws_sem), sem_count * sizeof(unsigned)) == cudaSuccess;

@@ -200,9 +200,16 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
   }
 
   float *P = m->params, *G = m->grads;
-  gpt2_linear_opts o;
+  gpt2_linear_opts o;   // forward and input-gradient GEMMs
   memset(&o, 0, sizeof(o));
   o.mode = m->mode;
+  // Their outputs are activation buffers, some of them reused several times inside one step, so a split
+  // reduction must not need a zeroed output: partial tiles go through the workspace and are combined by the
+  // last split to arrive. Weight gradients (`ow`) land in the gradient buffer, which the step zeroes whole,
+  // and keep the cheaper reduce-adds.
+  o.deterministic = 1;
+  gpt2_linear_opts ow = o;
+  ow.deterministic = 0;
   Builder b;
   const int rb_per_seq = T / BM;
 
@@ -278,11 +285,11 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     OpSpec t = row_spec(OPK_TRANSPOSE, M, BM, L);
     t.ra.in0 = m->lnf; t.ra.out0 = st->xt; t.ra.i0 = M; t.ra.i1 = C;
     b.emit(t, {{m->lnf, ROW, false}}, {{st->xt, WHOLE, false}});
-    OpSpec g = gemm_spec(GPT2L_OP_FORWARD, C, M, Vp, G + m->off_wte, nullptr, st->xt, m->logits, nullptr, o, L);
+    OpSpec g = gemm_spec(GPT2L_OP_FORWARD, C, M, Vp, G + m->off_wte, nullptr, st->xt, m->logits, nullptr, ow, L);
     g.transposed_a = true;
     b.emit(g, {{st->xt, WHOLE, false}, {m->logits, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
   } else {
-    b.emit(gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, Vp, G + m->off_wte, nullptr, m->lnf, m->logits, nullptr, o, L),
+    b.emit(gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, Vp, G + m->off_wte, nullptr, m->lnf, m->logits, nullptr, ow, L),
            {{m->lnf, WHOLE, false}, {m->logits, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
   }
   const float *res_last = L > 0 ? m->la[L - 1].res3 : m->encoded;
@@ -305,12 +312,12 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, 4 * C, C, m->dbig, nullptr, m->dresid, P + p.fcproj_w, nullptr, ogb, l),
            {{m->dresid, ROW, false}, {a.fc, ROW, false}}, {{m->dbig, ROW, false}});
     wgrads[l].push_back(b.emit(
-        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, 4 * C, C, G + p.fcproj_w, G + p.fcproj_b, a.fc_gelu, m->dresid, nullptr, o, l),
+        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, 4 * C, C, G + p.fcproj_w, G + p.fcproj_b, a.fc_gelu, m->dresid, nullptr, ow, l),
         {{m->dresid, WHOLE, false}, {a.fc_gelu, WHOLE, false}}, {{G + p.fcproj_w, WHOLE, false}}));
     b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, C, 4 * C, st->d_ln, nullptr, m->dbig, P + p.fc_w, nullptr, o, l),
            {{m->dbig, ROW, false}}, {{st->d_ln, ROW, false}});
     wgrads[l].push_back(b.emit(
-        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, 4 * C, G + p.fc_w, G + p.fc_b, a.ln2, m->dbig, nullptr, o, l),
+        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, 4 * C, G + p.fc_w, G + p.fc_b, a.ln2, m->dbig, nullptr, ow, l),
         {{m->dbig, WHOLE, false}, {a.ln2, WHOLE, false}}, {{G + p.fc_w, WHOLE, false}}));
     {
       OpSpec s = row_spec(OPK_LN_BWD, M, BM, l);
@@ -322,7 +329,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, C, C, st->d_atty, nullptr, m->dresid, P + p.proj_w, nullptr, o, l),
            {{m->dresid, ROW, false}}, {{st->d_atty, ROW, false}});
     wgrads[l].push_back(b.emit(
-        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, C, G + p.proj_w, G + p.proj_b, a.atty, m->dresid, nullptr, o, l),
+        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, C, G + p.proj_w, G + p.proj_b, a.atty, m->dresid, nullptr, ow, l),
         {{m->dresid, WHOLE, false}, {a.atty, WHOLE, false}}, {{G + p.proj_w, WHOLE, false}}));
     if (m->attn_flash) {  // the other attention implementations compute their row terms themselves
       OpSpec s = row_spec(OPK_ROWDOT, M, BM, l);
@@ -339,7 +346,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, C, 3 * C, st->d_ln, nullptr, st->dqkv, P + p.qkv_w, nullptr, o, l),
            {{st->dqkv, ROW, false}}, {{st->d_ln, ROW, false}});
     wgrads[l].push_back(b.emit(
-        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, 3 * C, G + p.qkv_w, G + p.qkv_b, a.ln1, st->dqkv, nullptr, o, l),
+        gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, 3 * C, G + p.qkv_w, G + p.qkv_b, a.ln1, st->dqkv, nullptr, ow, l),
         {{st->dqkv, WHOLE, false}, {a.ln1, WHOLE, false}}, {{G + p.qkv_w, WHOLE, false}}));
     {
       OpSpec s = row_spec(OPK_LN_BWD, M, BM, l);
@@ -511,6 +518,31 @@ int gpt2_megakernel_step_debug_set_expected(gpt2l_step *s, int piece, int op, in
   int k = 0;
   for (auto &it : s->items)
     if (it.sched && k++ == piece) return gpt2_schedule_debug_set_expected(it.sched, op, dep, expected, wait_limit_ms);
+  return GPT2L_ERR_BAD_ARG;
+}
+
+// Per-tile profile of the persistent pieces (see gpt2_schedule_profile): enable / disable for all pieces, and
+// read piece `piece` of the last step. Rows as in gpt2_schedule_read_profile, with the op's kind in the
+// upper half of the first value: out[4i] = op index | kind << 32.
+int gpt2_megakernel_step_profile(gpt2l_step *s, int enable) {
+  if (!s) return GPT2L_ERR_BAD_ARG;
+  for (auto &it : s->items)
+    if (it.sched) {
+      const int e = gpt2_schedule_profile(it.sched, enable);
+      if (e) return e;
+    }
+  return GPT2L_OK;
+}
+
+long long gpt2_megakernel_step_read_profile(gpt2l_step *s, int piece, long long *out, long long max_tiles) {
+  if (!s) return GPT2L_ERR_BAD_ARG;
+  int k = 0;
+  for (auto &it : s->items)
+    if (it.sched && k++ == piece) {
+      const long long n = gpt2_schedule_read_profile(it.sched, out, max_tiles);
+      for (long long i = 0; i < n; ++i) out[4 * i] |= (long long)it.sched->plan.ops[out[4 * i]].op_kind << 32;
+      return n;
+    }
   return GPT2L_ERR_BAD_ARG;
 }
 

@@ -112,6 +112,13 @@ int gpt2_megakernel_step(gpt2l_step *s, float lr, float beta1, float beta2, floa
 int gpt2_megakernel_step_status(gpt2l_step *s);
 /* out = {ops in the step, kernel launches per step, tiles per step}. */
 int gpt2_megakernel_step_info(const gpt2l_step *s, int out[3]);
+/* Per-tile profile of the persistent pieces of a step (the reference's megakernel records %globaltimer per
+ * instruction, src/mk.cu:966-971, 1117-1138, 1814-1819). enable = 1 records every following step.
+ * gpt2_megakernel_step_read_profile copies persistent piece `piece` of the last step: for tile i of that
+ * piece, out[4i..4i+3] = {op index | op kind << 32, start in ns, ns spent in the tile, SM id}; returns the
+ * number of tiles copied (at most max_tiles), or a negative error (no such piece, profile not enabled). */
+int gpt2_megakernel_step_profile(gpt2l_step *s, int enable);
+long long gpt2_megakernel_step_read_profile(gpt2l_step *s, int piece, long long *out, long long max_tiles);
 /* Test hook for the bounded waits (host-side fault injection; no device fault is provoked): overrides the
  * arrival count dependency `dep` of op `op` of persistent piece `piece` waits for, and that piece's wait
  * limit in milliseconds (0 keeps the default). */
