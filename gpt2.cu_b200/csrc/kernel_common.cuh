@@ -162,25 +162,35 @@ __device__ __forceinline__ bool wait_counter(const unsigned *ctr, unsigned expec
 // Every dependency of a tile at once (one lane calls this): the counters are probed with independent
 // relaxed loads, so a tile whose producers are done pays one round trip to L2 however many
 // dependencies it has, and one acquire fence orders the tile's reads behind them. Only a counter that
-// is still short is polled (bounded). `rb` is the consumer's 128-row block.
-__device__ __forceinline__ bool wait_deps(const GemmOp *op, int rb, Ctrl *ctrl, const LaunchParams &p) {
-  bool all = true;
+// is still short is polled (bounded). `rb` is the consumer's 128-row block. `done` remembers, per role and
+// op, which producers have been seen complete as a whole (bit w = dependency w): those are skipped from then
+// on, so the tiles of a long op stop paying for dependencies that were settled during its first wave.
+__device__ __forceinline__ bool wait_deps(const GemmOp *op, int rb, Ctrl *ctrl, const LaunchParams &p, unsigned &done) {
+  bool all = true, looked = false;
+  unsigned newly = 0u;
 #pragma unroll
   for (int w = 0; w < MAX_WAITS; ++w) {
     const int base = op->wait_ctr[w];
-    if (base < 0) continue;
+    if (base < 0 || ((done >> w) & 1u)) continue;
+    looked = true;
     const unsigned need = (unsigned)op->wait_expected[w];
+    const bool whole = ld_relaxed(p.counters + op->wait_op_ctr[w]) >= (unsigned)op->wait_op_expected[w];
+    bool ok;
     if (op->wait_kind[w] == DEP_SEQUENCE) {
       const int n = op->rb_per_seq, first = base + (rb / n) * n;
-      for (int i = 0; i < n; ++i) all &= ld_relaxed(p.counters + first + i) >= need;
+      ok = true;
+      for (int i = 0; i < n; ++i) ok &= ld_relaxed(p.counters + first + i) >= need;
     } else {
-      all &= ld_relaxed(p.counters + base + (op->wait_kind[w] == GPT2L_DEP_ROWBLOCK ? rb : 0)) >= need;
+      ok = ld_relaxed(p.counters + base + (op->wait_kind[w] == GPT2L_DEP_ROWBLOCK ? rb : 0)) >= need;
     }
+    if (whole) newly |= 1u << w;
+    all &= (ok || whole);
   }
+  if (!looked) return true;
   if (!all) {
     for (int w = 0; w < MAX_WAITS; ++w) {
       const int base = op->wait_ctr[w];
-      if (base < 0) continue;
+      if (base < 0 || (((done | newly) >> w) & 1u)) continue;
       const unsigned need = (unsigned)op->wait_expected[w];
       if (op->wait_kind[w] == DEP_SEQUENCE) {
         const int n = op->rb_per_seq, first = base + (rb / n) * n;
@@ -193,6 +203,7 @@ __device__ __forceinline__ bool wait_deps(const GemmOp *op, int rb, Ctrl *ctrl, 
     }
   }
   fence_acq_rel_gpu();
+  done |= newly;
   return true;
 }
 

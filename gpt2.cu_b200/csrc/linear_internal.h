@@ -149,6 +149,8 @@ struct alignas(64) GemmOp {
   int wait_ctr[MAX_WAITS];       // first counter index, -1 = none
   int wait_kind[MAX_WAITS];      // GPT2L_DEP_*
   int wait_expected[MAX_WAITS];  // arrivals to wait for
+  int wait_op_ctr[MAX_WAITS];       // the producer's op-level counter and the count that means "all of it is
+  int wait_op_expected[MAX_WAITS];  // done": once seen, the dependency is never looked at again
   int pub_rb_base;      // counter index of row block 0 (or -1)
   int pub_op_ctr;       // op-level counter index (or -1)
   unsigned idesc;       // tcgen05 instruction descriptor

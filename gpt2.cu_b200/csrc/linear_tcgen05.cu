@@ -313,13 +313,13 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
 // A non-GEMM tile of the step kernel, executed by one of the eight worker warps (w8 = 0..7). `scratch` is
 // the 32 KiB of epilogue boxes, free while all eight warps are inside the same tile.
 __device__ __noinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, int w8, int lane, float *scratch,
-                                            RowSync &rs, Ctrl *ctrl, const LaunchParams &p) {
+                                            RowSync &rs, Ctrl *ctrl, const LaunchParams &p, unsigned &deps_done) {
   const int tile = tc.m_tile;
   const int rpt = op->rows_per_tile;
   // dependencies are counted per 128-row block; every warp makes its own acquire before it reads
   const int rb = op->op_kind == OPK_ADAMW ? 0 : (int)(((long long)tile * rpt) >> 7);
   int okl = 1;
-  if (lane == 0) okl = wait_deps(op, rb, ctrl, p) ? 1 : 0;
+  if (lane == 0) okl = wait_deps(op, rb, ctrl, p, deps_done) ? 1 : 0;
   if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
   const int wtid = w8 * 32 + lane;
   bool ok = true;
@@ -368,6 +368,8 @@ struct AttnProgress {
   uint32_t steps[3] = {0u, 0u, 0u};
   uint32_t tiles[3] = {0u, 0u, 0u};
   uint32_t cta_phase = 0u;
+  int dep_op = -1;          // warp 0: the attention op `deps_done` belongs to
+  unsigned deps_done = 0u;  //         its dependencies already seen complete (see wait_deps)
 };
 
 // rendezvous of all STEP_THREADS / 32 warps (bounded like every other wait)
@@ -397,7 +399,11 @@ __device__ __noinline__ bool attention_tile_mode(const GemmOp *op, int grb, int 
   using namespace flash;
   if (warp == 0) {
     int okl = 1;
-    if (lane == 0) okl = wait_deps(op, grb, ctrl, p) ? 1 : 0;
+    if (ap.dep_op != op->op_index) {
+      ap.dep_op = op->op_index;
+      ap.deps_done = 0u;
+    }
+    if (lane == 0) okl = wait_deps(op, grb, ctrl, p, ap.deps_done) ? 1 : 0;
     if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
     fence_proxy_async_all();  // the operands were written with plain stores; TMA reads them next
   }
@@ -517,6 +523,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     uint32_t it = 0;
     bool ok = true;
     AttnProgress ap;
+    int dep_op = -1;
+    unsigned deps_done = 0u;
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
@@ -528,8 +536,12 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       if (tc.skip) continue;  // every role skips the same tiles, so no barrier phase is consumed
       // ---- dependency counters: do not touch the operands before their producers are done
       if (op->wait_ctr[0] >= 0) {  // dependencies fill the slots from 0 up
+        if (dep_op != op->op_index) {
+          dep_op = op->op_index;
+          deps_done = 0u;
+        }
         int okl = 1;
-        if (lane == 0) okl = wait_deps(op, tc.m_tile, ctrl, p) ? 1 : 0;
+        if (lane == 0) okl = wait_deps(op, tc.m_tile, ctrl, p, deps_done) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
         if (!ok) break;
         fence_proxy_async_all();  // producers wrote with plain stores; TMA reads next
@@ -719,14 +731,20 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     int cursor = 0;
     uint32_t it = 0, tcount = 0;
     bool ok = true;
+    int dep_op = -1;
+    unsigned deps_done = 0u;
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
+      if (dep_op != op->op_index) {
+        dep_op = op->op_index;
+        deps_done = 0u;
+      }
       long long t0 = 0;
       if (p.prof && tid == EPI_WARP0 * 32) t0 = globaltimer_ns();
       if (op->op_kind != OPK_GEMM) {
         if (is_attention(op)) ok = attention_tile(op, tc, ring_ptr, ring, ctrl, tmem_base, p, ap, warp, lane);
-        else ok = row_op_tile(op, tc, w8, lane, scratch, rs, ctrl, p);
+        else ok = row_op_tile(op, tc, w8, lane, scratch, rs, ctrl, p, deps_done);
       } else if (tc.skip) {
         continue;
       } else if (op->xform) {

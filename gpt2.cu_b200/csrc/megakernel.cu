@@ -139,10 +139,14 @@ int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
         g.wait_ctr[w] = pr.pub_rb_base;
         g.wait_kind[w] = dep.kind;
         g.wait_expected[w] = (int)per_block;
+        g.wait_op_ctr[w] = pr.pub_op_ctr;
+        g.wait_op_expected[w] = (int)whole;
       } else if (dep.kind == GPT2L_DEP_WHOLE_OP) {
         g.wait_ctr[w] = pr.pub_op_ctr;
         g.wait_kind[w] = GPT2L_DEP_WHOLE_OP;
         g.wait_expected[w] = (int)whole;
+        g.wait_op_ctr[w] = pr.pub_op_ctr;
+        g.wait_op_expected[w] = (int)whole;
       } else {
         return GPT2L_ERR_SCHEDULE;
       }
@@ -363,7 +367,62 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
   int dummy;
   if (!err) err = &dummy;
   if (!ops || n_ops <= 0) { *err = GPT2L_ERR_BAD_ARG; return nullptr; }
-  return schedule_build(specs_from(ops, n_ops), 0, err);
+  std::vector<OpSpec> in = specs_from(ops, n_ops);
+  // Wide weight gradients (lm_head: N >= 8192 and N >= 8 K) run faster from a K-major copy of the
+  // activations, as in the single-call entry point: a transpose op in front, then the product in the
+  // forward form. Ops move down the list, so the callers' producer indices are translated.
+  bool pairs = true;
+  for (const auto &s : in) pairs = pairs && s.gemm.opts.cta_pair == 2;
+  size_t xt_floats = 0;
+  for (const auto &s : in) {
+    const GemmDesc &d = s.gemm;
+    if (!pairs && d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.N >= 8192 && d.N >= 8 * d.K && d.M % 32 == 0 && d.M > 0)
+      xt_floats += (size_t)d.M * d.K;
+  }
+  float *xt = nullptr;
+  if (xt_floats && cudaMalloc(reinterpret_cast<void **>(&xt), xt_floats * sizeof(float)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    *err = GPT2L_ERR_CUDA;
+    return nullptr;
+  }
+  std::vector<OpSpec> out;
+  std::vector<int> where(in.size());
+  size_t used = 0;
+  for (size_t i = 0; i < in.size(); ++i) {
+    OpSpec s = in[i];
+    for (auto &d : s.deps) d.producer = (d.producer >= 0 && d.producer < (int)i) ? where[d.producer] : -1;
+    const GemmDesc d = s.gemm;
+    if (xt && d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.N >= 8192 && d.N >= 8 * d.K && d.M % 32 == 0) {
+      OpSpec t;
+      t.kind = OPK_TRANSPOSE;
+      t.rows = d.M;
+      t.rows_per_tile = BM;
+      t.layer = s.layer;
+      memset(&t.ra, 0, sizeof(t.ra));
+      t.ra.in0 = d.a; t.ra.out0 = xt + used; t.ra.i0 = d.M; t.ra.i1 = d.K;
+      t.deps = s.deps;  // the activations' producers
+      for (auto &dd : t.deps) dd.kind = GPT2L_DEP_WHOLE_OP;
+      out.push_back(t);
+      s.gemm.kind = GPT2L_OP_FORWARD;
+      s.gemm.M = d.K;  // output rows
+      s.gemm.K = d.M;  // reduction
+      s.gemm.a = xt + used;
+      s.gemm.bias = nullptr;
+      s.gemm.opts.flags = 0;
+      s.transposed_a = true;
+      s.deps.push_back({(int)out.size() - 1, GPT2L_DEP_WHOLE_OP});
+      used += (size_t)d.M * d.K;
+    }
+    where[i] = (int)out.size();
+    out.push_back(s);
+  }
+  gpt2l_schedule *sch = schedule_build(out, 0, err);
+  if (!sch) {
+    if (xt) cudaFree(xt);
+    return nullptr;
+  }
+  sch->xt = xt;
+  return sch;
 }
 
 void gpt2_schedule_destroy(gpt2l_schedule *s) {
@@ -374,6 +433,7 @@ void gpt2_schedule_destroy(gpt2l_schedule *s) {
   if (s->ws) cudaFree(s->ws);
   if (s->ws_sem) cudaFree(s->ws_sem);
   if (s->d_fmaps) cudaFree(s->d_fmaps);
+  if (s->xt) cudaFree(s->xt);
   if (s->d_prof) cudaFree(s->d_prof);
   delete s;
 }
@@ -403,6 +463,7 @@ int gpt2_megakernel_status(gpt2l_schedule *s) {
 int gpt2_schedule_debug_set_expected(gpt2l_schedule *s, int op, int dep, int expected, int wait_limit_ms) {
   if (!s || op < 0 || op >= (int)s->plan.ops.size() || dep < 0 || dep >= MAX_WAITS) return GPT2L_ERR_BAD_ARG;
   s->plan.ops[op].wait_expected[dep] = expected;
+  s->plan.ops[op].wait_op_expected[dep] = expected;
   if (wait_limit_ms > 0) s->wait_limit_ns = (long long)wait_limit_ms * 1000000ll;
   if (cudaMemcpy(s->d_ops + op, &s->plan.ops[op], sizeof(GemmOp), cudaMemcpyHostToDevice) != cudaSuccess)
     return GPT2L_ERR_CUDA;

@@ -52,6 +52,7 @@ struct gpt2l_schedule {
   float *ws = nullptr;
   unsigned *ws_sem = nullptr;
   g2l::FlashMaps *d_fmaps = nullptr;     // tensor maps of the attention ops (step schedules)
+  float *xt = nullptr;                   // transposed activation copies for wide weight gradients
   unsigned long long *d_prof = nullptr;  // [total_tiles][2] profile stamps, allocated on request
   int grid = 0;
   long long wait_limit_ns = 0;

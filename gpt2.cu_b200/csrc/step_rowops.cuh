@@ -32,6 +32,10 @@ struct RowSync {
   }
 };
 
+__device__ __forceinline__ void prefetch_l2(const void *ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
+
 __device__ __forceinline__ float rw_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -46,6 +50,7 @@ __device__ __forceinline__ void row_embed_fwd(const GemmOp *op, int tile, int wt
   const int r1 = min(M, r0 + op->rows_per_tile);
   const int c4n = C >> 2;
   const int total = (r1 - r0) * c4n;
+#pragma unroll 4
   for (int i = wtid; i < total; i += NUM_WORKER_WARPS * 32) {
     const int m = r0 + i / c4n, c = (i % c4n) * 4;
     const int tok = a.idx0[m], t = m % T;
@@ -72,47 +77,72 @@ __device__ __forceinline__ void row_embed_bwd(const GemmOp *op, int tile, int wt
   }
 }
 
-// ---- layernorm forward, a row per warp at a time, the row in registers --------------------------------
+// ---- layernorm forward: a warp takes its rows two at a time, both rows in registers, so that twice as many
+// loads are in flight per warp (eight warps per SM have to cover the memory latency alone) ------------------
 template <int K4>  // C <= 128 * K4, C % 4 == 0
 __device__ __forceinline__ void row_ln_fwd(const GemmOp *op, int tile, int w8, int lane) {
   const RowArgs &a = op->ra;
   const int M = a.i0, C = a.i1;
   const int r0 = tile * op->rows_per_tile;
   const int r1 = min(M, r0 + op->rows_per_tile);
-  for (int row = r0 + w8; row < r1; row += NUM_WORKER_WARPS) {
-    const float *x = a.in0 + (long long)row * C;
-    float4 v[K4];
-    float s = 0.f;
+  constexpr int R = K4 <= 6 ? 4 : 2;  // rows in flight per warp (R * K4 float4 registers)
+  for (int rowb = r0 + w8; rowb < r1; rowb += R * NUM_WORKER_WARPS) {
+    float4 v[R][K4];
+    float s[R];
 #pragma unroll
-    for (int k = 0; k < K4; ++k) {
-      const int c = 4 * (lane + 32 * k);
-      v[k] = c < C ? *reinterpret_cast<const float4 *>(x + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-      s += v[k].x + v[k].y + v[k].z + v[k].w;
-    }
-    const float mu = rw_warp_sum(s) / C;
-    float q = 0.f;
+    for (int j = 0; j < R; ++j) {
+      const int row = rowb + j * NUM_WORKER_WARPS;
+      const float *x = a.in0 + (long long)row * C;
+      s[j] = 0.f;
 #pragma unroll
-    for (int k = 0; k < K4; ++k) {
-      const int c = 4 * (lane + 32 * k);
-      if (c < C) {
-        const float dx = v[k].x - mu, dy = v[k].y - mu, dz = v[k].z - mu, dw = v[k].w - mu;
-        q += dx * dx + dy * dy + dz * dz + dw * dw;
+      for (int k = 0; k < K4; ++k) {
+        const int c = 4 * (lane + 32 * k);
+        v[j][k] = (c < C && row < r1) ? *reinterpret_cast<const float4 *>(x + c) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    const float rs = rsqrtf(rw_warp_sum(q) / C + 1e-5f);
-    float *o = a.out0 + (long long)row * C;
+#pragma unroll
+    for (int j = 0; j < R; ++j)
+#pragma unroll
+      for (int k = 0; k < K4; ++k) s[j] += v[j][k].x + v[j][k].y + v[j][k].z + v[j][k].w;
+    float mu[R], rs[R];
+#pragma unroll
+    for (int j = 0; j < R; ++j) mu[j] = rw_warp_sum(s[j]) / C;
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      float q = 0.f;
+#pragma unroll
+      for (int k = 0; k < K4; ++k) {
+        const int c = 4 * (lane + 32 * k);
+        if (c < C) {
+          const float dx = v[j][k].x - mu[j], dy = v[j][k].y - mu[j], dz = v[j][k].z - mu[j], dw = v[j][k].w - mu[j];
+          q += dx * dx + dy * dy + dz * dz + dw * dw;
+        }
+      }
+      rs[j] = rsqrtf(rw_warp_sum(q) / C + 1e-5f);
+    }
 #pragma unroll
     for (int k = 0; k < K4; ++k) {
       const int c = 4 * (lane + 32 * k);
       if (c < C) {
         const float4 wv = *reinterpret_cast<const float4 *>(a.in1 + c);
         const float4 bv = *reinterpret_cast<const float4 *>(a.in2 + c);
-        *reinterpret_cast<float4 *>(o + c) =
-            make_float4((v[k].x - mu) * rs * wv.x + bv.x, (v[k].y - mu) * rs * wv.y + bv.y,
-                        (v[k].z - mu) * rs * wv.z + bv.z, (v[k].w - mu) * rs * wv.w + bv.w);
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          const int row = rowb + j * NUM_WORKER_WARPS;
+          if (row < r1)
+            *reinterpret_cast<float4 *>(a.out0 + (long long)row * C + c) =
+                make_float4((v[j][k].x - mu[j]) * rs[j] * wv.x + bv.x, (v[j][k].y - mu[j]) * rs[j] * wv.y + bv.y,
+                            (v[j][k].z - mu[j]) * rs[j] * wv.z + bv.z, (v[j][k].w - mu[j]) * rs[j] * wv.w + bv.w);
+        }
       }
     }
-    if (lane == 0) { a.out1[row] = mu; a.out2[row] = rs; }
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        const int row = rowb + j * NUM_WORKER_WARPS;
+        if (row < r1) { a.out1[row] = mu[j]; a.out2[row] = rs[j]; }
+      }
+    }
   }
 }
 
@@ -131,43 +161,75 @@ __device__ __forceinline__ bool row_ln_bwd(const GemmOp *op, int tile, int w8, i
   float *sw = acc, *sb = acc + C;
   const int r0 = tile * op->rows_per_tile;
   const int r1 = min(M, r0 + op->rows_per_tile);
-  for (int row = r0 + w8; row < r1; row += NUM_WORKER_WARPS) {
-    const float *x = a.in1 + (long long)row * C;
-    const float *go = a.in0 + (long long)row * C;
-    const float mu = a.in3[row], rs = a.in4[row];
-    float4 nh[K4], g[K4];
-    float s1 = 0.f, s2 = 0.f;
+  constexpr int R = K4 <= 6 ? 2 : 1;  // rows in flight per warp: eight warps per SM have to cover the latency alone
+  for (int rowb = r0 + w8; rowb < r1; rowb += R * NUM_WORKER_WARPS) {
+    float4 nh[R][K4], g[R][K4];
+    float mu[R], rs[R], s1[R], s2[R];
 #pragma unroll
-    for (int k = 0; k < K4; ++k) {
-      const int c = 4 * (lane + 32 * k);
-      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 xv = c < C ? *reinterpret_cast<const float4 *>(x + c) : make_float4(mu, mu, mu, mu);
-      g[k] = c < C ? *reinterpret_cast<const float4 *>(go + c) : zero;
-      nh[k] = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
-      const float4 wv = c < C ? *reinterpret_cast<const float4 *>(a.in2 + c) : zero;
-      const float4 dn = make_float4(g[k].x * wv.x, g[k].y * wv.y, g[k].z * wv.z, g[k].w * wv.w);
-      s1 += dn.x + dn.y + dn.z + dn.w;
-      s2 += dn.x * nh[k].x + dn.y * nh[k].y + dn.z * nh[k].z + dn.w * nh[k].w;
+    for (int j = 0; j < R; ++j) {
+      const int row = rowb + j * NUM_WORKER_WARPS;
+      const bool live = row < r1;
+      const float *x = a.in1 + (long long)row * C;
+      const float *go = a.in0 + (long long)row * C;
+      mu[j] = live ? a.in3[row] : 0.f;
+      rs[j] = live ? a.in4[row] : 0.f;
+#pragma unroll
+      for (int k = 0; k < K4; ++k) {
+        const int c = 4 * (lane + 32 * k);
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        nh[j][k] = (live && c < C) ? *reinterpret_cast<const float4 *>(x + c) : zero;   // x for now
+        g[j][k] = (live && c < C) ? *reinterpret_cast<const float4 *>(go + c) : zero;
+      }
     }
-    s1 = rw_warp_sum(s1) / C;
-    s2 = rw_warp_sum(s2) / C;
-    float *gi = a.out0 + (long long)row * C;
 #pragma unroll
-    for (int k = 0; k < K4; ++k) {
-      const int c = 4 * (lane + 32 * k);
-      if (c < C) {
-        float4 o = *reinterpret_cast<float4 *>(gi + c);
-        const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
-        o.x += (g[k].x * wv.x - s1 - nh[k].x * s2) * rs;
-        o.y += (g[k].y * wv.y - s1 - nh[k].y * s2) * rs;
-        o.z += (g[k].z * wv.z - s1 - nh[k].z * s2) * rs;
-        o.w += (g[k].w * wv.w - s1 - nh[k].w * s2) * rs;
-        *reinterpret_cast<float4 *>(gi + c) = o;
-        const int q = lane + 32 * k;  // column c + j lives at plane j, slot q
-        atomicAdd(sw + q, g[k].x * nh[k].x); atomicAdd(sw + Cq + q, g[k].y * nh[k].y);
-        atomicAdd(sw + 2 * Cq + q, g[k].z * nh[k].z); atomicAdd(sw + 3 * Cq + q, g[k].w * nh[k].w);
-        atomicAdd(sb + q, g[k].x); atomicAdd(sb + Cq + q, g[k].y);
-        atomicAdd(sb + 2 * Cq + q, g[k].z); atomicAdd(sb + 3 * Cq + q, g[k].w);
+    for (int j = 0; j < R; ++j) {
+      s1[j] = 0.f;
+      s2[j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < K4; ++k) {
+        const int c = 4 * (lane + 32 * k);
+        if (c < C) {
+          const float4 xv = nh[j][k];
+          nh[j][k] = make_float4((xv.x - mu[j]) * rs[j], (xv.y - mu[j]) * rs[j], (xv.z - mu[j]) * rs[j], (xv.w - mu[j]) * rs[j]);
+          const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
+          const float4 dn = make_float4(g[j][k].x * wv.x, g[j][k].y * wv.y, g[j][k].z * wv.z, g[j][k].w * wv.w);
+          s1[j] += dn.x + dn.y + dn.z + dn.w;
+          s2[j] += dn.x * nh[j][k].x + dn.y * nh[j][k].y + dn.z * nh[j][k].z + dn.w * nh[j][k].w;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      s1[j] = rw_warp_sum(s1[j]) / C;
+      s2[j] = rw_warp_sum(s2[j]) / C;
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const int row = rowb + j * NUM_WORKER_WARPS;
+      if (row >= r1) continue;
+      float *gi = a.out0 + (long long)row * C;
+      float4 o[K4];
+#pragma unroll
+      for (int k = 0; k < K4; ++k) {
+        const int c = 4 * (lane + 32 * k);
+        o[k] = c < C ? *reinterpret_cast<float4 *>(gi + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int k = 0; k < K4; ++k) {
+        const int c = 4 * (lane + 32 * k);
+        if (c < C) {
+          const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
+          o[k].x += (g[j][k].x * wv.x - s1[j] - nh[j][k].x * s2[j]) * rs[j];
+          o[k].y += (g[j][k].y * wv.y - s1[j] - nh[j][k].y * s2[j]) * rs[j];
+          o[k].z += (g[j][k].z * wv.z - s1[j] - nh[j][k].z * s2[j]) * rs[j];
+          o[k].w += (g[j][k].w * wv.w - s1[j] - nh[j][k].w * s2[j]) * rs[j];
+          *reinterpret_cast<float4 *>(gi + c) = o[k];
+          const int q = lane + 32 * k;  // column c + i lives at plane i, slot q
+          atomicAdd(sw + q, g[j][k].x * nh[j][k].x); atomicAdd(sw + Cq + q, g[j][k].y * nh[j][k].y);
+          atomicAdd(sw + 2 * Cq + q, g[j][k].z * nh[j][k].z); atomicAdd(sw + 3 * Cq + q, g[j][k].w * nh[j][k].w);
+          atomicAdd(sb + q, g[j][k].x); atomicAdd(sb + Cq + q, g[j][k].y);
+          atomicAdd(sb + 2 * Cq + q, g[j][k].z); atomicAdd(sb + 3 * Cq + q, g[j][k].w);
+        }
       }
     }
   }
@@ -185,7 +247,9 @@ __device__ __forceinline__ bool row_ln_bwd(const GemmOp *op, int tile, int w8, i
 // ---- softmax + cross-entropy of one row by all 256 worker threads -----------------------------------
 // loss[row] = -log softmax(logits[row])[target]; the row is overwritten with (p - onehot) * scale, pad
 // columns V..Vp-1 with 0. Pass 1 streams the row once (running max / sum per thread), pass 2 reads it again
-// (from L2: one row per CTA is in flight, ~30 MB over the whole GPU) and writes the gradient.
+// (from L2: one row per CTA is in flight, ~30 MB over the whole GPU) and writes the gradient. Only 256
+// threads per SM work on this, so each keeps XU independent 16-byte loads in flight before it touches the
+// first value: with one load per trip the row took ~50 us, all of it memory latency.
 __device__ __forceinline__ bool row_xent(const GemmOp *op, int tile, int w8, int lane, float *red, RowSync &rs_,
                                          const LaunchParams &p) {
   const RowArgs &a = op->ra;
@@ -200,11 +264,24 @@ __device__ __forceinline__ bool row_xent(const GemmOp *op, int tile, int w8, int
     float *row = a.out0 + (long long)rowi * Vp;
     float m = -INFINITY, s = 0.f;
     const int V4 = V & ~3;
-    for (int c = wtid * 4; c < V4; c += NT * 4) {
-      float4 v = *reinterpret_cast<const float4 *>(row + c);
-      v.x *= L2E; v.y *= L2E; v.z *= L2E; v.w *= L2E;
-      const float mn = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
-      s = s * exp2f(m - mn) + exp2f(v.x - mn) + exp2f(v.y - mn) + exp2f(v.z - mn) + exp2f(v.w - mn);
+    constexpr int XU = 16;
+    for (int c0 = wtid * 4; c0 < V4; c0 += NT * 4 * XU) {
+      float4 v[XU];
+#pragma unroll
+      for (int u = 0; u < XU; ++u) {
+        const int c = c0 + u * NT * 4;
+        v[u] = c < V4 ? *reinterpret_cast<const float4 *>(row + c) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+      float mn = m;
+#pragma unroll
+      for (int u = 0; u < XU; ++u) {
+        v[u].x *= L2E; v[u].y *= L2E; v[u].z *= L2E; v[u].w *= L2E;
+        mn = fmaxf(fmaxf(mn, fmaxf(v[u].x, v[u].y)), fmaxf(v[u].z, v[u].w));
+      }
+      float add = 0.f;
+#pragma unroll
+      for (int u = 0; u < XU; ++u) add += exp2f(v[u].x - mn) + exp2f(v[u].y - mn) + exp2f(v[u].z - mn) + exp2f(v[u].w - mn);
+      s = (m == -INFINITY ? 0.f : s * exp2f(m - mn)) + add;  // c0 < V4: the first chunk is real, so mn is finite
       m = mn;
     }
     for (int c = V4 + wtid; c < V; c += NT) {
@@ -236,13 +313,25 @@ __device__ __forceinline__ bool row_xent(const GemmOp *op, int tile, int w8, int
     // read of every thread before the first overwrite of the row
     if (!rs_.sync(p, op->op_index, lane)) return false;
     const float k = scale / s;
-    for (int c = wtid * 4; c < Vp; c += NT * 4) {
-      float4 g = *reinterpret_cast<const float4 *>(row + c);
-      g.x = c + 0 < V ? exp2f(g.x * L2E - m) * k - (c + 0 == tgt ? scale : 0.f) : 0.f;
-      g.y = c + 1 < V ? exp2f(g.y * L2E - m) * k - (c + 1 == tgt ? scale : 0.f) : 0.f;
-      g.z = c + 2 < V ? exp2f(g.z * L2E - m) * k - (c + 2 == tgt ? scale : 0.f) : 0.f;
-      g.w = c + 3 < V ? exp2f(g.w * L2E - m) * k - (c + 3 == tgt ? scale : 0.f) : 0.f;
-      *reinterpret_cast<float4 *>(row + c) = g;
+    for (int c0 = wtid * 4; c0 < Vp; c0 += NT * 4 * XU) {
+      float4 gv[XU];
+#pragma unroll
+      for (int u = 0; u < XU; ++u) {
+        const int c = c0 + u * NT * 4;
+        gv[u] = c < Vp ? *reinterpret_cast<const float4 *>(row + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < XU; ++u) {
+        const int c = c0 + u * NT * 4;
+        if (c < Vp) {
+          float4 g = gv[u];
+          g.x = c + 0 < V ? exp2f(g.x * L2E - m) * k - (c + 0 == tgt ? scale : 0.f) : 0.f;
+          g.y = c + 1 < V ? exp2f(g.y * L2E - m) * k - (c + 1 == tgt ? scale : 0.f) : 0.f;
+          g.z = c + 2 < V ? exp2f(g.z * L2E - m) * k - (c + 2 == tgt ? scale : 0.f) : 0.f;
+          g.w = c + 3 < V ? exp2f(g.w * L2E - m) * k - (c + 3 == tgt ? scale : 0.f) : 0.f;
+          *reinterpret_cast<float4 *>(row + c) = g;
+        }
+      }
     }
   }
   // `red` lives in a GEMM epilogue box as well
@@ -286,6 +375,7 @@ __device__ __forceinline__ void row_adamw(const GemmOp *op, int tile, int wtid, 
   const float *G = a.in0;
   // the flat buffers are 16-byte aligned and every op range starts at a multiple of four floats
   const long long n4 = (hi - lo) >> 2;
+#pragma unroll 4
   for (long long i = wtid; i < n4; i += NUM_WORKER_WARPS * 32) {
     const long long o = lo + 4 * i;
     float4 pp = *reinterpret_cast<float4 *>(P + o), mm = *reinterpret_cast<float4 *>(Mo + o),
@@ -323,11 +413,16 @@ __device__ __forceinline__ void row_transpose(const GemmOp *op, int tile, int w8
     const int rb = blk / ncb, cb = blk % ncb;
     const int m0 = r0 + rb * 32, c0 = cb * 32;
     __syncwarp();
-    for (int r = 0; r < 32; ++r) {
+    float v[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {  // 32 independent loads in flight, then the box
       const int m = m0 + r, c = c0 + lane;
-      box[r * 32 + (lane ^ r)] = (m < M && c < C) ? a.in0[(long long)m * C + c] : 0.f;
+      v[r] = (m < M && c < C) ? a.in0[(long long)m * C + c] : 0.f;
     }
+#pragma unroll
+    for (int r = 0; r < 32; ++r) box[r * 32 + (lane ^ r)] = v[r];
     __syncwarp();
+#pragma unroll
     for (int r = 0; r < 32; ++r) {
       const int c = c0 + r, m = m0 + lane;
       if (c < C && m < M) a.out0[(long long)c * M + m] = box[lane * 32 + (r ^ lane)];
