@@ -42,7 +42,7 @@ MAX_DEPS = 2
 EXPORTS = [
     "gpt2_linear_init", "gpt2_linear_shutdown", "gpt2_linear_version", "gpt2_linear_launch_count",
     "gpt2_linear_last_status",
-    "gpt2_linear_forward", "gpt2_linear_backward_input", "gpt2_linear_backward_weight",
+    "gpt2_linear_forward", "gpt2_linear_backward_input", "gpt2_linear_backward_weight", "gpt2_linear_forward_xent",
     "gpt2_linear_forward_host", "gpt2_linear_backward_input_host", "gpt2_linear_backward_weight_host",
     "gpt2_linear_backward_weight_noalloc", "gpt2_linear_noalloc_last_status", "gpt2_linear_noalloc_debug_set_status",
     "gpt2_linear_forward_host_async", "gpt2_linear_backward_input_host_async",
@@ -83,6 +83,10 @@ class Opts(ctypes.Structure):
         ("cta_pair", ctypes.c_int),
         ("aux", ctypes.c_void_p),
         ("aux_op", ctypes.c_int),
+        ("xent_lse", ctypes.c_void_p),
+        ("xent_targets", ctypes.c_void_p),
+        ("xent_vocab", ctypes.c_int),
+        ("xent_scale", ctypes.c_float),
     ]
 
 
@@ -150,6 +154,8 @@ def _load():
         f = getattr(lib, name)
         f.argtypes = [P, P, P, P, I, I, I, I, OP, V]
         f.restype = I
+    lib.gpt2_linear_forward_xent.argtypes = [P, P, P, P, P, P, I, I, I, I, I, OP, V]
+    lib.gpt2_linear_forward_xent.restype = I
     lib.gpt2_linear_noalloc_last_status.argtypes = [ctypes.POINTER(I * 6)]
     lib.gpt2_linear_noalloc_last_status.restype = I
     lib.gpt2_linear_noalloc_debug_set_status.argtypes = [ctypes.POINTER(I * 6)]
@@ -267,8 +273,9 @@ def init(device=0):
 
 
 def make_opts(mode=MODE_TF32, flags=0, split_k=0, deterministic=0, out2=None, force_simt=0, cta_pair=0, aux=None,
-              aux_op=0):
-    return Opts(mode, flags, split_k, deterministic, out2, force_simt, cta_pair, aux, aux_op)
+              aux_op=0, xent_lse=None, xent_targets=None, xent_vocab=0, xent_scale=0.0):
+    return Opts(mode, flags, split_k, deterministic, out2, force_simt, cta_pair, _p(aux), aux_op, _p(xent_lse),
+                _p(xent_targets), xent_vocab, xent_scale)
 
 
 def _p(t):
@@ -285,6 +292,12 @@ def _p(t):
 def forward(out, x, w, b, B, S, K, N, opts=None, stream=None, host=False):
     fn = lib.gpt2_linear_forward_host if host else lib.gpt2_linear_forward
     return fn(_p(out), _p(x), _p(w), _p(b), B, S, K, N, ctypes.byref(opts) if opts else None, stream)
+
+
+def forward_xent(logits, losses, lse, x, w, targets, B, S, K, N, V, opts=None, stream=None):
+    """gpt2_linear_forward_xent: lm_head forward with softmax statistics and the cross-entropy loss"""
+    return lib.gpt2_linear_forward_xent(_p(logits), _p(losses), _p(lse), _p(x), _p(w), _p(targets), B, S, K, N, V,
+                                        ctypes.byref(opts) if opts else None, stream)
 
 
 def backward_input(g_in, g_out, w, B, S, K, N, opts=None, stream=None, host=False):

@@ -124,9 +124,10 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   if (d.opts.mode != GPT2L_MODE_TF32 && d.opts.mode != GPT2L_MODE_TF32X3) return GPT2L_ERR_BAD_ARG;
   if ((long long)d.M * d.N >= (1ll << 40) || (long long)d.M * d.K >= (1ll << 40)) return GPT2L_ERR_TOO_LARGE;
   if (d.opts.force_simt || !tma_eligible(d)) {
-    if ((d.opts.flags & GPT2L_EPI_GELU_DUAL) || d.opts.aux_op) return GPT2L_ERR_BAD_ARG;
+    if ((d.opts.flags & GPT2L_EPI_GELU_DUAL) || d.opts.aux_op || d.opts.xent_lse || d.xent_stats) return GPT2L_ERR_BAD_ARG;
     return launch_simt(d, st);
   }
+  if (d.opts.xent_lse && (d.kind == GPT2L_OP_FORWARD || d.opts.deterministic)) return GPT2L_ERR_BAD_ARG;
   // bias gradient: fused into the kernel (column sums of the staged g_out blocks) unless a
   // fixed summation order is requested, which the stand-alone column-sum kernel provides.
   float *fused_bias = d.out_bias;
@@ -267,6 +268,7 @@ void gpt2_linear_shutdown(void) {
     cudaFree(c.ws_sem);
     if (c.ws) cudaFree(c.ws);
     if (c.xt) cudaFree(c.xt);
+    if (c.xstats) cudaFree(c.xstats);
     for (int i = 0; i < 4; ++i)
       if (c.stage[i]) cudaFree(c.stage[i]);
     destroy_pipe(c.pipe);
@@ -298,7 +300,42 @@ int gpt2_linear_forward(float *out, const float *in, const float *w, const float
   d.M = B * S; d.K = K; d.N = N;
   d.out = out; d.out_bias = nullptr; d.a = in; d.b = w; d.bias = b;
   d.opts = opts_or_default(opts);
+  if (d.opts.xent_lse) return GPT2L_ERR_BAD_ARG;  // the fused cross-entropy has its own forward entry point
   return run_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+int gpt2_linear_forward_xent(float *logits, float *losses, float *lse, const float *in, const float *w,
+                             const int *targets, int B, int S, int K, int N, int V, const gpt2_linear_opts *opts,
+                             gpt2l_stream_t stream) {
+  if (B <= 0 || S <= 0 || !losses || !lse || !targets || V <= 0 || V > N) return GPT2L_ERR_BAD_ARG;
+  if ((long long)B * S > 0x7fffffffll) return GPT2L_ERR_TOO_LARGE;
+  int err;
+  DeviceCtx *ctx = ctx_current(&err);
+  if (!ctx) return err;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  GemmDesc d;
+  d.kind = GPT2L_OP_FORWARD;
+  d.M = B * S; d.K = K; d.N = N;
+  d.out = logits; d.out_bias = nullptr; d.a = in; d.b = w; d.bias = nullptr;
+  d.opts = opts_or_default(opts);
+  if (d.opts.flags || d.opts.aux_op || d.opts.xent_lse || d.opts.force_simt || !logits || !in || !w || K <= 0 || N <= 0 ||
+      !tma_eligible(d))
+    return GPT2L_ERR_BAD_ARG;
+  // the statistics buffer's size follows the tiling, which follows the shape: plan first
+  GemmOp probe;
+  d.xent_stats = reinterpret_cast<float *>(16);  // any non-null value: plan_op only looks at shapes
+  d.xent_vocab = V;
+  err = plan_op(d, ctx->num_sms, &probe);
+  if (err) return err;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    err = ensure_bytes(&ctx->xstats, &ctx->xstats_bytes, xent_stats_floats(probe) * sizeof(float));
+  }
+  if (err) return err;
+  d.xent_stats = ctx->xstats;
+  err = run_gemm(d, st);
+  if (err) return err;
+  return launch_xent_combine(lse, losses, ctx->xstats, probe.xent_stride, logits, N, targets, d.M, st);
 }
 
 int gpt2_linear_backward_input(float *g_in, const float *g_out, const float *w, int B, int S, int K, int N,

@@ -224,6 +224,20 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   return 0.5f * (1.f + th) + x * 0.5f * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * x * x);
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr float LOG2E_F = 1.4426950408889634f;
+
+// dlogit of one element: logits -> (softmax - onehot) * scale, columns at or past the true vocabulary -> 0
+__device__ __forceinline__ float xent_grad(float logit, float lse2, int col, int tgt, int vocab, float scale) {
+  const float p = ex2_approx(fmaf(logit, LOG2E_F, -lse2));
+  return col < vocab ? (p - (col == tgt ? 1.f : 0.f)) * scale : 0.f;
+}
+
 __device__ __forceinline__ float tf32_round(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));

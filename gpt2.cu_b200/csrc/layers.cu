@@ -356,6 +356,37 @@ softmax_xent_large_kernel(float *logits, float *losses, const int *targets, int 
 }
 
 // ------------------------------------------------------------------------------------
+// second half of the fused lm_head + softmax + cross-entropy: the GEMM epilogue left, per row and per
+// column tile, (max, sum of 2^(x - max)) in the base-2 domain; a warp per row folds the `stride` pairs into
+// lse[m] = max + log2(sum) and losses[m] = (lse[m] - logit[m][target] * log2 e) * ln 2.
+// ------------------------------------------------------------------------------------
+__global__ void xent_combine_kernel(float *lse, float *losses, const float2 *stats, int stride, const float *logits,
+                                    long long ld, const int *targets, int M) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float2 *s = stats + (size_t)row * stride;
+  float m = -INFINITY, sum = 0.f;
+  for (int i = lane; i < stride; i += 32) {
+    const float2 v = s[i];
+    const float mn = fmaxf(m, v.x);
+    if (mn > -INFINITY) sum = (m == -INFINITY ? 0.f : sum * exp2f(m - mn)) + (v.x == -INFINITY ? 0.f : v.y * exp2f(v.x - mn));
+    m = mn;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mn = fmaxf(m, m2);
+    sum = (m == -INFINITY ? 0.f : sum * exp2f(m - mn)) + (m2 == -INFINITY ? 0.f : s2 * exp2f(m2 - mn));
+    m = mn;
+  }
+  if (lane == 0) {
+    const float l2 = m + log2f(sum);
+    lse[row] = l2;
+    losses[row] = (l2 - logits[(long long)row * ld + targets[row]] * 1.4426950408889634f) * 0.6931471805599453f;
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // causal self-attention, flash style, head size 64. qkv[m][3C] = q | k | v, head h at columns h*64.
 // forward: out[m][h*64 + d], lse[b][h][t] = log sum_j exp(q_t.k_j / 8)
 // One thread per query row, 128 rows per block; keys / values stream through shared memory in
@@ -733,6 +764,12 @@ int softmax_xent(float *logits, float *losses, const int *targets, int M, int V,
   } else {
     softmax_xent_large_kernel<<<M, 512, 0, s>>>(logits, losses, targets, V, Vp, 1.f / (float)M);
   }
+  return LAUNCH_OK();
+}
+int launch_xent_combine(float *lse, float *losses, const float *stats, int stride, const float *logits, long long ld,
+                        const int *targets, int M, cudaStream_t s) {
+  xent_combine_kernel<<<cdiv(M, 8), 256, 0, s>>>(lse, losses, reinterpret_cast<const float2 *>(stats), stride, logits, ld,
+                                                  targets, M);
   return LAUNCH_OK();
 }
 int attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t s) {

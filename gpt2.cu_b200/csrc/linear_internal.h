@@ -60,7 +60,8 @@ enum OpKind : int {
   OPK_ATTN_FWD = 8,     // fused causal attention, forward (tile = 128 query rows of one head)
   OPK_ATTN_BWD_KV = 9,  //   dK, dV
   OPK_ATTN_BWD_Q = 10,  //   dQ
-  OPK_TRANSPOSE = 11    // out[c][m] = in[m][c] (K-major copy of activations for wide weight gradients)
+  OPK_TRANSPOSE = 11,   // out[c][m] = in[m][c] (K-major copy of activations for wide weight gradients)
+  OPK_XENT_COMBINE = 12 // lse[m], loss[m] from the per-tile softmax statistics the lm_head epilogue left
 };
 
 // Operands of a non-GEMM op (meaning per kind: see the builder in step_schedule.cu)
@@ -156,6 +157,19 @@ struct alignas(64) GemmOp {
   unsigned idesc;       // tcgen05 instruction descriptor
   int op_index;
   int layer;
+  // ---- softmax / cross-entropy fused around the lm_head ----
+  // 1: forward, the epilogue also leaves per-row (max, sum of 2^(x - max)) of the tile's columns (base-2
+  //    domain, columns >= xent_vocab excluded) in xent_stats[row * xent_stride + 2 * n_tile + (0 | 1)];
+  // 2: the A operand is the logits and is turned into dlogits = (2^(x log2e - lse[row]) - [col == target]) *
+  //    scale while it sits in shared memory (backward_input: rows = tokens, reduction index = vocabulary);
+  // 3: the same for the B operand (backward_weight: reduction index = tokens, columns = vocabulary)
+  int xent_mode;
+  int xent_stride;
+  int xent_vocab;
+  float xent_scale;
+  float *xent_stats;
+  const float *xent_lse;
+  const int *xent_tgt;
   // ---- non-GEMM ops of the step kernel ----
   int op_kind;          // OpKind; 0 = GEMM
   int rows_per_tile;    // rows one tile covers (divides 128, or a multiple of it); GEMM: 128
@@ -226,6 +240,8 @@ int encode_map_batched_mn(CUtensorMap *map, const float *base, uint64_t mn, uint
 struct GemmDesc {
   int kind;  // gpt2l_op_kind
   int M, K, N;
+  float *xent_stats = nullptr;  // forward: leave per-tile softmax statistics here (see GemmOp::xent_mode)
+  int xent_vocab = 0;
   float *out;
   float *out_bias;
   const float *a;
@@ -250,6 +266,8 @@ struct DeviceCtx {
   size_t ws_sem_count = 0;
   float *xt = nullptr;              // transposed activations for wide weight gradients
   size_t xt_bytes = 0;
+  float *xstats = nullptr;          // per-tile softmax statistics of gpt2_linear_forward_xent
+  size_t xstats_bytes = 0;
   // host-call staging
   float *stage[4] = {nullptr, nullptr, nullptr, nullptr};
   size_t stage_bytes[4] = {0, 0, 0, 0};
@@ -303,6 +321,11 @@ int attention_flash_build_maps(FlashMaps *maps, const float *qkv, const float *d
 int launch_simt(const GemmDesc &d, cudaStream_t stream);
 int launch_colsum(float *out, const float *x, int rows, int cols, cudaStream_t stream);
 int launch_transpose(float *dst, const float *src, int rows, int cols, cudaStream_t stream);
+// floats of statistics a forward GEMM with xent_stats leaves: rows * stride(op) * 2
+size_t xent_stats_floats(const GemmOp &op);
+// lse[m], losses[m] from the statistics and the stored logits (layers.cu)
+int launch_xent_combine(float *lse, float *losses, const float *stats, int stride, const float *logits, long long ld,
+                        const int *targets, int M, cudaStream_t stream);
 
 // --- driver entry point for tensor-map encoding ---
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,

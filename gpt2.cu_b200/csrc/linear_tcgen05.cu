@@ -65,6 +65,18 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
   using R = RingCfg<X3>;
   bool ok = true;
   const int bn = op->bn;
+  // softmax / cross-entropy backward folded into the operand: the logits become dlogits in shared memory
+  const int xmode = op->xent_mode;
+  const bool rewrites = X3 || xmode >= 2;
+  float x_lse = 0.f;
+  int x_tgt = -1;
+  if (xmode == 2) {  // A operand, K-major: this thread owns row x of the tile for the whole tile
+    const int grow = tc.m_tile * BM + x;
+    if (grow < op->Mc) {
+      x_lse = op->xent_lse[grow];
+      x_tgt = op->xent_tgt[grow];
+    }
+  }
   // bias gradient = column sums of the B blocks. Spread over the tile rows (row m takes the
   // k-blocks with kb % tiles_m == m) so that no CTA carries the whole extra pass: with tile row 0
   // doing all of it those CTAs ran ~30 % longer than the rest and the launch waited for them.
@@ -94,14 +106,52 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
     // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
     const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
-    const bool walk_b = op->b_mn && (X3 || cs_kb);
+    const bool walk_b = op->b_mn && (X3 || cs_kb || xmode == 3);
+    if (xmode == 2) {
+      // row x of the A block: eight 16-byte chunks, chunk j at physical position j ^ (x & 7)
+      uint8_t *arow = stage + x * 128;
+      const int k0 = kb * BK;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 *ptr = reinterpret_cast<float4 *>(arow + ((j ^ (x & 7)) << 4));
+        float4 v = *ptr;
+        const int col = k0 + 4 * j;
+        v.x = xent_grad(v.x, x_lse, col, x_tgt, op->xent_vocab, op->xent_scale);
+        v.y = xent_grad(v.y, x_lse, col + 1, x_tgt, op->xent_vocab, op->xent_scale);
+        v.z = xent_grad(v.z, x_lse, col + 2, x_tgt, op->xent_vocab, op->xent_scale);
+        v.w = xent_grad(v.w, x_lse, col + 3, x_tgt, op->xent_vocab, op->xent_scale);
+        if (X3) {
+          float4 h, l;
+          h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
+          l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+          *ptr = h;
+          *reinterpret_cast<float4 *>(reinterpret_cast<uint8_t *>(ptr) + R::LO_OFFSET) = l;
+        } else {
+          *ptr = v;
+        }
+      }
+    }
     if (walk_b) {
       uint8_t *bchunk = stage + A_TILE_BYTES + chunk * 4096;
 #pragma unroll 4
       for (int r = part * rows_per_part; r < (part + 1) * rows_per_part; ++r) {
         const int phys32 = (q16 >> 1) ^ (r & 3);
         float4 *ptr = reinterpret_cast<float4 *>(bchunk + r * 128 + phys32 * 32 + (q16 & 1) * 16);
-        const float4 v = *ptr;
+        float4 v = *ptr;
+        if (xmode == 3) {
+          // k-row r of this block is token kb * 32 + r; the columns are vocabulary entries
+          const int tokn = kb * BK + r;
+          const bool live = tokn < op->Kc;
+          const float lse2 = live ? op->xent_lse[tokn] : 0.f;
+          const int tg = live ? op->xent_tgt[tokn] : -1;
+          const int col = tc.n_tile * bn + grp * 4;
+          const float sc = live ? op->xent_scale : 0.f;
+          v.x = xent_grad(v.x, lse2, col, tg, op->xent_vocab, sc);
+          v.y = xent_grad(v.y, lse2, col + 1, tg, op->xent_vocab, sc);
+          v.z = xent_grad(v.z, lse2, col + 2, tg, op->xent_vocab, sc);
+          v.w = xent_grad(v.w, lse2, col + 3, tg, op->xent_vocab, sc);
+          if (!X3) *ptr = v;
+        }
         if (cs_kb) { csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w; }
         if (X3) {
           float4 h, l;
@@ -115,8 +165,10 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     if (X3) {
       float4 *hi = reinterpret_cast<float4 *>(stage);
       float4 *lo = reinterpret_cast<float4 *>(stage + R::LO_OFFSET);
-      const int lin_f4 = walk_b ? (A_TILE_BYTES >> 4) : stage_f4;  // A only, or A and a K-major B
-      for (int i = x; i < lin_f4; i += NUM_XFORM_WARPS * 32) {
+      // what is left to split linearly: A (unless its rows were rewritten above) and a K-major B
+      const int lin_lo = xmode == 2 ? (A_TILE_BYTES >> 4) : 0;
+      const int lin_f4 = walk_b ? (A_TILE_BYTES >> 4) : stage_f4;
+      for (int i = lin_lo + x; i < lin_f4; i += NUM_XFORM_WARPS * 32) {
         const float4 v = hi[i];
         float4 h, l;
         h.x = tf32_round(v.x); h.y = tf32_round(v.y); h.z = tf32_round(v.z); h.w = tf32_round(v.w);
@@ -124,11 +176,11 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
         hi[i] = h;
         lo[i] = l;
       }
-      fence_proxy_async_smem();
     }
+    if (rewrites) fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      if (X3) mbar_arrive(smem_u32(&ctrl->ready[s]));
+      if (rewrites) mbar_arrive(smem_u32(&ctrl->ready[s]));
       mbar_arrive(smem_u32(&ctrl->empty[s]));
     }
   }
@@ -198,6 +250,9 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
     }
     const EpiAux none;
     const float drow = (ea.row && row0 + lane < Mc) ? __ldg(ea.row + row0 + lane) : 0.f;
+    // softmax statistics of this thread's row over the columns this warp drains (base-2 domain)
+    const bool stats = op->xent_mode == 1;
+    float st_m = -INFINITY, st_s = 0.f;
     for (int c = c_first; c < bn / 32; c += n_epi) {
       const int nb = n0 + c * 32;
       if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
@@ -217,6 +272,19 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
         v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
         v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
       }
+      if (stats) {
+        float cm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) cm = fmaxf(cm, nb + j < op->xent_vocab ? v[j] : -INFINITY);
+        if (cm > -INFINITY) {
+          const float mn = fmaxf(st_m, cm * LOG2E_F);
+          float add = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) add += nb + j < op->xent_vocab ? ex2_approx(fmaf(v[j], LOG2E_F, -mn)) : 0.f;
+          st_s = (st_m == -INFINITY ? 0.f : st_s * ex2_approx(st_m - mn)) + add;
+          st_m = mn;
+        }
+      }
       for (int pass = 0; pass < (dual ? 2 : 1); ++pass) {
         if (pass == 1) {
 #pragma unroll
@@ -227,6 +295,11 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
         // split-K reduce-adds the split that also adds the bias carries it
         store_chunk(v, sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, pass == 0 ? ea : none, ar);
       }
+    }
+    if (stats && row < Mc) {
+      float2 *dst = reinterpret_cast<float2 *>(op->xent_stats) + (size_t)row * op->xent_stride + 2 * tc.n_tile;
+      dst[helper ? 1 : 0] = make_float2(st_m, st_s);
+      if (n_epi == 1) dst[1] = make_float2(-INFINITY, 0.f);  // no helper twin in this launch / op
     }
   } else if (!helper)  // fixed-order split-K: the quarter's own warp parks whole rows
   for (int c = 0; c < bn / 32; ++c) {
@@ -340,6 +413,7 @@ __device__ __noinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, int w
     case OPK_ROWDOT: row_rowdot(op, tile, wtid); break;
     case OPK_ADAMW: row_adamw(op, tile, wtid, p); break;
     case OPK_TRANSPOSE: row_transpose(op, tile, w8, lane, scratch + w8 * 1024); break;
+    case OPK_XENT_COMBINE: row_xent_combine(op, tile, w8, lane); break;
     default: break;
   }
   if (!ok) return false;
@@ -598,6 +672,9 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
     // tensor pipe holds less than a k-block of queued work, so nothing slow may sit there.
     int cursor = 0;
     uint32_t it = 0, tcount = 0;
+    // one parity bit per stage for the `ready` barriers: only k-blocks whose stage is rewritten (3xTF32
+    // split, logits -> dlogits) go through them, so their phases do not follow the ring position
+    uint32_t rdy_par = 0u;
     bool ok = true;
     AttnProgress ap;
     int t = blockIdx.x;
@@ -637,15 +714,18 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const uint32_t stepB = op->b_mn ? 1024u : 32u;
       // MEGA: an op that needs no operand transform leaves the transform warps' share of empty[s] to us
       const bool stand_in = MEGA && !op->xform;
+      const bool via_ready = X3 || op->xent_mode >= 2;  // the transform warps hand the stage over
 
       for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const int s = it % NST;
         const uint32_t ph = (it / NST) & 1u;
         okl = 1;
         if (lane == 0) {
-          const uint32_t bar = X3 ? smem_u32(&ctrl->ready[s]) : smem_u32(&ctrl->full[s]);
-          okl = wait_bar(bar, ph, ctrl, p, X3 ? SITE_SMEM_READY : SITE_SMEM_FULL, op->op_index, s);
+          const uint32_t bar = via_ready ? smem_u32(&ctrl->ready[s]) : smem_u32(&ctrl->full[s]);
+          okl = wait_bar(bar, via_ready ? ((rdy_par >> s) & 1u) : ph, ctrl, p, via_ready ? SITE_SMEM_READY : SITE_SMEM_FULL,
+                         op->op_index, s);
         }
+        if (via_ready) rdy_par ^= 1u << s;
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
         if (!ok) break;
         tc_fence_after();
@@ -934,9 +1014,27 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   if (d.opts.aux_op && !d.opts.aux) return GPT2L_ERR_BAD_ARG;
   if (d.opts.aux_op < 0 || d.opts.aux_op > GPT2L_AUX_GELU_GRAD) return GPT2L_ERR_BAD_ARG;
   if (op->aux_op && d.kind == GPT2L_OP_BACKWARD_WEIGHT) return GPT2L_ERR_BAD_ARG;
+  // softmax / cross-entropy around the lm_head: statistics in the forward epilogue, logits -> dlogits in
+  // the operand transform of the two backward GEMMs (whichever form they are given in)
+  if (d.xent_stats) {
+    if (d.kind != GPT2L_OP_FORWARD || d.xent_vocab <= 0 || d.xent_vocab > d.N) return GPT2L_ERR_BAD_ARG;
+    op->xent_mode = 1;
+    op->xent_stats = d.xent_stats;
+    op->xent_vocab = d.xent_vocab;
+  } else if (d.opts.xent_lse) {
+    if (!d.opts.xent_targets || d.opts.xent_vocab <= 0 || d.opts.aux_op) return GPT2L_ERR_BAD_ARG;
+    // the logits are the reduction-side operand: A for backward_input, B for backward_weight and for its
+    // forward form over a transposed activation copy
+    op->xent_mode = d.kind == GPT2L_OP_BACKWARD_INPUT ? 2 : 3;
+    op->xent_lse = d.opts.xent_lse;
+    op->xent_tgt = d.opts.xent_targets;
+    op->xent_vocab = d.opts.xent_vocab;
+    op->xent_scale = d.opts.xent_scale;
+  }
   op->kb_total = ceil_div(op->Kc, BK);
   int bn, splits;
   int forced = d.opts.split_k;
+  if (op->xent_mode == 1) forced = 1;  // statistics of partial sums would be meaningless
   if (op->aux_op == GPT2L_AUX_GELU_GRAD || (op->aux_op && d.opts.deterministic) || (op->aux_op && op->C2)) forced = 1;
   if (forced > op->kb_total) forced = op->kb_total;
   // CTA pairs (256-row tiles, B split between the two CTAs) cut operand traffic per flop by a
@@ -961,6 +1059,8 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
     op->band_m = ceil_div(op->tiles_dec, bands);  // balanced bands
   }
   op->atomic_out = (op->splits > 1 && !d.opts.deterministic && !op->C2) ? 1 : 0;
+  op->xent_stride = 2 * op->tiles_n;
+  if (op->xent_mode && op->pair) return GPT2L_ERR_BAD_ARG;  // the pair kernel has neither path
   op->idesc = make_idesc_tf32(op->pair ? 2 * BM : BM, bn, op->a_mn, op->b_mn);
   for (int w = 0; w < MAX_WAITS; ++w) { op->wait_ctr[w] = -1; op->wait_kind[w] = 0; op->wait_expected[w] = 0; }
   op->pub_rb_base = -1;
@@ -1081,6 +1181,8 @@ int build_batched_op(const BatchedDesc &d, int num_sms, GemmOp *op) {
   return e;
 }
 
+size_t xent_stats_floats(const GemmOp &op) { return (size_t)op.Mc * op.xent_stride * 2; }
+
 size_t op_workspace_bytes(const GemmOp &op) {
   if (op.splits <= 1 || op.atomic_out) return 0;
   return (size_t)op.tiles_m * op.tiles_n * op.splits * BM * op.bn * sizeof(float);
@@ -1118,7 +1220,7 @@ int launch_single(DeviceCtx *ctx, GemmOp &op, cudaStream_t stream) {
   p.prof = nullptr;
   for (float &f : p.adam) f = 0.f;
   p.wait_limit_ns = default_wait_limit_ns();
-  p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr) ? 1 : 0;
+  p.xform_active = (op.mode == GPT2L_MODE_TF32X3 || op.colsum != nullptr || op.xent_mode >= 2) ? 1 : 0;
   if (op.pair) {
     const int pairs = op.n_tiles < ctx->max_pairs ? op.n_tiles : ctx->max_pairs;
     if (pairs <= 0) return GPT2L_ERR_CUDA;

@@ -106,7 +106,7 @@ int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
   }
   // transform warps: per op in the step kernel, per launch in the pair kernel
   for (auto &g : plan->ops)
-    g.xform = (g.op_kind == OPK_GEMM && (plan->any_3x || (g.colsum != nullptr && g.b_mn))) ? 1 : 0;
+    g.xform = (g.op_kind == OPK_GEMM && (plan->any_3x || (g.colsum != nullptr && g.b_mn) || g.xent_mode >= 2)) ? 1 : 0;
   plan->arrivals = plan->pair ? NUM_EPI_WARPS : NUM_WORKER_WARPS;
   const unsigned A = (unsigned)plan->arrivals;
   for (int i = 0; i < n_ops; ++i) {
@@ -275,7 +275,7 @@ gpt2l_schedule *schedule_build(const std::vector<OpSpec> &specs, int grid_limit,
       // the forward form of a weight gradient: the B operand is still g_out, its column sums are g_b
       g.colsum = specs[i].gemm.out_bias;
       g.colsum_spread = g.colsum ? 1 : 0;
-      g.xform = (s->plan.any_3x || g.colsum) ? 1 : 0;
+      g.xform = (s->plan.any_3x || g.colsum || g.xent_mode >= 2) ? 1 : 0;
     }
     ws_bytes += op_workspace_bytes(g);
     if (g.splits > 1 && !g.atomic_out) sem_count += (size_t)g.tiles_m * g.tiles_n * 4;

@@ -98,7 +98,7 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
     o[12] = act(M * C);                                       // res3
   }
   const long long o_lnf = act(M * C), o_lnf_mean = act(M), o_lnf_rstd = act(M);
-  const long long o_logits = act(M * Vp), o_losses = act(M);
+  const long long o_logits = act(M * Vp), o_losses = act(M), o_xlse = act(M);
   const long long o_tmp = act(M * C), o_dres = act(M * C), o_dbig = act(M * 4 * C);
   const long long o_delta = act((long long)B * NH * T);
   const long long o_datt = act(att_floats);
@@ -135,7 +135,12 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
     x.fc = A + o[10]; x.fc_gelu = A + o[11]; x.res3 = A + o[12];
   }
   m->lnf = A + o_lnf; m->lnf_mean = A + o_lnf_mean; m->lnf_rstd = A + o_lnf_rstd;
-  m->logits = A + o_logits; m->losses = A + o_losses;
+  m->logits = A + o_logits; m->losses = A + o_losses; m->xlse = A + o_xlse;
+  // softmax / cross-entropy inside the lm_head GEMMs (GPT2_XENT=separate keeps the stand-alone kernel)
+  {
+    const char *env = getenv("GPT2_XENT");
+    m->fused_xent = !(env && !strcmp(env, "separate"));
+  }
   m->tmp_c = A + o_tmp; m->dresid = A + o_dres; m->dbig = A + o_dbig; m->delta = A + o_delta; m->datt = A + o_datt;
   *err = GPT2L_OK;
   return m;
@@ -217,8 +222,14 @@ int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt
     res = a.res3;
   }
   CK(layernorm_forward(m->lnf, m->lnf_mean, m->lnf_rstd, res, P + m->off_lnf_w, P + m->off_lnf_b, M, C, st));
-  CK(gpt2_linear_forward(m->logits, m->lnf, P + m->off_wte, nullptr, B, T, C, Vp, &o, stream));
-  CK(softmax_xent(m->logits, m->losses, targets, M, V, Vp, st));
+  m->targets = targets;
+  if (m->fused_xent) {
+    // loss and log-sum-exp come out of the lm_head's epilogue; the logits stay logits
+    CK(gpt2_linear_forward_xent(m->logits, m->losses, m->xlse, m->lnf, P + m->off_wte, targets, B, T, C, Vp, V, &o, stream));
+  } else {
+    CK(gpt2_linear_forward(m->logits, m->lnf, P + m->off_wte, nullptr, B, T, C, Vp, &o, stream));
+    CK(softmax_xent(m->logits, m->losses, targets, M, V, Vp, st));
+  }
   return GPT2L_OK;
 }
 
@@ -234,9 +245,17 @@ int gpt2_model_backward_head(gpt2_model *m, gpt2l_stream_t stream) {
   gpt2_linear_opts o = opts_for(m);
   if (cudaMemsetAsync(G, 0, (size_t)m->n_params * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
   if (cudaMemsetAsync(m->dresid, 0, (size_t)M * C * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;
-  // lm_head: the logits buffer holds dlogits since the forward pass
-  CK(gpt2_linear_backward_input(m->tmp_c, m->logits, P + m->off_wte, B, T, C, Vp, &o, stream));
-  CK(gpt2_linear_backward_weight(G + m->off_wte, nullptr, m->logits, m->lnf, B, T, C, Vp, &o, stream));
+  // lm_head: the logits buffer holds dlogits since the forward pass — or, with the fused cross-entropy, still
+  // the logits, which the two GEMMs turn into dlogits tile by tile as they read them
+  gpt2_linear_opts oh = o;
+  if (m->fused_xent) {
+    oh.xent_lse = m->xlse;
+    oh.xent_targets = m->targets;
+    oh.xent_vocab = m->cfg.vocab_size;
+    oh.xent_scale = 1.f / (float)M;
+  }
+  CK(gpt2_linear_backward_input(m->tmp_c, m->logits, P + m->off_wte, B, T, C, Vp, &oh, stream));
+  CK(gpt2_linear_backward_weight(G + m->off_wte, nullptr, m->logits, m->lnf, B, T, C, Vp, &oh, stream));
   const float *res_last = L > 0 ? m->la[L - 1].res3 : m->encoded;
   CK(layernorm_backward(m->dresid, G + m->off_lnf_w, G + m->off_lnf_b, m->tmp_c, res_last, P + m->off_lnf_w,
                         m->lnf_mean, m->lnf_rstd, M, C, st));

@@ -33,6 +33,9 @@ struct gpt2_model {
   long long acts_floats = 0;
   float *encoded = nullptr, *lnf = nullptr, *lnf_mean = nullptr, *lnf_rstd = nullptr, *logits = nullptr,
         *losses = nullptr;
+  float *xlse = nullptr;     // [M] base-2 log-sum-exp of the logits rows (fused lm_head + cross-entropy)
+  bool fused_xent = false;   // the loss rides in the lm_head epilogue and its gradient in the operand transform
+  const int *targets = nullptr;  // of the last forward
   float *tmp_c = nullptr;    // [M][C]   GEMM output before a residual add / small gradient scratch
   float *dresid = nullptr;   // [M][C]   gradient of the residual stream
   float *dbig = nullptr;     // [M][4C]  gradient scratch (d_fc, d_qkv)

@@ -338,6 +338,36 @@ __device__ __forceinline__ bool row_xent(const GemmOp *op, int tile, int w8, int
   return rs_.sync(p, op->op_index, lane);
 }
 
+// ---- lse[m], losses[m] from the softmax statistics the lm_head epilogue left (a warp per row; see
+// xent_combine_kernel in layers.cu for the stand-alone form) ----------------------------------------------
+__device__ __forceinline__ void row_xent_combine(const GemmOp *op, int tile, int w8, int lane) {
+  const RowArgs &a = op->ra;
+  const int M = a.i0, stride = a.i1, Vp = a.i4;
+  const int r0 = tile * op->rows_per_tile;
+  const int r1 = min(M, r0 + op->rows_per_tile);
+  for (int row = r0 + w8; row < r1; row += NUM_WORKER_WARPS) {
+    const float2 *s = reinterpret_cast<const float2 *>(a.in0) + (size_t)row * stride;
+    float m = -INFINITY, sum = 0.f;
+    for (int i = lane; i < stride; i += 32) {
+      const float2 v = s[i];
+      const float mn = fmaxf(m, v.x);
+      if (mn > -INFINITY) sum = (m == -INFINITY ? 0.f : sum * exp2f(m - mn)) + (v.x == -INFINITY ? 0.f : v.y * exp2f(v.x - mn));
+      m = mn;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, sum, o);
+      const float mn = fmaxf(m, m2);
+      sum = (m == -INFINITY ? 0.f : sum * exp2f(m - mn)) + (m2 == -INFINITY ? 0.f : s2 * exp2f(m2 - mn));
+      m = mn;
+    }
+    if (lane == 0) {
+      const float l2 = m + log2f(sum);
+      a.out0[row] = l2;
+      a.out1[row] = (l2 - a.in1[(long long)row * Vp + a.idx1[row]] * 1.4426950408889634f) * 0.6931471805599453f;
+    }
+  }
+}
+
 // ---- delta[b][h][t] = sum_d dout[m][h*64+d] * out[m][h*64+d]: a thread per (row, head) ----------------
 __device__ __forceinline__ void row_rowdot(const GemmOp *op, int tile, int wtid) {
   const RowArgs &a = op->ra;

@@ -150,6 +150,7 @@ struct gpt2l_step {
   std::vector<StepItem> items;
   float *scratch = nullptr;  // d_ln, d_atty, dqkv, xt of this step object
   float *d_ln = nullptr, *d_atty = nullptr, *dqkv = nullptr, *xt = nullptr;
+  float *xstats = nullptr;   // per-tile softmax statistics of the lm_head (fused cross-entropy)
   int with_update = 0;
   int n_ops = 0;
   int launches = 0;
@@ -162,6 +163,7 @@ void gpt2_free_schedule(gpt2l_step *s) {
   for (auto &it : s->items)
     if (it.sched) gpt2_schedule_destroy(it.sched);
   if (s->scratch) cudaFree(s->scratch);
+  if (s->xstats) cudaFree(s->xstats);
   delete s;
 }
 
@@ -266,9 +268,40 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     s.ra.out0 = m->lnf; s.ra.out1 = m->lnf_mean; s.ra.out2 = m->lnf_rstd; s.ra.i0 = M; s.ra.i1 = C;
     b.emit(s, {{res, ROW, false}}, {{m->lnf, ROW, false}});
   }
-  b.emit(gemm_spec(GPT2L_OP_FORWARD, M, C, Vp, m->logits, nullptr, m->lnf, P + m->off_wte, nullptr, o, L),
-         {{m->lnf, ROW, false}}, {{m->logits, ROW, false}});
-  {
+  gpt2_linear_opts oh = o, ohw = ow;  // the lm_head's backward GEMMs
+  if (m->fused_xent) {
+    // softmax statistics in the lm_head's epilogue, a small combine per row, and the gradient formed from the
+    // stored logits inside the two backward GEMMs: no pass over the [M][Vp] tensor of its own
+    OpSpec g = gemm_spec(GPT2L_OP_FORWARD, M, C, Vp, m->logits, nullptr, m->lnf, P + m->off_wte, nullptr, o, L);
+    g.gemm.opts.deterministic = 0;
+    g.gemm.xent_vocab = V;
+    g.gemm.xent_stats = reinterpret_cast<float *>(16);  // placeholder while the tiling is planned
+    GemmOp probe;
+    e = plan_op(g.gemm, ctx->num_sms, &probe);
+    if (!e && cudaMalloc(reinterpret_cast<void **>(&st->xstats), xent_stats_floats(probe) * sizeof(float)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      e = GPT2L_ERR_CUDA;
+    }
+    if (e) {
+      *err = e;
+      gpt2_free_schedule(st);
+      return nullptr;
+    }
+    g.gemm.xent_stats = st->xstats;
+    b.emit(g, {{m->lnf, ROW, false}}, {{m->logits, ROW, false}, {st->xstats, ROW, false}});
+    OpSpec s = row_spec(OPK_XENT_COMBINE, M, BM, L);
+    s.ra.in0 = st->xstats; s.ra.in1 = m->logits; s.ra.out0 = m->xlse; s.ra.out1 = m->losses; s.ra.idx1 = targets;
+    s.ra.i0 = M; s.ra.i1 = probe.xent_stride; s.ra.i3 = V; s.ra.i4 = Vp;
+    b.emit(s, {{st->xstats, ROW, false}, {m->logits, ROW, false}}, {{m->xlse, ROW, false}, {m->losses, ROW, false}});
+    for (gpt2_linear_opts *x : {&oh, &ohw}) {
+      x->xent_lse = m->xlse;
+      x->xent_targets = targets;
+      x->xent_vocab = V;
+      x->xent_scale = 1.f / (float)M;
+    }
+  } else {
+    b.emit(gemm_spec(GPT2L_OP_FORWARD, M, C, Vp, m->logits, nullptr, m->lnf, P + m->off_wte, nullptr, o, L),
+           {{m->lnf, ROW, false}}, {{m->logits, ROW, false}});
     OpSpec s = row_spec(OPK_XENT, M, 8, L);
     s.ra.out0 = m->logits; s.ra.out1 = m->losses; s.ra.idx1 = targets;
     s.ra.i0 = M; s.ra.i3 = V; s.ra.i4 = Vp; s.ra.f0 = 1.f / (float)M;
@@ -276,21 +309,21 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
   }
 
   // ---------------- backward ----------------
-  // lm_head: the logits buffer holds dlogits now
-  b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, C, Vp, st->d_ln, nullptr, m->logits, P + m->off_wte, nullptr, o, L),
-         {{m->logits, ROW, false}}, {{st->d_ln, ROW, false}});
+  // lm_head: the logits buffer holds dlogits now (or still the logits, with the fused cross-entropy)
+  b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, C, Vp, st->d_ln, nullptr, m->logits, P + m->off_wte, nullptr, oh, L),
+         {{m->logits, ROW, false}, {m->xlse, ROW, false}}, {{st->d_ln, ROW, false}});
   if (wide_head) {
     // the weight gradient of the lm_head reads its activations K-major: one transposed copy, then the
     // product in the forward form g_wte[C][Vp] = lnf^T[C][M] . dlogits[M][Vp]
     OpSpec t = row_spec(OPK_TRANSPOSE, M, BM, L);
     t.ra.in0 = m->lnf; t.ra.out0 = st->xt; t.ra.i0 = M; t.ra.i1 = C;
     b.emit(t, {{m->lnf, ROW, false}}, {{st->xt, WHOLE, false}});
-    OpSpec g = gemm_spec(GPT2L_OP_FORWARD, C, M, Vp, G + m->off_wte, nullptr, st->xt, m->logits, nullptr, ow, L);
+    OpSpec g = gemm_spec(GPT2L_OP_FORWARD, C, M, Vp, G + m->off_wte, nullptr, st->xt, m->logits, nullptr, ohw, L);
     g.transposed_a = true;
-    b.emit(g, {{st->xt, WHOLE, false}, {m->logits, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
+    b.emit(g, {{st->xt, WHOLE, false}, {m->logits, WHOLE, false}, {m->xlse, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
   } else {
-    b.emit(gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, Vp, G + m->off_wte, nullptr, m->lnf, m->logits, nullptr, ow, L),
-           {{m->lnf, WHOLE, false}, {m->logits, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
+    b.emit(gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, Vp, G + m->off_wte, nullptr, m->lnf, m->logits, nullptr, ohw, L),
+           {{m->lnf, WHOLE, false}, {m->logits, WHOLE, false}, {m->xlse, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
   }
   const float *res_last = L > 0 ? m->la[L - 1].res3 : m->encoded;
   std::vector<int> adam_after(L + 2, -1);  // op whose completion makes bucket i's gradients final
@@ -442,7 +475,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     }
     if (getenv("GPT2_STEP_DUMP")) {  // debugging aid: the piece as the kernel will see it
       static const char *names[] = {"gemm", "embed_fwd", "ln_fwd", "xent", "ln_bwd", "rowdot", "embed_bwd", "adamw",
-                                    "attn_fwd", "attn_bwd_kv", "attn_bwd_q", "transpose"};
+                                    "attn_fwd", "attn_bwd_kv", "attn_bwd_q", "transpose", "xent_combine"};
       fprintf(stderr, "piece %d: %d ops, %d tiles, grid %d\n", (int)st->items.size(), (int)specs.size(),
               piece.sched->plan.total_tiles, piece.sched->grid);
       for (size_t j = 0; j < specs.size(); ++j) {

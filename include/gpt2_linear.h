@@ -72,6 +72,13 @@ typedef struct gpt2_linear_opts {
   int cta_pair;      /* 0 = choose; 1 = one CTA per 128-row tile; 2 = CTA pairs, 256-row tiles */
   const float *aux;  /* epilogue operand, [rows][cols] of the output; NULL = none           */
   int aux_op;        /* GPT2L_AUX_*                                                         */
+  /* Softmax / cross-entropy folded into the lm_head's backward calls (see gpt2_linear_forward_xent).
+   * With xent_lse set, the g_out argument of backward_input / backward_weight holds the LOGITS and the
+   * kernels turn them into (softmax - onehot(target)) * xent_scale while the tiles sit in shared memory. */
+  const float *xent_lse;   /* [B*S] base-2 log-sum-exp of each row, from gpt2_linear_forward_xent; NULL = off */
+  const int *xent_targets; /* [B*S] target column of each row                                                  */
+  int xent_vocab;          /* true vocabulary <= N: columns at or past it carry no probability and no gradient  */
+  float xent_scale;        /* gradient scale, 1 / (B*S) for the mean loss                                       */
 } gpt2_linear_opts;
 
 /* One-time set-up for the current device: checks the architecture, raises the dynamic
@@ -101,6 +108,22 @@ int gpt2_linear_last_status(int out[6]);
 int gpt2_linear_forward(float *out, const float *in, const float *w, const float *b,
                         int B, int S, int K, int N,
                         const gpt2_linear_opts *opts, gpt2l_stream_t stream);
+
+/*
+ * The lm_head forward with softmax and cross-entropy in its epilogue: logits[M][N] = in[M][K] . w[K][N] as
+ * gpt2_linear_forward (no bias), and for every row lse[m] = log2 sum_{c < V} 2^(logits[m][c] log2 e) and
+ * losses[m] = -log softmax(logits[m][:V])[targets[m]]. The reference computes the same in three more kernels
+ * over the logits (softmax_forward, cross_entropy_forward, cross_entropy_backward: src/train.cu:378, 388, 402;
+ * megakernel cases 14-16, src/mk.cu:1384-1412), reading and writing the [M][V] tensor again each time; here
+ * the epilogue keeps running (max, sum) pairs per row while it stores the tile, a small second kernel
+ * combines them, and the gradient is never stored: pass `lse`, `targets`, V and the scale through
+ * opts->xent_* to gpt2_linear_backward_input / _backward_weight, with the logits in place of g_out.
+ * V <= N; columns V..N-1 (vocabulary padding) are excluded. Tensor-core path only (GPT2L_ERR_BAD_ARG for
+ * shapes it cannot take).
+ */
+int gpt2_linear_forward_xent(float *logits, float *losses, float *lse, const float *in, const float *w,
+                             const int *targets, int B, int S, int K, int N, int V,
+                             const gpt2_linear_opts *opts, gpt2l_stream_t stream);
 
 /*
  * g_in[M][K] = g_out[M][N] . w[K][N]^T          (overwrites g_in)
