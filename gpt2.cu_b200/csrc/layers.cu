@@ -386,6 +386,25 @@ __global__ void xent_combine_kernel(float *lse, float *losses, const float2 *sta
   }
 }
 
+// logits[m][c] <- (2^(logits[m][c] log2 e - lse[m]) - [c == target[m]]) * scale for c < V, 0 for the pad columns:
+// the gradient of the mean cross-entropy, in place, one read and one write of the tensor (the row maxima and
+// sums are known already, so nothing is reduced here). A block per row.
+__global__ void __launch_bounds__(512)
+xent_grad_inplace_kernel(float *logits, const float *lse, const int *targets, int V, int Vp, float scale) {
+  float *row = logits + (long long)blockIdx.x * Vp;
+  const float l2 = lse[blockIdx.x];
+  const int tgt = targets[blockIdx.x];
+  const float L2E = 1.4426950408889634f;
+  for (int c = threadIdx.x * 4; c < Vp; c += 512 * 4) {  // Vp is a multiple of 4
+    float4 g = *reinterpret_cast<const float4 *>(row + c);
+    g.x = c + 0 < V ? (exp2f(g.x * L2E - l2) - (c + 0 == tgt ? 1.f : 0.f)) * scale : 0.f;
+    g.y = c + 1 < V ? (exp2f(g.y * L2E - l2) - (c + 1 == tgt ? 1.f : 0.f)) * scale : 0.f;
+    g.z = c + 2 < V ? (exp2f(g.z * L2E - l2) - (c + 2 == tgt ? 1.f : 0.f)) * scale : 0.f;
+    g.w = c + 3 < V ? (exp2f(g.w * L2E - l2) - (c + 3 == tgt ? 1.f : 0.f)) * scale : 0.f;
+    *reinterpret_cast<float4 *>(row + c) = g;
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // causal self-attention, flash style, head size 64. qkv[m][3C] = q | k | v, head h at columns h*64.
 // forward: out[m][h*64 + d], lse[b][h][t] = log sum_j exp(q_t.k_j / 8)
@@ -770,6 +789,11 @@ int launch_xent_combine(float *lse, float *losses, const float *stats, int strid
                         const int *targets, int M, cudaStream_t s) {
   xent_combine_kernel<<<cdiv(M, 8), 256, 0, s>>>(lse, losses, reinterpret_cast<const float2 *>(stats), stride, logits, ld,
                                                   targets, M);
+  return LAUNCH_OK();
+}
+int xent_grad_inplace(float *logits, const float *lse, const int *targets, int M, int V, int Vp, cudaStream_t s) {
+  if (Vp & 3) return GPT2L_ERR_BAD_ARG;
+  xent_grad_inplace_kernel<<<M, 512, 0, s>>>(logits, lse, targets, V, Vp, 1.f / (float)M);
   return LAUNCH_OK();
 }
 int attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t s) {

@@ -16,6 +16,8 @@ int layernorm_backward(float *g_in, float *g_w, float *g_b, const float *g_out, 
 int add_forward(float *out, const float *a, const float *b, long long n, cudaStream_t s);
 int gelu_backward(float *g, const float *pre, long long n, cudaStream_t s);
 int softmax_xent(float *logits, float *losses, const int *targets, int M, int V, int Vp, cudaStream_t s);
+// logits <- gradient of the mean cross-entropy, in place, from the rows' base-2 log-sum-exp (one read, one write)
+int xent_grad_inplace(float *logits, const float *lse, const int *targets, int M, int V, int Vp, cudaStream_t s);
 int attention_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t s);
 int attention_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
                        const float *lse, int B, int T, int C, int NH, cudaStream_t s);

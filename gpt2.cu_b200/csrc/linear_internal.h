@@ -61,7 +61,8 @@ enum OpKind : int {
   OPK_ATTN_BWD_KV = 9,  //   dK, dV
   OPK_ATTN_BWD_Q = 10,  //   dQ
   OPK_TRANSPOSE = 11,   // out[c][m] = in[m][c] (K-major copy of activations for wide weight gradients)
-  OPK_XENT_COMBINE = 12 // lse[m], loss[m] from the per-tile softmax statistics the lm_head epilogue left
+  OPK_XENT_COMBINE = 12, // lse[m], loss[m] from the per-tile softmax statistics the lm_head epilogue left
+  OPK_XENT_GRAD = 13     // logits[m][:] <- gradient of the mean cross-entropy, elementwise from lse[m]
 };
 
 // Operands of a non-GEMM op (meaning per kind: see the builder in step_schedule.cu)

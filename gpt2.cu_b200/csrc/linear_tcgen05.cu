@@ -68,15 +68,8 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
   // softmax / cross-entropy backward folded into the operand: the logits become dlogits in shared memory
   const int xmode = op->xent_mode;
   const bool rewrites = X3 || xmode >= 2;
-  float x_lse = 0.f;
+  float x_lse = 0.f;  // xmode 2 (A operand, K-major): this thread owns row x of the tile for the whole tile
   int x_tgt = -1;
-  if (xmode == 2) {  // A operand, K-major: this thread owns row x of the tile for the whole tile
-    const int grow = tc.m_tile * BM + x;
-    if (grow < op->Mc) {
-      x_lse = op->xent_lse[grow];
-      x_tgt = op->xent_tgt[grow];
-    }
-  }
   // bias gradient = column sums of the B blocks. Spread over the tile rows (row m takes the
   // k-blocks with kb % tiles_m == m) so that no CTA carries the whole extra pass: with tile row 0
   // doing all of it those CTAs ran ~30 % longer than the rest and the launch waited for them.
@@ -97,11 +90,21 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     const int s = it % R::NST;
     const uint32_t ph = (it / R::NST) & 1u;
     int okl = 1;
+    // a stage these warps rewrite is on the MMA's critical path: no back-off while waiting for it
     if (lane == 0)
-      okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s, X3 ? 0 : 64);
+      okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s, rewrites ? 0 : 64);
     ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
     if (!ok) break;
     uint8_t *stage = ring_ptr + s * R::STAGE_STRIDE;
+    if (xmode == 2 && kb == tc.kb0) {
+      // only now: the tile's first block has landed, so the producer has seen the tile's dependencies
+      // (the row statistics among them) complete
+      const int grow = tc.m_tile * BM + x;
+      if (grow < op->Mc) {
+        x_lse = op->xent_lse[grow];
+        x_tgt = op->xent_tgt[grow];
+      }
+    }
     // An MN-major B block is walked by (column group, k-row) so that the thread that sums a
     // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
     // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
@@ -414,6 +417,7 @@ __device__ __noinline__ bool row_op_tile(const GemmOp *op, const Tile &tc, int w
     case OPK_ADAMW: row_adamw(op, tile, wtid, p); break;
     case OPK_TRANSPOSE: row_transpose(op, tile, w8, lane, scratch + w8 * 1024); break;
     case OPK_XENT_COMBINE: row_xent_combine(op, tile, w8, lane); break;
+    case OPK_XENT_GRAD: row_xent_grad(op, tile, wtid); break;
     default: break;
   }
   if (!ok) return false;

@@ -136,10 +136,12 @@ gpt2_model *gpt2_model_create(const gpt2_model_config *cfg, int B, int T, int mo
   }
   m->lnf = A + o_lnf; m->lnf_mean = A + o_lnf_mean; m->lnf_rstd = A + o_lnf_rstd;
   m->logits = A + o_logits; m->losses = A + o_losses; m->xlse = A + o_xlse;
-  // softmax / cross-entropy inside the lm_head GEMMs (GPT2_XENT=separate keeps the stand-alone kernel)
+  // where softmax / cross-entropy run (see model_internal.h): GPT2_XENT = separate | stats | fused
   {
     const char *env = getenv("GPT2_XENT");
-    m->fused_xent = !(env && !strcmp(env, "separate"));
+    m->xent_path = 1;
+    if (env && !strcmp(env, "separate")) m->xent_path = 0;
+    if (env && !strcmp(env, "fused")) m->xent_path = 2;
   }
   m->tmp_c = A + o_tmp; m->dresid = A + o_dres; m->dbig = A + o_dbig; m->delta = A + o_delta; m->datt = A + o_datt;
   *err = GPT2L_OK;
@@ -223,9 +225,10 @@ int gpt2_model_forward(gpt2_model *m, const int *tokens, const int *targets, gpt
   }
   CK(layernorm_forward(m->lnf, m->lnf_mean, m->lnf_rstd, res, P + m->off_lnf_w, P + m->off_lnf_b, M, C, st));
   m->targets = targets;
-  if (m->fused_xent) {
-    // loss and log-sum-exp come out of the lm_head's epilogue; the logits stay logits
+  if (m->xent_path) {
+    // loss and log-sum-exp come out of the lm_head's epilogue
     CK(gpt2_linear_forward_xent(m->logits, m->losses, m->xlse, m->lnf, P + m->off_wte, targets, B, T, C, Vp, V, &o, stream));
+    if (m->xent_path == 1) CK(xent_grad_inplace(m->logits, m->xlse, targets, M, V, Vp, st));
   } else {
     CK(gpt2_linear_forward(m->logits, m->lnf, P + m->off_wte, nullptr, B, T, C, Vp, &o, stream));
     CK(softmax_xent(m->logits, m->losses, targets, M, V, Vp, st));
@@ -248,7 +251,7 @@ int gpt2_model_backward_head(gpt2_model *m, gpt2l_stream_t stream) {
   // lm_head: the logits buffer holds dlogits since the forward pass — or, with the fused cross-entropy, still
   // the logits, which the two GEMMs turn into dlogits tile by tile as they read them
   gpt2_linear_opts oh = o;
-  if (m->fused_xent) {
+  if (m->xent_path == 2) {
     oh.xent_lse = m->xlse;
     oh.xent_targets = m->targets;
     oh.xent_vocab = m->cfg.vocab_size;

@@ -34,7 +34,10 @@ struct gpt2_model {
   float *encoded = nullptr, *lnf = nullptr, *lnf_mean = nullptr, *lnf_rstd = nullptr, *logits = nullptr,
         *losses = nullptr;
   float *xlse = nullptr;     // [M] base-2 log-sum-exp of the logits rows (fused lm_head + cross-entropy)
-  bool fused_xent = false;   // the loss rides in the lm_head epilogue and its gradient in the operand transform
+  // how the loss is computed: 0 = a softmax / cross-entropy kernel over the logits after the lm_head;
+  // 1 = statistics in the lm_head's epilogue, then one elementwise pass that turns the logits into their gradient;
+  // 2 = statistics in the epilogue and the gradient formed inside the two backward GEMMs (no pass of its own)
+  int xent_path = 0;
   const int *targets = nullptr;  // of the last forward
   float *tmp_c = nullptr;    // [M][C]   GEMM output before a residual add / small gradient scratch
   float *dresid = nullptr;   // [M][C]   gradient of the residual stream

@@ -368,6 +368,42 @@ __device__ __forceinline__ void row_xent_combine(const GemmOp *op, int tile, int
   }
 }
 
+// ---- logits[m][:] <- (softmax - onehot) * scale from the rows' log-sum-exp: elementwise, every thread keeps
+// XG independent 16-byte loads in flight; no thread needs another's result ------------------------------------
+__device__ __forceinline__ void row_xent_grad(const GemmOp *op, int tile, int wtid) {
+  const RowArgs &a = op->ra;
+  const int M = a.i0, V = a.i3, Vp = a.i4;
+  const float scale = a.f0;
+  constexpr int NT = NUM_WORKER_WARPS * 32, XG = 8;
+  const int r0 = tile * op->rows_per_tile;
+  const int r1 = min(M, r0 + op->rows_per_tile);
+  for (int rowi = r0; rowi < r1; ++rowi) {
+    float *row = a.out0 + (long long)rowi * Vp;
+    const float l2 = a.in0[rowi];
+    const int tgt = a.idx1[rowi];
+    for (int c0 = wtid * 4; c0 < Vp; c0 += NT * 4 * XG) {
+      float4 gv[XG];
+#pragma unroll
+      for (int u = 0; u < XG; ++u) {
+        const int c = c0 + u * NT * 4;
+        gv[u] = c < Vp ? *reinterpret_cast<const float4 *>(row + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < XG; ++u) {
+        const int c = c0 + u * NT * 4;
+        if (c < Vp) {
+          float4 g = gv[u];
+          g.x = xent_grad(g.x, l2, c, tgt, V, scale);
+          g.y = xent_grad(g.y, l2, c + 1, tgt, V, scale);
+          g.z = xent_grad(g.z, l2, c + 2, tgt, V, scale);
+          g.w = xent_grad(g.w, l2, c + 3, tgt, V, scale);
+          *reinterpret_cast<float4 *>(row + c) = g;
+        }
+      }
+    }
+  }
+}
+
 // ---- delta[b][h][t] = sum_d dout[m][h*64+d] * out[m][h*64+d]: a thread per (row, head) ----------------
 __device__ __forceinline__ void row_rowdot(const GemmOp *op, int tile, int wtid) {
   const RowArgs &a = op->ra;

@@ -269,9 +269,10 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     b.emit(s, {{res, ROW, false}}, {{m->lnf, ROW, false}});
   }
   gpt2_linear_opts oh = o, ohw = ow;  // the lm_head's backward GEMMs
-  if (m->fused_xent) {
-    // softmax statistics in the lm_head's epilogue, a small combine per row, and the gradient formed from the
-    // stored logits inside the two backward GEMMs: no pass over the [M][Vp] tensor of its own
+  if (m->xent_path) {
+    // softmax statistics in the lm_head's epilogue and a small combine per row; then either one elementwise
+    // pass that turns the logits into their gradient, or the gradient formed from the stored logits inside the
+    // two backward GEMMs
     OpSpec g = gemm_spec(GPT2L_OP_FORWARD, M, C, Vp, m->logits, nullptr, m->lnf, P + m->off_wte, nullptr, o, L);
     g.gemm.opts.deterministic = 0;
     g.gemm.xent_vocab = V;
@@ -293,11 +294,18 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     s.ra.in0 = st->xstats; s.ra.in1 = m->logits; s.ra.out0 = m->xlse; s.ra.out1 = m->losses; s.ra.idx1 = targets;
     s.ra.i0 = M; s.ra.i1 = probe.xent_stride; s.ra.i3 = V; s.ra.i4 = Vp;
     b.emit(s, {{st->xstats, ROW, false}, {m->logits, ROW, false}}, {{m->xlse, ROW, false}, {m->losses, ROW, false}});
-    for (gpt2_linear_opts *x : {&oh, &ohw}) {
-      x->xent_lse = m->xlse;
-      x->xent_targets = targets;
-      x->xent_vocab = V;
-      x->xent_scale = 1.f / (float)M;
+    if (m->xent_path == 2) {
+      for (gpt2_linear_opts *x : {&oh, &ohw}) {
+        x->xent_lse = m->xlse;
+        x->xent_targets = targets;
+        x->xent_vocab = V;
+        x->xent_scale = 1.f / (float)M;
+      }
+    } else {
+      OpSpec d = row_spec(OPK_XENT_GRAD, M, 8, L);
+      d.ra.in0 = m->xlse; d.ra.out0 = m->logits; d.ra.idx1 = targets;
+      d.ra.i0 = M; d.ra.i3 = V; d.ra.i4 = Vp; d.ra.f0 = 1.f / (float)M;
+      b.emit(d, {{m->logits, ROW, false}, {m->xlse, ROW, false}}, {{m->logits, ROW, false}});
     }
   } else {
     b.emit(gemm_spec(GPT2L_OP_FORWARD, M, C, Vp, m->logits, nullptr, m->lnf, P + m->off_wte, nullptr, o, L),
@@ -475,7 +483,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     }
     if (getenv("GPT2_STEP_DUMP")) {  // debugging aid: the piece as the kernel will see it
       static const char *names[] = {"gemm", "embed_fwd", "ln_fwd", "xent", "ln_bwd", "rowdot", "embed_bwd", "adamw",
-                                    "attn_fwd", "attn_bwd_kv", "attn_bwd_q", "transpose", "xent_combine"};
+                                    "attn_fwd", "attn_bwd_kv", "attn_bwd_q", "transpose", "xent_combine", "xent_grad"};
       fprintf(stderr, "piece %d: %d ops, %d tiles, grid %d\n", (int)st->items.size(), (int)specs.size(),
               piece.sched->plan.total_tiles, piece.sched->grid);
       for (size_t j = 0; j < specs.size(); ++j) {

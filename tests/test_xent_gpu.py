@@ -102,9 +102,10 @@ def test_fused_cross_entropy_argument_checks(gpu):
 
 
 def test_model_with_fused_cross_entropy_equals_the_separate_kernel(gpu, monkeypatch):
-    """One forward + backward of a two-layer model at GPT-2 small's width (3xTF32): the fused lm_head +
-    cross-entropy and the stand-alone softmax / cross-entropy kernel give the same loss (1e-6) and the same
-    gradients (1e-5 of each tensor's largest entry)."""
+    """One forward + backward of a two-layer model at GPT-2 small's width (3xTF32): the three ways the loss
+    can run (GPT2_XENT = fused | stats | separate: gradient inside the backward GEMMs; statistics in the lm_head
+    epilogue + one elementwise pass; the stand-alone softmax / cross-entropy kernel) give the same loss (1e-6)
+    and the same gradients (1e-5 of each tensor's largest entry)."""
     import os, sys
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     import gpt2_ref
@@ -114,9 +115,8 @@ def test_model_with_fused_cross_entropy_equals_the_separate_kernel(gpu, monkeypa
     tok = torch.from_numpy(rng.integers(0, vocab, B * T).astype(np.int32)).cuda()
     tgt = torch.from_numpy(rng.integers(0, vocab, B * T).astype(np.int32)).cuda()
     res = {}
-    for kind in ("fused", "separate"):
-        if kind == "separate":
-            monkeypatch.setenv("GPT2_XENT", "separate")
+    for kind in ("fused", "stats", "separate"):
+        monkeypatch.setenv("GPT2_XENT", kind)
         m = gpu.Model(vocab, padded, n_layer, n_head, n_embd, block, B, T, mode=1)
         m.set_params(params)
         assert m.forward(tok, tgt) == 0
@@ -131,9 +131,10 @@ def test_model_with_fused_cross_entropy_equals_the_separate_kernel(gpu, monkeypa
         res[kind] = (loss, g)
         m.close()
     monkeypatch.delenv("GPT2_XENT")
-    assert abs(res["fused"][0] - res["separate"][0]) <= 1e-6
-    a, b = res["fused"][1], res["separate"][1]
-    assert np.isfinite(a).all()
-    for i in range(len(bounds) - 1):
-        x, y = a[bounds[i]:bounds[i + 1]], b[bounds[i]:bounds[i + 1]]
-        assert np.abs(x - y).max() <= 1e-5 * max(np.abs(y).max(), 1e-12), (i, np.abs(x - y).max(), np.abs(y).max())
+    for kind in ("fused", "stats"):
+        assert abs(res[kind][0] - res["separate"][0]) <= 1e-6
+        a, b = res[kind][1], res["separate"][1]
+        assert np.isfinite(a).all()
+        for i in range(len(bounds) - 1):
+            x, y = a[bounds[i]:bounds[i + 1]], b[bounds[i]:bounds[i + 1]]
+            assert np.abs(x - y).max() <= 1e-5 * max(np.abs(y).max(), 1e-12), (kind, i, np.abs(x - y).max(), np.abs(y).max())
