@@ -222,9 +222,15 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = 485.5e6  # profiles/tcgen05_kernel_gemm_set_launc
 
 
 def init_nccl(torch, dist, local_rank):
-    """NCCL with a cap on the CTAs a collective may take: the persistent GEMM kernels want every SM, and a
-    collective that spreads over many of them delays a whole GEMM launch (the cap is reported)."""
-    cap = 8
+    """NCCL, optionally with a cap on the CTAs a collective may take (environment variable
+    GPT2_NCCL_MAX_CTAS; default 0 = NCCL's own choice). The persistent GEMM kernels want every SM, so a
+    collective that spreads over many of them delays a GEMM launch — but on two GPUs a cap of 8 made the
+    training step slower (44.3 against 43.0 ms), the all-reduce itself becoming the longer pole, so no cap is
+    the default and whatever was used is reported."""
+    cap = int(os.environ.get("GPT2_NCCL_MAX_CTAS", "0"))
+    if cap <= 0:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        return None
     try:
         opts = dist.ProcessGroupNCCL.Options()
         opts.config.max_ctas = cap
@@ -240,6 +246,10 @@ def init_nccl(torch, dist, local_rank):
 def run_ours(args):
     import torch
     import torch.distributed as dist
+
+    # stdout carries exactly one JSON line: whatever libraries print there meanwhile goes to stderr
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -333,8 +343,11 @@ def run_ours(args):
     # ---- the GEMM path inside a whole training step (GPT-2 small, B=16 per GPU, T=1024)
     dd = dist if world > 1 else None
     train = wl.measure_train(g, dp, torch, local_rank, rank, world, barrier, dd, mode)
-    train_step = None
+    train_step = train_eager = None
     if world == 1:
+        # the same step the way ranks of a multi-GPU run execute it (no graph replay): the N = 1 point of a
+        # like-with-like scaling curve
+        train_eager = wl.measure_train(g, dp, torch, local_rank, rank, world, barrier, None, mode, graph=False)
         try:
             train_step = wl.measure_train(g, dp, torch, local_rank, rank, world, barrier, None, mode, path="step")
         except BaseException as exc:  # reported beside the separate-launch figure, never instead of it
@@ -372,7 +385,7 @@ def run_ours(args):
         "peak_source": f"MEASURED_PEAKS.json bf16 {'burst' if timed_s < 1.0 else 'sustained'} figure / 2 (TF32 rate), of "
                        f"{peaks['source']}; timed region {timed_s:.2f} s; burst-derived {burst}, sustained-derived {sustained}",
     }
-    for t in (train, train_step):
+    for t in (train, train_step, train_eager):
         if t and "gemm_tflops" in t:
             t["roofline"] = {"bound": "tensor", "achieved": t["gemm_tflops"], "peak": sustained, "unit": "TFLOP/s",
                              "frac": t["gemm_tflops"] / sustained,
@@ -398,12 +411,15 @@ def run_ours(args):
     if base:
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
     line["train"] = train
+    if train_eager is not None:
+        line["train_eager"] = train_eager
     if train_step is not None:
         line["train_step_kernel"] = train_step
     line["train_small"] = train_small
     if gemm_list is not None:
         line["gemm_list"] = gemm_list
-    print(json.dumps(line), flush=True)
+    json_out.write(json.dumps(line) + "\n")
+    json_out.flush()
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -6,6 +6,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "linear_internal.h"
@@ -113,6 +114,59 @@ static int ensure_bytes(float **buf, size_t *have, size_t need) {
   return GPT2L_OK;
 }
 
+// Built ops (tiling, instruction descriptor and the three or four tensor maps) keyed by everything that
+// went into them: a training loop makes the same calls on the same buffers every step, so the tensor maps
+// are encoded once per (pointers, shape, options) instead of once per call.
+struct OpKey {
+  alignas(16) unsigned char bytes[sizeof(GemmDesc)];
+  bool operator==(const OpKey &o) const { return memcmp(bytes, o.bytes, sizeof(bytes)) == 0; }
+};
+struct OpKeyHash {
+  size_t operator()(const OpKey &k) const {
+    size_t h = 1469598103934665603ull;  // FNV-1a
+    for (unsigned char b : k.bytes) h = (h ^ b) * 1099511628211ull;
+    return h;
+  }
+};
+static std::unordered_map<OpKey, GemmOp, OpKeyHash> g_op_cache[MAX_DEVICES];
+static std::mutex g_cache_mu;
+constexpr size_t OP_CACHE_MAX = 4096;
+
+static OpKey key_of(const GemmDesc &d) {
+  OpKey k;
+  memset(k.bytes, 0, sizeof(k.bytes));
+  GemmDesc *dst = reinterpret_cast<GemmDesc *>(k.bytes);  // field by field: padding bytes stay zero
+  dst->kind = d.kind; dst->M = d.M; dst->K = d.K; dst->N = d.N;
+  dst->xent_stats = d.xent_stats; dst->xent_vocab = d.xent_vocab;
+  dst->out = d.out; dst->out_bias = d.out_bias; dst->a = d.a; dst->b = d.b; dst->bias = d.bias;
+  dst->opts.mode = d.opts.mode; dst->opts.flags = d.opts.flags; dst->opts.split_k = d.opts.split_k;
+  dst->opts.deterministic = d.opts.deterministic; dst->opts.out2 = d.opts.out2; dst->opts.force_simt = d.opts.force_simt;
+  dst->opts.cta_pair = d.opts.cta_pair; dst->opts.aux = d.opts.aux; dst->opts.aux_op = d.opts.aux_op;
+  dst->opts.xent_lse = d.opts.xent_lse; dst->opts.xent_targets = d.opts.xent_targets;
+  dst->opts.xent_vocab = d.opts.xent_vocab; dst->opts.xent_scale = d.opts.xent_scale;
+  return k;
+}
+
+static int build_op_cached(DeviceCtx *ctx, const GemmDesc &d, GemmOp *op) {
+  const OpKey k = key_of(d);
+  {
+    std::lock_guard<std::mutex> lk(g_cache_mu);
+    auto &cache = g_op_cache[ctx->device];
+    auto it = cache.find(k);
+    if (it != cache.end()) {
+      *op = it->second;
+      return GPT2L_OK;
+    }
+  }
+  int e = build_op(d, ctx->num_sms, op);
+  if (e) return e;
+  std::lock_guard<std::mutex> lk(g_cache_mu);
+  auto &cache = g_op_cache[ctx->device];
+  if (cache.size() >= OP_CACHE_MAX) cache.clear();
+  cache.emplace(k, *op);
+  return GPT2L_OK;
+}
+
 static int run_gemm(GemmDesc &d, cudaStream_t st) {
   int err;
   DeviceCtx *ctx = ctx_current(&err);
@@ -159,7 +213,7 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
     dd.opts.flags = 0;
     transposed_a = true;
   }
-  err = build_op(dd, ctx->num_sms, &op);
+  err = build_op_cached(ctx, dd, &op);
   if (err) return err;
   if (transposed_a) op.colsum = fused_bias;  // the B operand is still g_out: its column sums are g_b
   if (op.splits > 1) {
@@ -272,6 +326,10 @@ void gpt2_linear_shutdown(void) {
     for (int i = 0; i < 4; ++i)
       if (c.stage[i]) cudaFree(c.stage[i]);
     destroy_pipe(c.pipe);
+    {
+      std::lock_guard<std::mutex> lk2(g_cache_mu);
+      g_op_cache[d].clear();
+    }
     c = DeviceCtx();
   }
   if (cur >= 0) cudaSetDevice(cur);

@@ -167,13 +167,14 @@ def seeded_model(g, model_name, B, T, mode):
 
 
 def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=16, T=1024, steps=5, warmup=3,
-                  model_name="small", path="launches"):
+                  model_name="small", path="launches", graph=None):
     """Tokens/s of whole training steps (forward, backward, gradient all-reduce over NCCL overlapped with the
     backward pass, AdamW) at B sequences of T tokens per GPU, random-init weights and uniform random tokens.
 
     path = "launches": one launch per layer call; with one rank, forward + backward are replayed from a CUDA
-    graph. path = "step": the whole step as a schedule of the persistent kernel (one rank only: AdamW is part
-    of the launch). Returns tokens/s, ms per step, the last loss, and a checksum of the parameters that all
+    graph (graph=False keeps the eager launches that more than one rank uses, for a like-with-like scaling
+    curve). path = "step": the whole step as a schedule of the persistent kernel (one rank only: AdamW is
+    part of the launch). Returns tokens/s, ms per step, the last loss, and a checksum of the parameters that all
     ranks must share."""
     C, L, NH = MODELS[model_name]
     model = seeded_model(g, model_name, B, T, mode)
@@ -192,7 +193,8 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
         def one(t):
             return sched.run(*hyper, t, stream)
     else:
-        runner = dp.DataParallelStep(model, torch.device("cuda", local_rank), use_graph=(world == 1))
+        use_graph = (world == 1) if graph is None else (graph and world == 1)
+        runner = dp.DataParallelStep(model, torch.device("cuda", local_rank), use_graph=use_graph)
 
         def one(t):
             return runner(tok, tgt, *hyper, t, stream)
@@ -242,7 +244,8 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
         out["ops"] = info["ops"]
         out["tiles"] = info["tiles"]
     elif world == 1:
-        out["launches_per_step"] = "forward + backward replayed from a CUDA graph"
+        out["launches_per_step"] = ("forward + backward replayed from a CUDA graph" if use_graph else
+                                    "separate launches, eager (the path more than one rank uses)")
     if path == "step":
         sched.close()
     model.close()
