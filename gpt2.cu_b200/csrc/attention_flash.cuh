@@ -312,9 +312,9 @@ __device__ __forceinline__ void attn_tile_body(const FlashMaps &maps, const Flas
               mma_tf32_tmem_a(d, a_tmem + kb * 32 + ks * 8, smem_desc(hiMN, b_addr + kb * 8192 + ks * 1024), idesc_ac, acc);
             }
         }
+        mma_commit(smem_u32(&ctrl->acc_done[I & 1u]));
         mma_commit(smem_u32(&ctrl->ac_empty[st]));
         mma_commit(smem_u32(&ctrl->slot_free[I % K::NSB]));
-        mma_commit(smem_u32(&ctrl->acc_done[I & 1u]));  // last: whoever sees it may assume the other two have fired
         return true;
       };
       bool ok = true;
