@@ -217,8 +217,9 @@ def workload_config(args, rows=M_ROWS):
 # our arm
 # ------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over the
-# 15 launches of one step, from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 485.5e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
+# 15 launches of one step: the ncu capture of the half-size set (4096 rows: 246.1 MB per launch against
+# 244.2 MB algorithmic, 1.008x) carried to 8192 rows by that ratio (452.5 MB algorithmic per launch).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 456.0e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
 
 
 def init_nccl(torch, dist, local_rank):
