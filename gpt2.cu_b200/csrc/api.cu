@@ -215,7 +215,11 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   }
   err = build_op_cached(ctx, dd, &op);
   if (err) return err;
-  if (transposed_a) op.colsum = fused_bias;  // the B operand is still g_out: its column sums are g_b
+  if (transposed_a) {  // the B operand is still g_out: its column sums are g_b
+    op.colsum = fused_bias;
+    op.colsum_spread = (fused_bias && !op.pair) ? 1 : 0;
+    op.cs_src = d.b;
+  }
   if (op.splits > 1) {
     if (op.atomic_out) {
       if (cudaMemsetAsync(op.C, 0, (size_t)op.Mc * op.Nc * sizeof(float), st) != cudaSuccess) return GPT2L_ERR_CUDA;

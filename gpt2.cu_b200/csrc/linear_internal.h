@@ -120,6 +120,8 @@ struct alignas(64) GemmOp {
   float aux_scale;
   const float *bias;    // [Nc] or null
   float *colsum;        // wgrad: g_b[Nc] or null (column sums of B over the reduction)
+  const float *cs_src;  // the B operand [Kc][Nc] as a plain pointer (row stride Nc): TF32-mode column sums read it
+                        // from global memory, beside the ring
   int colsum_spread;     // 1: every tile row sums its share of the k-blocks (kb % tiles_m == m_tile) and adds
                          // it atomically into a zeroed colsum; 0: tile row 0 sums everything
   float *ws;            // deterministic split-K: partial tiles [n_tiles][BM*bn]

@@ -86,13 +86,64 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
   float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
   const int stage_f4 = (A_TILE_BYTES + bn * BK * 4) >> 4;
 
+  if (!rewrites && (spread || !has_cs)) {
+    // TF32 mode: the stages need nothing from these warps (the MMA lane arrives on empty[s] in their place),
+    // and the column sums do not go through the ring at all. Shared-memory loads of these warps crawl while
+    // the tensor core and the copy engine keep the banks busy, and a stage held for them stalls a ring that
+    // is only four deep; so this tile row's share of the k-blocks (kb % tiles_m == m_tile) is read once more
+    // from global memory, where the copy engine has just brought it into L2, whole rows at a time.
+    it += (uint32_t)(tc.kb1 - tc.kb0);
+    if (!has_cs) return true;
+    if (op->wait_ctr[0] >= 0) {  // step kernel: the operand's producers are done before it is read
+      unsigned seen = 0u;
+      int okl = 1;
+      if (lane == 0) okl = wait_deps(op, tc.m_tile, ctrl, p, seen) ? 1 : 0;
+      if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
+    }
+    const int g_groups = bn >> 2;          // float4 column groups of the tile: 16, 32 or 64
+    const int g_parts = 128 / g_groups;    // threads that share a group, each with 32 / g_parts rows of a block
+    const int g_rows = 32 / g_parts;
+    const int g_grp = x % g_groups, g_part = x / g_groups;
+    const int col = tc.n_tile * bn + g_grp * 4;
+    if (col < op->Nc) {
+      const int tm = op->tiles_m;
+      int kb = tc.kb0 + ((tc.m_tile - tc.kb0 % tm) % tm + tm) % tm;
+      for (; kb < tc.kb1; kb += tm) {
+        const int r0 = kb * BK + g_part * g_rows;
+        const float *src = op->cs_src + (long long)r0 * op->Nc + col;
+#pragma unroll 8
+        for (int i = 0; i < g_rows; ++i) {
+          if (r0 + i < op->Kc) {
+            // plain loads: in a schedule the operand may have been written earlier in the same launch
+            const float4 v = *reinterpret_cast<const float4 *>(src + (long long)i * op->Nc);
+            csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w;
+          }
+        }
+      }
+      // Nc is a multiple of four (TMA row pitch), so the group is inside the matrix as a whole
+      atomicAdd(op->colsum + col, csum.x);
+      atomicAdd(op->colsum + col + 1, csum.y);
+      atomicAdd(op->colsum + col + 2, csum.z);
+      atomicAdd(op->colsum + col + 3, csum.w);
+    }
+    return true;
+  }
+
   for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
     const int s = it % R::NST;
     const uint32_t ph = (it / R::NST) & 1u;
     int okl = 1;
-    // a stage these warps rewrite is on the MMA's critical path: no back-off while waiting for it
-    if (lane == 0)
-      okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s, rewrites ? 0 : 64);
+    const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
+    // TF32 mode: a k-block whose column sums belong to another tile row is none of these warps' business
+    // (the MMA lane arrives on empty[s] for them). They do not even watch it land: a watcher that fell two
+    // ring revolutions behind could not tell the phases of a barrier apart by parity. For the k-blocks they
+    // do sum, the MMA lane's running count says when the block has landed; the barrier wait behind it then
+    // passes at once (its phase cannot advance before these warps arrive on empty[s]) and orders the reads.
+    if (!rewrites && !cs_kb) continue;
+    if (lane == 0) {
+      if (!rewrites) okl = wait_landed(it + 1u, ctrl, p, op->op_index, s) ? 1 : 0;
+      if (okl) okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
+    }
     ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
     if (!ok) break;
     uint8_t *stage = ring_ptr + s * R::STAGE_STRIDE;
@@ -108,7 +159,6 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     // An MN-major B block is walked by (column group, k-row) so that the thread that sums a
     // column is also the one that rewrites it in 3xTF32 mode (no cross-thread hazard).
     // TMA zero-fills rows and columns outside the matrix, so no guards are needed.
-    const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
     const bool walk_b = op->b_mn && (X3 || cs_kb || xmode == 3);
     if (xmode == 2) {
       // row x of the A block: eight 16-byte chunks, chunk j at physical position j ^ (x & 7)
@@ -184,7 +234,8 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     __syncwarp();
     if (lane == 0) {
       if (rewrites) mbar_arrive(smem_u32(&ctrl->ready[s]));
-      mbar_arrive(smem_u32(&ctrl->empty[s]));
+      // a stage these warps only watched is released by the MMA lane on their behalf
+      if (rewrites || cs_kb) mbar_arrive(smem_u32(&ctrl->empty[s]));
     }
   }
   if (!ok) return false;
@@ -583,6 +634,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       flash::attn_init_barriers(fc + flash::F_BWD_KV, flash::Cfg<flash::F_BWD_KV>::NCW);
     }
     ctrl->abort = 0;
+    ctrl->landed = 0u;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -716,9 +768,16 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const uint64_t hiB = op->b_mn ? smem_desc_hi(4096, 512, 1) : smem_desc_hi(16, 1024, 2);
       const uint32_t stepA = op->a_mn ? 1024u : 32u;
       const uint32_t stepB = op->b_mn ? 1024u : 32u;
-      // MEGA: an op that needs no operand transform leaves the transform warps' share of empty[s] to us
-      const bool stand_in = MEGA && !op->xform;
+      // The transform warps' share of empty[s] is left to us wherever they have nothing to do with a stage:
+      // in the step kernel for a whole op that needs no operand transform, and in TF32 mode for every k-block
+      // whose column sums belong to another tile row (they only watch those stages go by: a stage must not
+      // wait for a sleeping watcher before it can be refilled).
       const bool via_ready = X3 || op->xent_mode >= 2;  // the transform warps hand the stage over
+      const bool xf_counted = MEGA || p.xform_active != 0;
+      const bool xf_walks = MEGA ? (op->xform != 0) : (p.xform_active != 0);
+      const bool has_cs = (op->colsum != nullptr) && op->b_mn;
+      const bool cs_spread = has_cs && op->colsum_spread != 0;
+      const bool cs_tile = has_cs && (cs_spread || tc.m_tile == 0);
 
       for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const int s = it % NST;
@@ -734,6 +793,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
+          *reinterpret_cast<volatile uint32_t *>(&ctrl->landed) = it + 1u;
           const uint32_t a_addr = ring + s * STAGE_STRIDE;
           const uint32_t b_addr = a_addr + A_TILE_BYTES;
 #pragma unroll
@@ -752,7 +812,8 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             }
           }
           mma_commit(smem_u32(&ctrl->empty[s]));  // frees the stage once these MMAs have read it
-          if (stand_in) mbar_arrive_cnt(smem_u32(&ctrl->empty[s]), NUM_XFORM_WARPS);
+          const bool xf_kb = xf_walks && (via_ready || (cs_tile && !cs_spread));
+          if (xf_counted && !xf_kb) mbar_arrive_cnt(smem_u32(&ctrl->empty[s]), NUM_XFORM_WARPS);
         }
         __syncwarp();
       }
@@ -997,6 +1058,7 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
       op->Mc = d.K; op->Nc = d.N; op->Kc = d.M; op->a_mn = 1; op->b_mn = 1;
       op->colsum = d.out_bias;
       op->colsum_spread = (d.out_bias && d.opts.cta_pair != 2) ? 1 : 0;
+      op->cs_src = d.b;
       break;
     default:
       return GPT2L_ERR_BAD_ARG;

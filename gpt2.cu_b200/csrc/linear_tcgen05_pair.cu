@@ -85,6 +85,9 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
   const int pair_id = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
   const bool xform = p.xform_active != 0;
+  // TF32 launches without an operand transform: no CTA looks at its own ring, so the loads of both CTAs
+  // complete directly on the leader's full[s] and the relay hop disappears
+  const bool direct = !X3 && !xform;
 
   if (tid == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
@@ -154,25 +157,48 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
         if (!ok) break;
         if (lane == 0) {
-          const uint32_t bar = smem_u32(&ctrl->full[s]);
           const uint32_t a_dst = ring + s * STAGE_STRIDE;
           const uint32_t b_dst = a_dst + A_TILE_BYTES;
-          mbar_arrive_expect_tx(bar, tx_bytes);
           const int k0 = kb * BK;
-          if (!a_mn) {
-            tma_load_2d(a_dst, &op->tmA, bar, k0, m0);
-          } else if (op->a_3d) {
-            tma_load_3d(a_dst, &op->tmA, bar, 0, k0, m0 >> 5);
-          } else {
+          if (direct) {
+            // both CTAs' loads of this k-block complete on the leader's full[s]: the leader arms it for
+            // the bytes of both (the peer's bytes may land first: the transaction count may run negative
+            // inside a phase, which cannot complete before the leader's arrival)
+            const uint32_t bar = mapa_cluster(smem_u32(&ctrl->full[s]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&ctrl->full[s]), 2u * tx_bytes);
+            if (!a_mn) {
+              tma_load_2d_pair(a_dst, &op->tmA, bar, k0, m0);
+            } else if (op->a_3d) {
+              tma_load_3d_pair(a_dst, &op->tmA, bar, 0, k0, m0 >> 5);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + c * 4096, &op->tmA, bar, m0 + c * 32, k0);
-          }
-          if (!b_mn) {
-            tma_load_2d(b_dst, &op->tmB, bar, k0, n0);
-          } else if (op->b_3d) {
-            tma_load_3d(b_dst, &op->tmB, bar, 0, k0, n0 >> 5);
+              for (int c = 0; c < BM / 32; ++c) tma_load_2d_pair(a_dst + c * 4096, &op->tmA, bar, m0 + c * 32, k0);
+            }
+            if (!b_mn) {
+              tma_load_2d_pair(b_dst, &op->tmB, bar, k0, n0);
+            } else if (op->b_3d) {
+              tma_load_3d_pair(b_dst, &op->tmB, bar, 0, k0, n0 >> 5);
+            } else {
+              for (int c = 0; c < bh / 32; ++c) tma_load_2d_pair(b_dst + c * 4096, &op->tmB, bar, n0 + c * 32, k0);
+            }
           } else {
-            for (int c = 0; c < bh / 32; ++c) tma_load_2d(b_dst + c * 4096, &op->tmB, bar, n0 + c * 32, k0);
+            const uint32_t bar = smem_u32(&ctrl->full[s]);
+            mbar_arrive_expect_tx(bar, tx_bytes);
+            if (!a_mn) {
+              tma_load_2d(a_dst, &op->tmA, bar, k0, m0);
+            } else if (op->a_3d) {
+              tma_load_3d(a_dst, &op->tmA, bar, 0, k0, m0 >> 5);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / 32; ++c) tma_load_2d(a_dst + c * 4096, &op->tmA, bar, m0 + c * 32, k0);
+            }
+            if (!b_mn) {
+              tma_load_2d(b_dst, &op->tmB, bar, k0, n0);
+            } else if (op->b_3d) {
+              tma_load_3d(b_dst, &op->tmB, bar, 0, k0, n0 >> 5);
+            } else {
+              for (int c = 0; c < bh / 32; ++c) tma_load_2d(b_dst + c * 4096, &op->tmB, bar, n0 + c * 32, k0);
+            }
           }
         }
         __syncwarp();
@@ -212,7 +238,7 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
           // TF32: our own ring (full) and the peer's ring (ready <- its relay).
           // 3xTF32: ready counts the transform warps of both CTAs, which implies both rings landed.
           if (!X3) okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
-          if (okl)
+          if (okl && !direct)
             okl = wait_bar_cluster(smem_u32(&ctrl->ready[s]), ph, ctrl, p, SITE_SMEM_READY, op->op_index, s);
         }
         ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
@@ -254,7 +280,7 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
   } else if (warp == 1) {
     // =============================== relay (peer CTA, TF32 mode) ===============================
     // tells the leader that this CTA's ring holds the k-block
-    if (!X3) {
+    if (!X3 && !direct) {
       int cursor = 0;
       uint32_t it = 0;
       bool ok = true;

@@ -275,6 +275,7 @@ gpt2l_schedule *schedule_build(const std::vector<OpSpec> &specs, int grid_limit,
       // the forward form of a weight gradient: the B operand is still g_out, its column sums are g_b
       g.colsum = specs[i].gemm.out_bias;
       g.colsum_spread = g.colsum ? 1 : 0;
+      g.cs_src = specs[i].gemm.b;
       g.xform = (s->plan.any_3x || g.colsum || g.xent_mode >= 2) ? 1 : 0;
     }
     ws_bytes += op_workspace_bytes(g);

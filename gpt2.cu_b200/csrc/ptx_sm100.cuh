@@ -92,6 +92,25 @@ __device__ __forceinline__ void tma_load_5d(uint32_t smem_dst, const CUtensorMap
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(v), "r"(bar)
       : "memory");
 }
+// The same loads issued by either CTA of a pair (cta_group::2): the mbarrier may live in the peer CTA's
+// shared memory (a cluster address from mapa_cluster), so both CTAs' loads of one k-block can complete
+// on ONE barrier of the leader. No multicast: each load lands in the issuing CTA's shared memory only.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap *map, uint32_t cluster_bar,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap *map, uint32_t cluster_bar,
+                                                 int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(cluster_bar)
+      : "memory");
+}
 // ---------------- TMA stores (shared -> global, bulk-group completion) ----------------
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
