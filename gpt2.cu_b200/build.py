@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libgpt2_linear.so")
 SOURCES = ["linear_tcgen05.cu", "linear_tcgen05_pair.cu", "linear_simt.cu", "api.cu", "megakernel.cu", "step_schedule.cu", "noalloc.cu", "layers.cu", "attention_gemm.cu", "attention_flash.cu", "attention_api.cu", "model.cu"]
-HEADERS = ["linear_internal.h", "ptx_sm100.cuh", "kernel_common.cuh", "layers.h", "step_rowops.cuh", "schedule_internal.h", "model_internal.h",
+HEADERS = ["linear_internal.h", "ptx_sm100.cuh", "kernel_common.cuh", "epilogue.cuh", "attention_flash.cuh", "layers.h", "step_rowops.cuh", "schedule_internal.h", "model_internal.h",
            os.path.join(ROOT, "include", "gpt2_model.h"), os.path.join(ROOT, "include", "gpt2_linear.h")]
 
 NVCC_FLAGS = [

@@ -190,6 +190,13 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   }
   GemmDesc dd = d;
   dd.out_bias = fused_bias;
+  // CTA pairs when the caller leaves the choice open (cta_pair = 0): 256 x 256 tiles stage a third less
+  // operand data per flop, which pays on the vocabulary-wide GEMMs (lm_head forward 1142 against 1225 us,
+  // backward_input 982 / 1011, backward_weight 982 / 1035) and not on the K = 768 layers, whose short tiles
+  // lose more to the pair's hand-shakes than they gain (attn_proj forward 47.6 against 42.4 us).
+  if (dd.opts.cta_pair == 0 && dd.opts.mode == GPT2L_MODE_TF32 && d.N >= 8192 && !dd.opts.xent_lse &&
+      ctx->max_pairs >= ctx->num_sms / 2)
+    dd.opts.cta_pair = 2;
   GemmOp op;
   // Wide weight gradients (lm_head: N = 50304 against K = 768): the tensor core reads an MN-major A
   // operand about 20 % slower than a K-major one, and here A = in^T is tiny next to the GEMM. So
@@ -217,7 +224,7 @@ static int run_gemm(GemmDesc &d, cudaStream_t st) {
   if (err) return err;
   if (transposed_a) {  // the B operand is still g_out: its column sums are g_b
     op.colsum = fused_bias;
-    op.colsum_spread = (fused_bias && !op.pair) ? 1 : 0;
+    op.colsum_spread = fused_bias ? 1 : 0;
     op.cs_src = d.b;
   }
   if (op.splits > 1) {

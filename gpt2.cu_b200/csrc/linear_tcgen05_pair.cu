@@ -28,6 +28,7 @@
 #include <string.h>
 
 #include "kernel_common.cuh"
+#include "epilogue.cuh"
 
 namespace g2l {
 
@@ -38,29 +39,6 @@ constexpr int P_STAGE_BYTES = A_TILE_BYTES + P_B_TILE_BYTES;      // 32 KiB
 constexpr int P_STAGES_1X = RING_BYTES / P_STAGE_BYTES;           // 6
 constexpr int P_STAGES_3X = RING_BYTES / (2 * P_STAGE_BYTES);     // 3
 static_assert(P_STAGES_1X <= MAX_STAGES, "control block too small");
-
-// wait on a local barrier whose arrivals may come from the peer CTA (cluster-scope acquire)
-__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, Ctrl *ctrl, const LaunchParams &p,
-                                                 int site, int op, int idx, unsigned backoff_ns = 0) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    if (backoff_ns) __nanosleep(backoff_ns);
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((++spins & 127u) == 0) {
-      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
-      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
-        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
-        return false;
-      }
-      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
-        raise_timeout(ctrl, p, site, op, idx, -1, (int)parity);
-        return false;
-      }
-    }
-  }
-}
 
 template <bool X3>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -300,9 +278,9 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
         }
       }
     }
-  } else if (warp < EPI_WARP0) {
+  } else if (warp < EPI_WARP0 && xform) {
     // =============================== operand transform (both CTAs) ===============================
-    if (xform) {
+    {
       const int x = tid - XFORM_WARP0 * 32;  // 0..127
       int cursor = 0;
       uint32_t it = 0;
@@ -392,143 +370,24 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
     }
   } else {
     // =============================== epilogue (both CTAs) ===============================
-    const int q = warp & 3;
-    const uint32_t epi_base = ring + RING_BYTES + (uint32_t)(warp - EPI_WARP0) * 2u * EPI_BUF_BYTES;
-    uint32_t epi_cc = 0;
+    // Warps 6-9 drain the accumulator, each CTA its own 128 rows of the pair's tile, every warp with two
+    // staging boxes (eight warps on it measured slower here than four: lm_head forward 1186 against 1125 us).
+    // Warps 2-5, when there is nothing to transform, sum their tile's share of the bias gradient beside the ring.
+    const bool helper = warp < EPI_WARP0;
+    const uint32_t sbuf = ring + RING_BYTES + (uint32_t)(warp - EPI_WARP0) * 2u * EPI_BUF_BYTES;
     int cursor = 0;
     uint32_t tcount = 0;
     bool ok = true;
     for (int t = pair_id; t < p.total_tiles && ok; t += n_pairs, ++tcount) {
       Tile tc;
       const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
-      const uint32_t as = tcount & 1u;
-      const uint32_t aph = (tcount >> 1) & 1u;
-      int okl = 1;
-      if (lane == 0)
-        okl = wait_bar_cluster(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128);
-      ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-      if (!ok) break;
-      tc_fence_after();
-
-      const int bn = op->bn;
-      const int Mc = op->Mc, Nc = op->Nc;
-      const long long ldc = op->ldc;
       const int m_tile = 2 * tc.m_tile + (int)rank;
-      const bool live = m_tile < op->tiles_m;  // false: this CTA's rows lie outside the matrix
-      const int row0 = m_tile * BM + q * 32;
-      const int row = row0 + lane;
-      const int n0 = tc.n_tile * bn;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + as * MAX_BN;
-      const bool det_split = (op->splits > 1) && !op->atomic_out;
-      const bool add_bias = (op->bias != nullptr) && (tc.split == 0 || det_split);
-      const bool dual = (op->flags & GPT2L_EPI_GELU_DUAL) && op->C2 != nullptr;
-      const int out_tile = m_tile * op->tiles_n + tc.n_tile;
-      float *ws_tile = nullptr;
-      if (det_split && live)
-        ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
-                  (size_t)(q * 32 + lane) * bn;
-
-      if (live && !det_split) {
-        for (int c = 0; c < bn / 32; ++c) {
-          const int nb = n0 + c * 32;
-          if (nb >= Nc || row0 >= Mc) break;  // warp-uniform
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (add_bias && nb + 4 * j < Nc) bv = __ldg(reinterpret_cast<const float4 *>(op->bias + nb) + j);
-            v[4 * j + 0] = __uint_as_float(r[4 * j + 0]) + bv.x;
-            v[4 * j + 1] = __uint_as_float(r[4 * j + 1]) + bv.y;
-            v[4 * j + 2] = __uint_as_float(r[4 * j + 2]) + bv.z;
-            v[4 * j + 3] = __uint_as_float(r[4 * j + 3]) + bv.w;
-          }
-          for (int pass = 0; pass < (dual ? 2 : 1); ++pass, ++epi_cc) {
-            const uint32_t sbuf = epi_base + (epi_cc & 1u) * EPI_BUF_BYTES;
-            if (pass == 1) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
-            }
-            EpiAux ea;
-            if (pass == 0 && op->aux_op && tc.split == 0) { ea.aux = op->aux; ea.op = op->aux_op; }
-            AuxRegs ar;
-            load_aux(ar, ea, ldc, row0, nb, Mc, Nc, lane);
-            store_chunk(v, sbuf, pass == 0 ? op->C : op->C2, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, ea, ar);
-          }
-        }
-      } else if (live) {
-        for (int c = 0; c < bn / 32; ++c) {
-          const int nb = n0 + c * 32;
-          if (nb >= Nc) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          float4 *dst = reinterpret_cast<float4 *>(ws_tile + c * 32);
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-        }
-      }
-      // hand the accumulator pair back: the leader's barrier counts the epilogue warps of both CTAs
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&ctrl->tmem_empty[as]), 0));
-
-      if (det_split && live) {
-        __threadfence();
-        __syncwarp();
-        unsigned old = 0;
-        unsigned *sem = op->ws_sem + (size_t)out_tile * 4 + q;
-        if (lane == 0) old = atom_acq_rel_add(sem, 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == (unsigned)(op->splits - 1)) {
-          __threadfence();
-          if (lane == 0) *sem = 0;
-          const size_t split_stride = (size_t)op->tiles_m * op->tiles_n * (size_t)(BM * bn);
-          const float *p0 = op->ws + (size_t)out_tile * (size_t)(BM * bn) + (size_t)(q * 32 + lane) * bn;
-          if (row < Mc) {
-            for (int c4 = 0; c4 < bn / 4; ++c4) {
-              const int col = n0 + c4 * 4;
-              if (col >= Nc) break;
-              float4 acc = __ldcg(reinterpret_cast<const float4 *>(p0 + c4 * 4));
-              for (int sp = 1; sp < op->splits; ++sp) {
-                const float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + sp * split_stride + c4 * 4));
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-              }
-              float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-              float *dst = op->C + (long long)row * ldc + col;
-              if (col + 4 <= Nc) {
-                if (add_bias) {
-                  const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + col));
-                  vals[0] += bv.x; vals[1] += bv.y; vals[2] += bv.z; vals[3] += bv.w;
-                }
-                *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
-                if (dual)
-                  *reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + col) =
-                      make_float4(gelu_tanh(vals[0]), gelu_tanh(vals[1]), gelu_tanh(vals[2]), gelu_tanh(vals[3]));
-              } else {
-                for (int j = 0; j < 4; ++j)
-                  if (col + j < Nc) {
-                    float v = vals[j] + (add_bias ? __ldg(op->bias + col + j) : 0.f);
-                    dst[j] = v;
-                    if (dual) op->C2[(long long)row * ldc + col + j] = gelu_tanh(v);
-                  }
-              }
-            }
-          }
-        }
-      }
-
-      if (live && (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0)) {
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) {
-          if (op->pub_rb_base >= 0) red_release_add(p.counters + op->pub_rb_base + m_tile, 1u);
-          if (op->pub_op_ctr >= 0) red_release_add(p.counters + op->pub_op_ctr, 1u);
-        }
+      if (helper) {
+        if (!X3 && op->colsum != nullptr && op->colsum_spread && m_tile < op->tiles_m)
+          ok = colsum_global_tile(op, tc, m_tile, tid - XFORM_WARP0 * 32, lane, ctrl, p);
+      } else {
+        ok = epilogue_tile<true>(op, tc, m_tile, tcount, false, 1, 0, 1u, 1u, sbuf, sbuf + EPI_BUF_BYTES, tmem_base, ctrl,
+                                 p, warp, lane);
       }
     }
   }

@@ -106,7 +106,7 @@ int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
   }
   // transform warps: per op in the step kernel, per launch in the pair kernel
   for (auto &g : plan->ops)
-    g.xform = (g.op_kind == OPK_GEMM && (plan->any_3x || (g.colsum != nullptr && g.b_mn) || g.xent_mode >= 2)) ? 1 : 0;
+    g.xform = (g.op_kind == OPK_GEMM && (plan->any_3x || (g.colsum != nullptr && g.b_mn && !g.colsum_spread) || g.xent_mode >= 2)) ? 1 : 0;
   plan->arrivals = plan->pair ? NUM_EPI_WARPS : NUM_WORKER_WARPS;
   const unsigned A = (unsigned)plan->arrivals;
   for (int i = 0; i < n_ops; ++i) {
@@ -276,7 +276,7 @@ gpt2l_schedule *schedule_build(const std::vector<OpSpec> &specs, int grid_limit,
       g.colsum = specs[i].gemm.out_bias;
       g.colsum_spread = g.colsum ? 1 : 0;
       g.cs_src = specs[i].gemm.b;
-      g.xform = (s->plan.any_3x || g.colsum || g.xent_mode >= 2) ? 1 : 0;
+      g.xform = (s->plan.any_3x || g.xent_mode >= 2) ? 1 : 0;  // (the column sums are read beside the ring)
     }
     ws_bytes += op_workspace_bytes(g);
     if (g.splits > 1 && !g.atomic_out) sem_count += (size_t)g.tiles_m * g.tiles_n * 4;
