@@ -1,6 +1,9 @@
 // Per-tile bodies shared by the GEMM kernel, the step kernel and the CTA-pair kernel: the epilogue of one
 // tile by one warp, and the TF32-mode bias gradient read beside the ring.
 #pragma once
+#ifndef G2L_TMEM_FULL_BACKOFF
+#define G2L_TMEM_FULL_BACKOFF 128
+#endif
 
 #include "kernel_common.cuh"
 
@@ -88,8 +91,8 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
   const uint32_t aph = (tcount >> 1) & 1u;
   int okl = 1;
   if (lane == 0)
-    okl = PAIR ? wait_bar_cluster(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128)
-               : wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, 128);
+    okl = PAIR ? wait_bar_cluster(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, G2L_TMEM_FULL_BACKOFF)
+               : wait_bar(smem_u32(&ctrl->tmem_full[as]), aph, ctrl, p, SITE_TMEM_FULL, op->op_index, as, G2L_TMEM_FULL_BACKOFF);
   if (__shfl_sync(0xffffffffu, okl, 0) == 0) return false;
   tc_fence_after();
 
@@ -110,6 +113,7 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
     ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
               (size_t)(q * 32 + lane) * bn;
 
+  bool tma_used = false;
   if (live && !det_split) {
     // ---- registers -> swizzled 32x32 box in shared memory -> coalesced stores (or vector
     // reductions for split-K partials); see store_chunk
@@ -122,6 +126,8 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
       if (op->aux_row) ea.row = op->aux_row + ((long long)tc.bb * op->batch_inner + tc.bh) * Mc;
     }
     const EpiAux none;
+    const bool use_tma = op->epi_tma && ea.op == 0 && op->batch <= 1;
+    tma_used = use_tma;
     const float drow = (ea.row && row0 + lane < Mc) ? __ldg(ea.row + row0 + lane) : 0.f;
     // softmax statistics of this thread's row over the columns this warp drains (base-2 domain)
     const bool stats = op->xent_mode == 1;
@@ -169,8 +175,29 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
         // split-K reduce-adds the split that also adds the bias carries it
         // (a warp with two boxes alternates between them, so a chunk's stores are not held up by the previous
         // chunk's reads of the same box)
-        store_chunk(v, (box++ & 1u) ? sbuf_alt : sbuf, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0,
-                    pass == 0 ? ea : none, ar);
+        const uint32_t bx = (box++ & 1u) ? sbuf_alt : sbuf;
+        if (use_tma) {
+          // the copy engine takes the box from here: no read-back through the load/store unit and no store
+          // instructions, which is what the tensor core's own operand fetches compete with
+          if (lane == 0) {  // the bulk group that read this box last is done reading
+            if (sbuf_alt != sbuf) bulk_wait_read<1>();
+            else bulk_wait_read<0>();
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(bx + lane * 128 + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const CUtensorMap *map = pass == 0 ? &op->tmC : &op->tmC2;
+            if (op->atomic_out) tma_reduce_add_2d(map, bx, nb, row0);
+            else tma_store_2d(map, bx, nb, row0);
+            bulk_commit();
+          }
+        } else {
+          store_chunk(v, bx, cbase, ldc, row0, nb, Mc, Nc, lane, op->atomic_out != 0, pass == 0 ? ea : none, ar);
+        }
       }
     }
     if (stats && row < Mc) {
@@ -251,6 +278,17 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
     }
   }
 
+  if (tma_used && lane == 0) {
+    // the boxes may be rewritten (or the CTA may exit) only after the copy engine has read them; a published
+    // tile must also have landed in global memory
+    if (live && pub != 0u && (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0)) {
+      bulk_wait_all();
+      fence_proxy_async_all();
+    } else {
+      bulk_wait_read<0>();
+    }
+  }
+  __syncwarp();
   // ---- publish: everything this warp stored is visible before the counters move (helpers
   // publish too, so a tile counts NUM_EPI_WARPS or 2 * NUM_EPI_WARPS arrivals: epi_arrivals())
   if (live && pub != 0u && (op->pub_rb_base >= 0 || op->pub_op_ctr >= 0)) {

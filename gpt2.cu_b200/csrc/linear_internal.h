@@ -112,6 +112,7 @@ struct alignas(64) GemmOp {
   CUtensorMap tmB;  // box {32, bn}  (K-major) or {32, 32} (MN-major)
   CUtensorMap tmC;  // output, box {32, 32}: epilogue stores / split-K reduce-adds
   CUtensorMap tmC2; // second output of the GELU dual store
+  int epi_tma;      // 1: the epilogue hands its staged boxes to the copy engine (TMA stores / reduce-adds)
   float *C;
   float *C2;            // gelu(C) when flags & GPT2L_EPI_GELU_DUAL
   const float *aux;     // epilogue operand shaped like C (residual to add / pre-activation for GELU')

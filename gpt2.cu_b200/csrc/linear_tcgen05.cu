@@ -918,6 +918,11 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
   }
   op->atomic_out = (op->splits > 1 && !d.opts.deterministic && !op->C2) ? 1 : 0;
   op->xent_stride = 2 * op->tiles_n;
+  {
+    // (GPT2L_EPI_TMA=0 keeps the boxes on the load/store path: read back and stored by the warps themselves)
+    static const int env_tma = [] { const char *e = getenv("GPT2L_EPI_TMA"); return e ? atoi(e) : 1; }();
+    op->epi_tma = env_tma;
+  }
   if (op->xent_mode >= 2 && op->pair) return GPT2L_ERR_BAD_ARG;  // the pair kernel's transform warps only split
   op->idesc = make_idesc_tf32(op->pair ? 2 * BM : BM, bn, op->a_mn, op->b_mn);
   for (int w = 0; w < MAX_WAITS; ++w) { op->wait_ctr[w] = -1; op->wait_kind[w] = 0; op->wait_expected[w] = 0; }
