@@ -344,7 +344,9 @@ __device__ __noinline__ bool attention_tile_mode(const GemmOp *op, int grb, int 
   ap.tiles[MODE] += 1u;
   if (*reinterpret_cast<volatile int *>(&fc->abort)) return false;
   tc_fence_before();
-  __threadfence();  // the row-work warps' stores, before the rendezvous the publishing warps leave through
+  // the row-work warps' stores, before the rendezvous the publishing warps leave through (the loader and the
+  // MMA issuers stored nothing)
+  if (warp >= XFORM_WARP0) __threadfence();
   if (!cta_sync(ctrl, p, ap, op->op_index, lane)) return false;
   tc_fence_after();
   if (warp >= XFORM_WARP0 && warp < EPI_WARP0 + NUM_EPI_WARPS && lane == 0) {

@@ -386,33 +386,56 @@ gpt2l_schedule *gpt2_schedule_create(const gpt2l_op *ops, int n_ops, int *err) {
     *err = GPT2L_ERR_CUDA;
     return nullptr;
   }
+  // A transpose goes as far up the list as its own producers allow (right behind the last of them, or to
+  // the front): placed directly before its weight gradient it ran when that op's tiles were already
+  // waiting for it, behind whatever long op happened to precede them.
+  auto wide = [&](const GemmDesc &d) {
+    return xt && d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.N >= 8192 && d.N >= 8 * d.K && d.M % 32 == 0;
+  };
+  std::vector<std::vector<size_t>> hoisted(in.size() + 1);  // original position -> wide gradients whose transpose goes there
+  for (size_t i = 0; i < in.size(); ++i) {
+    if (!wide(in[i].gemm)) continue;
+    int last = -1;
+    for (const auto &d : in[i].deps)
+      if (d.producer >= 0 && d.producer < (int)i && d.producer > last) last = d.producer;
+    hoisted[(size_t)(last + 1)].push_back(i);
+  }
   std::vector<OpSpec> out;
-  std::vector<int> where(in.size());
+  std::vector<int> where(in.size()), t_where(in.size(), -1);
+  std::vector<size_t> t_off(in.size(), 0);
   size_t used = 0;
   for (size_t i = 0; i < in.size(); ++i) {
-    OpSpec s = in[i];
-    for (auto &d : s.deps) d.producer = (d.producer >= 0 && d.producer < (int)i) ? where[d.producer] : -1;
-    const GemmDesc d = s.gemm;
-    if (xt && d.kind == GPT2L_OP_BACKWARD_WEIGHT && d.N >= 8192 && d.N >= 8 * d.K && d.M % 32 == 0) {
+    for (size_t w : hoisted[i]) {
+      const GemmDesc d = in[w].gemm;
       OpSpec t;
       t.kind = OPK_TRANSPOSE;
       t.rows = d.M;
       t.rows_per_tile = BM;
-      t.layer = s.layer;
+      t.layer = in[w].layer;
       memset(&t.ra, 0, sizeof(t.ra));
       t.ra.in0 = d.a; t.ra.out0 = xt + used; t.ra.i0 = d.M; t.ra.i1 = d.K;
-      t.deps = s.deps;  // the activations' producers
-      for (auto &dd : t.deps) dd.kind = GPT2L_DEP_WHOLE_OP;
+      t.deps = in[w].deps;  // the activations' producers, all above this position
+      for (auto &dd : t.deps) {
+        dd.producer = (dd.producer >= 0 && dd.producer < (int)w) ? where[dd.producer] : -1;
+        dd.kind = GPT2L_DEP_WHOLE_OP;
+      }
+      t_where[w] = (int)out.size();
+      t_off[w] = used;
+      used += (size_t)d.M * d.K;
       out.push_back(t);
+    }
+    OpSpec s = in[i];
+    for (auto &d : s.deps) d.producer = (d.producer >= 0 && d.producer < (int)i) ? where[d.producer] : -1;
+    const GemmDesc d = s.gemm;
+    if (wide(d)) {
       s.gemm.kind = GPT2L_OP_FORWARD;
       s.gemm.M = d.K;  // output rows
       s.gemm.K = d.M;  // reduction
-      s.gemm.a = xt + used;
+      s.gemm.a = xt + t_off[i];
       s.gemm.bias = nullptr;
       s.gemm.opts.flags = 0;
       s.transposed_a = true;
-      s.deps.push_back({(int)out.size() - 1, GPT2L_DEP_WHOLE_OP});
-      used += (size_t)d.M * d.K;
+      s.deps.push_back({t_where[i], GPT2L_DEP_WHOLE_OP});
     }
     where[i] = (int)out.size();
     out.push_back(s);

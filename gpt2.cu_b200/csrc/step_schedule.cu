@@ -267,6 +267,13 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     s.ra.in0 = res; s.ra.in1 = P + m->off_lnf_w; s.ra.in2 = P + m->off_lnf_b;
     s.ra.out0 = m->lnf; s.ra.out1 = m->lnf_mean; s.ra.out2 = m->lnf_rstd; s.ra.i0 = M; s.ra.i1 = C;
     b.emit(s, {{res, ROW, false}}, {{m->lnf, ROW, false}});
+    if (wide_head) {
+      // the lm_head's weight gradient reads these activations K-major: the transposed copy is made here, long
+      // before that op's tiles come up, so that they never wait for it
+      OpSpec t = row_spec(OPK_TRANSPOSE, M, BM, L);
+      t.ra.in0 = m->lnf; t.ra.out0 = st->xt; t.ra.i0 = M; t.ra.i1 = C;
+      b.emit(t, {{m->lnf, ROW, false}}, {{st->xt, WHOLE, false}});
+    }
   }
   gpt2_linear_opts oh = o, ohw = ow;  // the lm_head's backward GEMMs
   if (m->xent_path) {
@@ -323,9 +330,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
   if (wide_head) {
     // the weight gradient of the lm_head reads its activations K-major: one transposed copy, then the
     // product in the forward form g_wte[C][Vp] = lnf^T[C][M] . dlogits[M][Vp]
-    OpSpec t = row_spec(OPK_TRANSPOSE, M, BM, L);
-    t.ra.in0 = m->lnf; t.ra.out0 = st->xt; t.ra.i0 = M; t.ra.i1 = C;
-    b.emit(t, {{m->lnf, ROW, false}}, {{st->xt, WHOLE, false}});
+    // (the transposed copy was made right behind the final layernorm, see above)
     OpSpec g = gemm_spec(GPT2L_OP_FORWARD, C, M, Vp, G + m->off_wte, nullptr, st->xt, m->logits, nullptr, ohw, L);
     g.transposed_a = true;
     b.emit(g, {{st->xt, WHOLE, false}, {m->logits, WHOLE, false}, {m->xlse, WHOLE, false}}, {{G + m->off_wte, WHOLE, false}});
