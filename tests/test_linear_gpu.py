@@ -311,3 +311,33 @@ def test_linearity_at_full_size(gpu):
     rel = (lhs - outs[2]).abs().max().item() / outs[2].abs().max().item()
     assert rel <= 1e-5, rel
     assert torch.equal(outs[3], b.expand(M, N))  # x = 0 leaves exactly the bias
+
+
+def test_epilogue_on_the_load_store_path_gives_the_same_results(gpu, orc):
+    """GPT2L_EPI_TMA=0 keeps the epilogue's staged boxes on the load/store path (read back and stored by the
+    warps) instead of handing them to the copy engine. The switch is read once per process, so the three
+    calls run in a child process with it set; ragged and aligned shapes, plain and split-K."""
+    import os
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    code = r"""
+import os, sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import __graft_entry__ as ge
+import test_linear_gpu as t
+g = ge.load_package(); g.init(0)
+orc = ge.load_oracle()
+for (M, K, N), sk in (((256, 768, 768), 0), ((129, 36, 68), 0), ((384, 96, 320), 3), ((256, 768, 50304), 0)):
+    x, w, b, dy = t.seeded(M, K, N, seed=5)
+    for pair in (1, 2):
+        outs = t.run_all(g, x, w, b, dy, 0, split_k=sk, cta_pair=pair)
+        t.check_all(orc, outs, x, w, b, dy, t.TIGHT[0])
+print("ok")
+"""
+    env = dict(os.environ, GPT2L_EPI_TMA="0")
+    res = subprocess.run([sys.executable, "-c", code, ROOT], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and res.stdout.strip().endswith("ok"), res.stdout[-2000:] + res.stderr[-2000:]
