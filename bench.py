@@ -217,9 +217,9 @@ def workload_config(args, rows=M_ROWS):
 # our arm
 # ------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over the
-# 15 launches of one step: the ncu capture of the half-size set (4096 rows: 246.1 MB per launch against
-# 244.2 MB algorithmic, 1.008x) carried to 8192 rows by that ratio (452.5 MB algorithmic per launch).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 456.0e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
+# 15 launches of one step: the ncu capture of the half-size set (4096 rows: 252.2 MB per launch against
+# 244.2 MB algorithmic, 1.033x) carried to 8192 rows by that ratio (452.5 MB algorithmic per launch).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 467.0e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
 
 
 def init_nccl(torch, dist, local_rank):
@@ -379,7 +379,7 @@ def run_ours(args):
         "frac_burst": (achieved / burst) if achieved else None,
         "frac_sustained": (achieved / sustained) if achieved else None,
         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-        "kernel": "gpt2_linear_tcgen05_kernel", "launches_timed": n_launch,
+        "kernel": "gpt2_linear_tcgen05_kernel (12 layer GEMMs) + gpt2_linear_tcgen05_pair_kernel (3 lm_head GEMMs)", "launches_timed": n_launch,
         "avg_launch_ms": kernel_ms / n_launch if n_launch else None,
         "flops_per_launch": flops_step / 15.0,
         "per_gemm": per_gemm,
