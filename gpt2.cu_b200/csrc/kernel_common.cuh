@@ -24,7 +24,6 @@ struct Ctrl {
   uint64_t cta_bar;  // step kernel: rendezvous of every warp of the CTA (attention tiles)
   uint32_t tmem_base;
   int abort;
-  uint32_t landed;  // k-blocks (a CTA-wide running count) the MMA lane has seen land
 };
 constexpr int CTRL_MAIN_BYTES = 256;  // the attention tiles' three barrier sets follow at this offset
 static_assert(sizeof(Ctrl) <= CTRL_MAIN_BYTES, "control block too large");
@@ -129,30 +128,6 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl *ct
       }
       if (globaltimer_ns() - t0 > p.wait_limit_ns) {
         raise_timeout(ctrl, p, site, op, idx, -1, (int)parity);
-        return false;
-      }
-    }
-  }
-}
-
-// Bounded poll until the MMA lane has seen `count` k-blocks land (Ctrl::landed is monotonic, so a waiter may
-// come arbitrarily late or early: an mbarrier parity could not tell a phase from the one two later).
-__device__ __forceinline__ bool wait_landed(uint32_t count, Ctrl *ctrl, const LaunchParams &p, int op, int idx) {
-  volatile uint32_t *w = &ctrl->landed;
-  if ((int)(*w - count) >= 0) return true;
-  const long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    __nanosleep(32);
-    if ((int)(*w - count) >= 0) return true;
-    if ((++spins & 127u) == 0) {
-      if (*reinterpret_cast<volatile int *>(&ctrl->abort)) return false;
-      if (*reinterpret_cast<volatile int *>(&p.status->status) != 0) {
-        *reinterpret_cast<volatile int *>(&ctrl->abort) = 1;
-        return false;
-      }
-      if (globaltimer_ns() - t0 > p.wait_limit_ns) {
-        raise_timeout(ctrl, p, SITE_SMEM_FULL, op, idx, (int)*w, (int)count);
         return false;
       }
     }

@@ -87,9 +87,10 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
   float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);
   const int stage_f4 = (A_TILE_BYTES + bn * BK * 4) >> 4;
 
-  if (!rewrites && (spread || !has_cs)) {
+  if (!rewrites) {
     // TF32 mode: the stages need nothing from these warps (the MMA lane arrives on empty[s] in their place);
-    // the column sums, if any, do not go through the ring (colsum_global_tile)
+    // the column sums, if any, do not go through the ring (colsum_global_tile; every weight gradient is planned
+    // with its column sums spread over the tile rows)
     it += (uint32_t)(tc.kb1 - tc.kb0);
     return has_cs ? colsum_global_tile(op, tc, tc.m_tile, x, lane, ctrl, p) : true;
   }
@@ -99,16 +100,8 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     const uint32_t ph = (it / R::NST) & 1u;
     int okl = 1;
     const bool cs_kb = do_colsum && (!spread || (kb % op->tiles_m) == tc.m_tile);
-    // TF32 mode: a k-block whose column sums belong to another tile row is none of these warps' business
-    // (the MMA lane arrives on empty[s] for them). They do not even watch it land: a watcher that fell two
-    // ring revolutions behind could not tell the phases of a barrier apart by parity. For the k-blocks they
-    // do sum, the MMA lane's running count says when the block has landed; the barrier wait behind it then
-    // passes at once (its phase cannot advance before these warps arrive on empty[s]) and orders the reads.
-    if (!rewrites && !cs_kb) continue;
-    if (lane == 0) {
-      if (!rewrites) okl = wait_landed(it + 1u, ctrl, p, op->op_index, s) ? 1 : 0;
-      if (okl) okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
-    }
+    // (these warps rewrite or sum every stage here, so each is on the ring's critical path: no back-off)
+    if (lane == 0) okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
     ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
     if (!ok) break;
     uint8_t *stage = ring_ptr + s * R::STAGE_STRIDE;
@@ -199,8 +192,7 @@ __device__ __forceinline__ bool xform_tile(const GemmOp *op, const Tile &tc, uin
     __syncwarp();
     if (lane == 0) {
       if (rewrites) mbar_arrive(smem_u32(&ctrl->ready[s]));
-      // a stage these warps only watched is released by the MMA lane on their behalf
-      if (rewrites || cs_kb) mbar_arrive(smem_u32(&ctrl->empty[s]));
+      mbar_arrive(smem_u32(&ctrl->empty[s]));
     }
   }
   if (!ok) return false;
@@ -424,7 +416,6 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       flash::attn_init_barriers(fc + flash::F_BWD_KV, flash::Cfg<flash::F_BWD_KV>::NCW);
     }
     ctrl->abort = 0;
-    ctrl->landed = 0u;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -558,16 +549,13 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
       const uint64_t hiB = op->b_mn ? smem_desc_hi(4096, 512, 1) : smem_desc_hi(16, 1024, 2);
       const uint32_t stepA = op->a_mn ? 1024u : 32u;
       const uint32_t stepB = op->b_mn ? 1024u : 32u;
-      // The transform warps' share of empty[s] is left to us wherever they have nothing to do with a stage:
-      // in the step kernel for a whole op that needs no operand transform, and in TF32 mode for every k-block
-      // whose column sums belong to another tile row (they only watch those stages go by: a stage must not
-      // wait for a sleeping watcher before it can be refilled).
+      // The transform warps' share of empty[s] is left to us wherever they do not touch the stages: in the step
+      // kernel for every op that needs no operand transform, and in any TF32 launch whose barriers count them
+      // (they rewrite stages only in 3xTF32 mode and for the fused cross-entropy; the bias gradient is read
+      // beside the ring).
       const bool via_ready = X3 || op->xent_mode >= 2;  // the transform warps hand the stage over
       const bool xf_counted = MEGA || p.xform_active != 0;
-      const bool xf_walks = MEGA ? (op->xform != 0) : (p.xform_active != 0);
-      const bool has_cs = (op->colsum != nullptr) && op->b_mn;
-      const bool cs_spread = has_cs && op->colsum_spread != 0;
-      const bool cs_tile = has_cs && (cs_spread || tc.m_tile == 0);
+      const bool stand_in = xf_counted && !((MEGA ? (op->xform != 0) : (p.xform_active != 0)) && via_ready);
 
       for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
         const int s = it % NST;
@@ -583,7 +571,6 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
-          *reinterpret_cast<volatile uint32_t *>(&ctrl->landed) = it + 1u;
           const uint32_t a_addr = ring + s * STAGE_STRIDE;
           const uint32_t b_addr = a_addr + A_TILE_BYTES;
 #pragma unroll
@@ -602,8 +589,7 @@ gpt2_linear_tcgen05_kernel(const __grid_constant__ GemmOp op0, const LaunchParam
             }
           }
           mma_commit(smem_u32(&ctrl->empty[s]));  // frees the stage once these MMAs have read it
-          const bool xf_kb = xf_walks && (via_ready || (cs_tile && !cs_spread));
-          if (xf_counted && !xf_kb) mbar_arrive_cnt(smem_u32(&ctrl->empty[s]), NUM_XFORM_WARPS);
+          if (stand_in) mbar_arrive_cnt(smem_u32(&ctrl->empty[s]), NUM_XFORM_WARPS);
         }
         __syncwarp();
       }
@@ -1116,7 +1102,8 @@ int launch_list(DeviceCtx *ctx, const GemmOp *d_ops, int n_ops, int total_tiles,
   p.host_flag = ctx ? ctx->d_flag : nullptr;
   p.counters = d_counters;
   p.wait_limit_ns = wait_limit_ns > 0 ? wait_limit_ns : default_wait_limit_ns();
-  p.xform_active = (any_3x || any_colsum) ? 1 : 0;
+  p.xform_active = any_3x ? 1 : 0;  // (read by the pair kernel only; TF32 column sums are read beside the ring)
+  (void)any_colsum;
   for (int i = 0; i < 7; ++i) p.adam[i] = adam ? adam[i] : 0.f;
   p.fmaps = fmaps;
   p.prof = prof;

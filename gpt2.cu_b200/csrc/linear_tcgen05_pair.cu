@@ -1,19 +1,22 @@
 // The CTA-pair variant of the GEMM kernel: a cluster of two CTAs computes one 256 x bn tile with
 // tcgen05.mma.cta_group::2.
 //
-// Why: with fp32 operands a 128 x 256 tile needs 48 KiB of operands per k-block for 2.1 MFLOP —
-// more than an SM can pull from L2 at full tensor rate. In a pair each CTA stages its own 128 rows
-// of A and only HALF of B (bn/2 columns), 32 KiB per k-block for the same 2.1 MFLOP per CTA; the
-// tensor cores of both SMs read both halves of B through the pair's shared memory. Operand traffic
-// per flop drops by a third and shared-memory read traffic per MMA from 12 KiB to 8 KiB.
+// Why: in a pair each CTA stages its own 128 rows of A and only HALF of B (bn/2 columns), 32 KiB per
+// k-block instead of 48 KiB for the same 2.1 MFLOP per CTA; the tensor cores of both SMs read both halves
+// of B through the pair's shared memory. Operand traffic per flop drops by a third, the ring is six
+// stages deep instead of four, and the epilogue that runs beside the main loop disturbs it less. That
+// pays on the vocabulary-wide GEMMs; short tiles lose more to the cluster's hand-shakes than they gain.
 //
 // Protocol (rank 0 = leader, the only CTA that issues MMAs):
-//   * every TMA load is an ordinary local load (no multicast, no remote barrier): CTA r loads A
-//     rows [256*mp + 128*r, +128) and B columns [n0 + r*bn/2, +bn/2) into its own ring and signals
-//     its own full[s];
-//   * the leader may only issue a k-block when BOTH rings hold it: in TF32 mode warp 1 of CTA 1
-//     relays its full[s] to the leader's ready[s] (one remote arrive); in 3xTF32 mode the transform
-//     warps of both CTAs arrive there after the hi/lo split (eight arrivals);
+//   * no load is multicast: CTA r loads A rows [256*mp + 128*r, +128) and B columns [n0 + r*bn/2, +bn/2)
+//     into its own ring;
+//   * TF32 mode: the loads of BOTH CTAs are issued in the .cta_group::2 form and complete on ONE barrier,
+//     the leader's full[s], which the leader arms for the bytes of both (the peer's bytes may land first:
+//     the transaction count may run negative inside a phase, which cannot complete before the leader's
+//     arrival). The leader issues a k-block when that barrier flips;
+//   * 3xTF32 mode: each CTA's loads complete on its own full[s]; the transform warps of both CTAs split
+//     their stage into hi + lo and arrive on the leader's ready[s] (eight arrivals), which the leader
+//     waits for instead;
 //   * tcgen05.commit (cta_group::2) then arrives on empty[s] of BOTH CTAs (two commits, one per
 //     CTA, each to a plain cluster address) and, after the last k-block, on tmem_full[acc] of both;
 //   * each CTA's epilogue drains its own 128 x bn accumulator and arrives on the LEADER's
@@ -62,17 +65,17 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
   const uint32_t rank = cluster_ctarank();       // 0 = leader
   const int pair_id = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
-  const bool xform = p.xform_active != 0;
-  // TF32 launches without an operand transform: no CTA looks at its own ring, so the loads of both CTAs
-  // complete directly on the leader's full[s] and the relay hop disappears
-  const bool direct = !X3 && !xform;
+  const bool xform = X3 && p.xform_active != 0;  // the transform warps only work in 3xTF32 mode
+  // TF32 launches: no warp looks at its own CTA's ring (the transform warps only work in 3xTF32 mode), so the
+  // loads of both CTAs complete directly on the leader's full[s]
+  const bool direct = !X3;
 
   if (tid == 0) {
     for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), 1);
       mbar_init(smem_u32(&ctrl->empty[s]), 1 + (xform ? NUM_XFORM_WARPS : 0));
-      // leader only: TF32 = the peer's relay; 3xTF32 = the transform warps of both CTAs
-      mbar_init(smem_u32(&ctrl->ready[s]), X3 ? 2 * NUM_XFORM_WARPS : 1);
+      // leader only, 3xTF32 mode: the transform warps of both CTAs
+      mbar_init(smem_u32(&ctrl->ready[s]), 2 * NUM_XFORM_WARPS);
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
@@ -213,8 +216,8 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
         const uint32_t ph = (it / NST) & 1u;
         okl = 1;
         if (lane == 0) {
-          // TF32: our own ring (full) and the peer's ring (ready <- its relay).
-          // 3xTF32: ready counts the transform warps of both CTAs, which implies both rings landed.
+          // TF32: full[s] counts the bytes of both CTAs.
+          // 3xTF32: ready counts the transform warps of both CTAs, which implies both rings landed and were split.
           if (!X3) okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
           if (okl && !direct)
             okl = wait_bar_cluster(smem_u32(&ctrl->ready[s]), ph, ctrl, p, SITE_SMEM_READY, op->op_index, s);
@@ -256,28 +259,7 @@ gpt2_linear_tcgen05_pair_kernel(const __grid_constant__ GemmOp op0, const Launch
       __syncwarp();
     }
   } else if (warp == 1) {
-    // =============================== relay (peer CTA, TF32 mode) ===============================
-    // tells the leader that this CTA's ring holds the k-block
-    if (!X3 && !direct) {
-      int cursor = 0;
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = pair_id; t < p.total_tiles && ok; t += n_pairs) {
-        Tile tc;
-        const GemmOp *op = decode_tile(ops, n_ops, t, cursor, tc);
-        for (int kb = tc.kb0; kb < tc.kb1; ++kb, ++it) {
-          const int s = it % NST;
-          const uint32_t ph = (it / NST) & 1u;
-          int okl = 1;
-          if (lane == 0) {
-            okl = wait_bar(smem_u32(&ctrl->full[s]), ph, ctrl, p, SITE_SMEM_FULL, op->op_index, s);
-            if (okl) mbar_arrive_cluster_relaxed(mapa_cluster(smem_u32(&ctrl->ready[s]), 0));
-          }
-          ok = __shfl_sync(0xffffffffu, okl, 0) != 0;
-          if (!ok) break;
-        }
-      }
-    }
+    // (the peer CTA issues no MMAs: its warp 1 only allocates and frees tensor memory)
   } else if (warp < EPI_WARP0 && xform) {
     // =============================== operand transform (both CTAs) ===============================
     {
