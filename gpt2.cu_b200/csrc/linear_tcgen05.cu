@@ -903,6 +903,12 @@ int plan_op(const GemmDesc &d, int num_sms, GemmOp *op) {
     if (g > op->tiles_dec) g = op->tiles_dec;
     const int bands = ceil_div(op->tiles_dec, g);
     op->band_m = ceil_div(op->tiles_dec, bands);  // balanced bands
+    // A B operand that stays in L2 anyway (the layers' weights: 2 - 9 MB) needs no bands: its tiles are walked
+    // one tile row after the other, so that row blocks complete in order from the first wave on. Inside a
+    // schedule a consumer's first tiles then find their row blocks done long before the producer's last wave;
+    // with the row index fastest a row block is complete only when nearly the whole op is.
+    static const int env_rows = [] { const char *e = getenv("GPT2L_ROW_MAJOR_TILES"); return e ? atoi(e) : 1; }();
+    if (env_rows && op->splits == 1 && (double)op->Kc * (double)op->Nc * 4.0 <= 24.0 * 1024 * 1024) op->band_m = 1;
   }
   op->atomic_out = (op->splits > 1 && !d.opts.deterministic && !op->C2) ? 1 : 0;
   op->xent_stride = 2 * op->tiles_n;

@@ -147,100 +147,93 @@ __device__ __forceinline__ void row_ln_fwd(const GemmOp *op, int tile, int w8, i
 }
 
 // ---- layernorm backward -------------------------------------------------------------------------------
-// g_in[row] += backward of g_out[row]; the column sums for g_w / g_b of the tile's rows are gathered in
-// shared memory (`acc`, 2 * C floats, stored as four interleaved planes so that the 32 lanes of a warp hit
-// 32 different banks) and leave the CTA as one atomicAdd per column per tile.
+// g_in[row] += backward of g_out[row]. A warp takes every eighth row of the tile and keeps the column sums
+// for g_w / g_b of its rows in registers; after the tile the eight warps' sums meet in shared memory (`acc`,
+// 8 x C floats per pass, plain stores) and leave the CTA as one atomicAdd per column per tile. (Shared-memory
+// float atomics per row were tried first: they are compare-and-swap loops, and with 48 of them per lane and
+// row a 128-row tile took 160 us.)
 template <int K4>
 __device__ __forceinline__ bool row_ln_bwd(const GemmOp *op, int tile, int w8, int lane, float *acc, RowSync &rs_,
                                            const LaunchParams &p) {
   const RowArgs &a = op->ra;
-  const int M = a.i0, C = a.i1, Cq = C >> 2;
+  const int M = a.i0, C = a.i1;
   const int wtid = w8 * 32 + lane;
-  for (int i = wtid; i < 2 * C; i += NUM_WORKER_WARPS * 32) acc[i] = 0.f;
-  if (!rs_.sync(p, op->op_index, lane)) return false;
-  float *sw = acc, *sb = acc + C;
   const int r0 = tile * op->rows_per_tile;
   const int r1 = min(M, r0 + op->rows_per_tile);
-  constexpr int R = K4 <= 6 ? 2 : 1;  // rows in flight per warp: eight warps per SM have to cover the latency alone
-  for (int rowb = r0 + w8; rowb < r1; rowb += R * NUM_WORKER_WARPS) {
-    float4 nh[R][K4], g[R][K4];
-    float mu[R], rs[R], s1[R], s2[R];
+  float4 dw[K4], db[K4];
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
-      const int row = rowb + j * NUM_WORKER_WARPS;
-      const bool live = row < r1;
-      const float *x = a.in1 + (long long)row * C;
-      const float *go = a.in0 + (long long)row * C;
-      mu[j] = live ? a.in3[row] : 0.f;
-      rs[j] = live ? a.in4[row] : 0.f;
+  for (int k = 0; k < K4; ++k) dw[k] = db[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int row = r0 + w8; row < r1; row += NUM_WORKER_WARPS) {
+    float4 nh[K4], g[K4], o[K4];
+    const float *x = a.in1 + (long long)row * C;
+    const float *go = a.in0 + (long long)row * C;
+    float *gi = a.out0 + (long long)row * C;
+    const float mu = a.in3[row], rs = a.in4[row];
+    // all three rows in one round trip: the residual gradient this row is added to comes with its inputs
 #pragma unroll
-      for (int k = 0; k < K4; ++k) {
-        const int c = 4 * (lane + 32 * k);
-        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-        nh[j][k] = (live && c < C) ? *reinterpret_cast<const float4 *>(x + c) : zero;   // x for now
-        g[j][k] = (live && c < C) ? *reinterpret_cast<const float4 *>(go + c) : zero;
+    for (int k = 0; k < K4; ++k) {
+      const int c = 4 * (lane + 32 * k);
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      nh[k] = c < C ? *reinterpret_cast<const float4 *>(x + c) : zero;   // x for now
+      g[k] = c < C ? *reinterpret_cast<const float4 *>(go + c) : zero;
+      o[k] = c < C ? *reinterpret_cast<const float4 *>(gi + c) : zero;
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K4; ++k) {
+      const int c = 4 * (lane + 32 * k);
+      if (c < C) {
+        const float4 xv = nh[k];
+        nh[k] = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
+        const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
+        const float4 dn = make_float4(g[k].x * wv.x, g[k].y * wv.y, g[k].z * wv.z, g[k].w * wv.w);
+        s1 += dn.x + dn.y + dn.z + dn.w;
+        s2 += dn.x * nh[k].x + dn.y * nh[k].y + dn.z * nh[k].z + dn.w * nh[k].w;
       }
     }
+    s1 = rw_warp_sum(s1) / C;
+    s2 = rw_warp_sum(s2) / C;
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
-      s1[j] = 0.f;
-      s2[j] = 0.f;
-#pragma unroll
-      for (int k = 0; k < K4; ++k) {
-        const int c = 4 * (lane + 32 * k);
-        if (c < C) {
-          const float4 xv = nh[j][k];
-          nh[j][k] = make_float4((xv.x - mu[j]) * rs[j], (xv.y - mu[j]) * rs[j], (xv.z - mu[j]) * rs[j], (xv.w - mu[j]) * rs[j]);
-          const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
-          const float4 dn = make_float4(g[j][k].x * wv.x, g[j][k].y * wv.y, g[j][k].z * wv.z, g[j][k].w * wv.w);
-          s1[j] += dn.x + dn.y + dn.z + dn.w;
-          s2[j] += dn.x * nh[j][k].x + dn.y * nh[j][k].y + dn.z * nh[j][k].z + dn.w * nh[j][k].w;
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < R; ++j) {
-      s1[j] = rw_warp_sum(s1[j]) / C;
-      s2[j] = rw_warp_sum(s2[j]) / C;
-    }
-#pragma unroll
-    for (int j = 0; j < R; ++j) {
-      const int row = rowb + j * NUM_WORKER_WARPS;
-      if (row >= r1) continue;
-      float *gi = a.out0 + (long long)row * C;
-      float4 o[K4];
-#pragma unroll
-      for (int k = 0; k < K4; ++k) {
-        const int c = 4 * (lane + 32 * k);
-        o[k] = c < C ? *reinterpret_cast<float4 *>(gi + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int k = 0; k < K4; ++k) {
-        const int c = 4 * (lane + 32 * k);
-        if (c < C) {
-          const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
-          o[k].x += (g[j][k].x * wv.x - s1[j] - nh[j][k].x * s2[j]) * rs[j];
-          o[k].y += (g[j][k].y * wv.y - s1[j] - nh[j][k].y * s2[j]) * rs[j];
-          o[k].z += (g[j][k].z * wv.z - s1[j] - nh[j][k].z * s2[j]) * rs[j];
-          o[k].w += (g[j][k].w * wv.w - s1[j] - nh[j][k].w * s2[j]) * rs[j];
-          *reinterpret_cast<float4 *>(gi + c) = o[k];
-          const int q = lane + 32 * k;  // column c + i lives at plane i, slot q
-          atomicAdd(sw + q, g[j][k].x * nh[j][k].x); atomicAdd(sw + Cq + q, g[j][k].y * nh[j][k].y);
-          atomicAdd(sw + 2 * Cq + q, g[j][k].z * nh[j][k].z); atomicAdd(sw + 3 * Cq + q, g[j][k].w * nh[j][k].w);
-          atomicAdd(sb + q, g[j][k].x); atomicAdd(sb + Cq + q, g[j][k].y);
-          atomicAdd(sb + 2 * Cq + q, g[j][k].z); atomicAdd(sb + 3 * Cq + q, g[j][k].w);
-        }
+    for (int k = 0; k < K4; ++k) {
+      const int c = 4 * (lane + 32 * k);
+      if (c < C) {
+        const float4 wv = *reinterpret_cast<const float4 *>(a.in2 + c);
+        o[k].x += (g[k].x * wv.x - s1 - nh[k].x * s2) * rs;
+        o[k].y += (g[k].y * wv.y - s1 - nh[k].y * s2) * rs;
+        o[k].z += (g[k].z * wv.z - s1 - nh[k].z * s2) * rs;
+        o[k].w += (g[k].w * wv.w - s1 - nh[k].w * s2) * rs;
+        *reinterpret_cast<float4 *>(gi + c) = o[k];
+        dw[k].x += g[k].x * nh[k].x; dw[k].y += g[k].y * nh[k].y; dw[k].z += g[k].z * nh[k].z; dw[k].w += g[k].w * nh[k].w;
+        db[k].x += g[k].x; db[k].y += g[k].y; db[k].z += g[k].z; db[k].w += g[k].w;
       }
     }
   }
-  if (!rs_.sync(p, op->op_index, lane)) return false;
-  for (int i = wtid; i < C; i += NUM_WORKER_WARPS * 32) {
-    const int c = (i % Cq) * 4 + i / Cq;  // plane i / Cq, slot i % Cq
-    atomicAdd(a.out1 + c, sw[i]);
-    atomicAdd(a.out2 + c, sb[i]);
+  // Two passes (weight, bias) through the 32 KiB of scratch: warp w parks its C sums at acc + slot * C, the 256
+  // threads add the copies of their columns and send one atomic per column. As many warps per round as fit
+  // (all eight up to C = 1024, four at 1280 and 1600).
+  const int per_round = C <= 1024 ? NUM_WORKER_WARPS : (C <= 2048 ? 4 : (C <= 4096 ? 2 : 1));
+  for (int pass = 0; pass < 2; ++pass) {
+    float *dst = pass == 0 ? a.out1 : a.out2;
+    for (int first = 0; first < NUM_WORKER_WARPS; first += per_round) {
+      if (!rs_.sync(p, op->op_index, lane)) return false;  // the scratch is free (everybody has read the last round)
+      if (w8 >= first && w8 < first + per_round) {
+        float4 *mine = reinterpret_cast<float4 *>(acc + (size_t)(w8 - first) * C);
+#pragma unroll
+        for (int k = 0; k < K4; ++k) {
+          const int q = lane + 32 * k;
+          if (4 * q < C) mine[q] = pass == 0 ? dw[k] : db[k];
+        }
+      }
+      if (!rs_.sync(p, op->op_index, lane)) return false;
+      for (int c = wtid; c < C; c += NUM_WORKER_WARPS * 32) {
+        float v = 0.f;
+        for (int w = 0; w < per_round; ++w) v += acc[(size_t)w * C + c];
+        atomicAdd(dst + c, v);
+      }
+    }
   }
-  // the shared-memory accumulators double as the warps' GEMM epilogue boxes: nobody may move on to a
-  // GEMM tile before every warp has read its share
+  // the scratch doubles as the warps' GEMM epilogue boxes: nobody may move on to a GEMM tile before every
+  // warp has read its share
   return rs_.sync(p, op->op_index, lane);
 }
 
