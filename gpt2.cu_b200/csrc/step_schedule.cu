@@ -187,6 +187,13 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
   st->m = m;
   st->with_update = (flags & GPT2_STEP_WITH_UPDATE) ? 1 : 0;
   const bool wide_head = (Vp >= 8192 && Vp >= 8 * C && (M & 3) == 0 && M % 32 == 0);
+  // Rows per layernorm tile. A GEMM's first wave waits for the layernorm tiles of its first row blocks, which
+  // were all handed out at the same moment: short tiles keep that wait short.
+  int ln_rows = 64;
+  if (const char *e = getenv("GPT2_STEP_LN_ROWS")) {
+    const int v = atoi(e);
+    if (v == 8 || v == 16 || v == 32 || v == 64 || v == 128) ln_rows = v;
+  }
   {
     const size_t floats = (size_t)M * C * 2 + (size_t)M * 3 * C + (wide_head ? (size_t)M * C : 0);
     if (cudaMalloc(reinterpret_cast<void **>(&st->scratch), floats * sizeof(float)) != cudaSuccess) {
@@ -227,7 +234,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     const LayerParams &p = m->lp[l];
     LayerActs &a = m->la[l];
     {
-      OpSpec s = row_spec(OPK_LN_FWD, M, BM, l);
+      OpSpec s = row_spec(OPK_LN_FWD, M, ln_rows, l);
       s.ra.in0 = res; s.ra.in1 = P + p.ln1_w; s.ra.in2 = P + p.ln1_b;
       s.ra.out0 = a.ln1; s.ra.out1 = a.ln1_mean; s.ra.out2 = a.ln1_rstd; s.ra.i0 = M; s.ra.i1 = C;
       b.emit(s, {{res, ROW, false}}, {{a.ln1, ROW, false}});
@@ -247,7 +254,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     b.emit(gemm_spec(GPT2L_OP_FORWARD, M, C, C, a.res2, nullptr, a.atty, P + p.proj_w, P + p.proj_b, orr, l),
            {{a.atty, ROW, false}, {res, ROW, false}}, {{a.res2, ROW, false}});
     {
-      OpSpec s = row_spec(OPK_LN_FWD, M, BM, l);
+      OpSpec s = row_spec(OPK_LN_FWD, M, ln_rows, l);
       s.ra.in0 = a.res2; s.ra.in1 = P + p.ln2_w; s.ra.in2 = P + p.ln2_b;
       s.ra.out0 = a.ln2; s.ra.out1 = a.ln2_mean; s.ra.out2 = a.ln2_rstd; s.ra.i0 = M; s.ra.i1 = C;
       b.emit(s, {{a.res2, ROW, false}}, {{a.ln2, ROW, false}});
@@ -263,7 +270,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     res = a.res3;
   }
   {
-    OpSpec s = row_spec(OPK_LN_FWD, M, BM, L);
+    OpSpec s = row_spec(OPK_LN_FWD, M, ln_rows, L);
     s.ra.in0 = res; s.ra.in1 = P + m->off_lnf_w; s.ra.in2 = P + m->off_lnf_b;
     s.ra.out0 = m->lnf; s.ra.out1 = m->lnf_mean; s.ra.out2 = m->lnf_rstd; s.ra.i0 = M; s.ra.i1 = C;
     b.emit(s, {{res, ROW, false}}, {{m->lnf, ROW, false}});
@@ -342,7 +349,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
   std::vector<int> adam_after(L + 2, -1);  // op whose completion makes bucket i's gradients final
   std::vector<std::vector<int>> wgrads(L);
   {
-    OpSpec s = row_spec(OPK_LN_BWD, M, BM, L);
+    OpSpec s = row_spec(OPK_LN_BWD, M, ln_rows, L);
     s.ra.in0 = st->d_ln; s.ra.in1 = res_last; s.ra.in2 = P + m->off_lnf_w; s.ra.in3 = m->lnf_mean; s.ra.in4 = m->lnf_rstd;
     s.ra.out0 = m->dresid; s.ra.out1 = G + m->off_lnf_w; s.ra.out2 = G + m->off_lnf_b; s.ra.i0 = M; s.ra.i1 = C;
     adam_after[L] = b.emit(s, {{st->d_ln, ROW, false}, {res_last, ROW, false}}, {{m->dresid, ROW, false}});
@@ -366,7 +373,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
         gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, 4 * C, G + p.fc_w, G + p.fc_b, a.ln2, m->dbig, nullptr, ow, l),
         {{m->dbig, WHOLE, false}, {a.ln2, WHOLE, false}}, {{G + p.fc_w, WHOLE, false}}));
     {
-      OpSpec s = row_spec(OPK_LN_BWD, M, BM, l);
+      OpSpec s = row_spec(OPK_LN_BWD, M, ln_rows, l);
       s.ra.in0 = st->d_ln; s.ra.in1 = a.res2; s.ra.in2 = P + p.ln2_w; s.ra.in3 = a.ln2_mean; s.ra.in4 = a.ln2_rstd;
       s.ra.out0 = m->dresid; s.ra.out1 = G + p.ln2_w; s.ra.out2 = G + p.ln2_b; s.ra.i0 = M; s.ra.i1 = C;
       b.emit(s, {{st->d_ln, ROW, false}, {a.res2, ROW, false}}, {{m->dresid, ROW, false}});
@@ -395,7 +402,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
         gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, 3 * C, G + p.qkv_w, G + p.qkv_b, a.ln1, st->dqkv, nullptr, ow, l),
         {{st->dqkv, WHOLE, false}, {a.ln1, WHOLE, false}}, {{G + p.qkv_w, WHOLE, false}}));
     {
-      OpSpec s = row_spec(OPK_LN_BWD, M, BM, l);
+      OpSpec s = row_spec(OPK_LN_BWD, M, ln_rows, l);
       s.ra.in0 = st->d_ln; s.ra.in1 = res_in; s.ra.in2 = P + p.ln1_w; s.ra.in3 = a.ln1_mean; s.ra.in4 = a.ln1_rstd;
       s.ra.out0 = m->dresid; s.ra.out1 = G + p.ln1_w; s.ra.out2 = G + p.ln1_b; s.ra.i0 = M; s.ra.i1 = C;
       adam_after[l] = b.emit(s, {{st->d_ln, ROW, false}, {res_in, ROW, false}}, {{m->dresid, ROW, false}});
