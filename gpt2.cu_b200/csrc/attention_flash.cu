@@ -143,4 +143,24 @@ int attention_flash_backward(float *dqkv, float *delta, const float *dout, const
   return launch<F_BWD_KV>(maps_kv, a, st);
 }
 
+// the two backward kernels alone: delta[b][h][t] = rowsum(dout o out) has been computed by the caller
+int attention_flash_backward_core(float *dqkv, const float *delta, const float *dout, const float *qkv,
+                                  const float *lse, int B, int T, int C, int NH, cudaStream_t st) {
+  if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
+  FlashMaps maps, maps_kv;  // the two kernels step by different widths: different K-major boxes
+  int e = build_maps(&maps, qkv, dout, B, T, C, NH, Cfg<F_BWD_Q>::FC);
+  if (e) return e;
+  e = build_maps(&maps_kv, qkv, dout, B, T, C, NH, Cfg<F_BWD_KV>::FC);
+  if (e) return e;
+  FlashArgs a = {};
+  a.B = B; a.T = T; a.C = C; a.NH = NH;
+  a.lse = const_cast<float *>(lse); a.delta = delta; a.dqkv = dqkv;
+  a.status = flash_status_ptr();
+  a.wait_limit_ns = 2000000000LL;
+  if (!a.status) return GPT2L_ERR_CUDA;
+  e = launch<F_BWD_KV>(maps_kv, a, st);
+  if (e) return e;
+  return launch<F_BWD_Q>(maps, a, st);
+}
+
 }  // namespace g2l

@@ -41,7 +41,8 @@ bool attention_flash_supported(int T, int C, int NH);
 int attention_flash_forward(float *out, float *lse, const float *qkv, int B, int T, int C, int NH, cudaStream_t st);
 int attention_flash_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
                              const float *lse, int B, int T, int C, int NH, cudaStream_t st);
-
+int attention_flash_backward_core(float *dqkv, const float *delta, const float *dout, const float *qkv,
+                                  const float *lse, int B, int T, int C, int NH, cudaStream_t st);
 int attention_flash_status();
 
 }  // namespace g2l

@@ -324,11 +324,7 @@ __device__ __noinline__ bool attention_tile_mode(const GemmOp *op, int grb, int 
   a.out = ra.out0;
   a.lse = MODE == F_FWD ? ra.out1 : const_cast<float *>(ra.in2);
   a.delta = ra.in3;
-  // the dQ op of a step schedule carries the forward output: its tiles form delta themselves
-  const bool own_delta = MODE == F_BWD_Q && ra.in4 != nullptr;
-  a.dout = own_delta ? ra.in1 : nullptr;
-  a.out_fwd = own_delta ? ra.in4 : nullptr;
-  a.delta_out = own_delta ? const_cast<float *>(ra.in3) : nullptr;
+  a.dout = nullptr; a.out_fwd = nullptr; a.delta_out = nullptr;  // a ROWDOT op of the schedule has formed delta
   a.dqkv = ra.out0;
   a.status = nullptr;
   a.wait_limit_ns = p.wait_limit_ns;

@@ -384,18 +384,17 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     wgrads[l].push_back(b.emit(
         gemm_spec(GPT2L_OP_BACKWARD_WEIGHT, M, C, C, G + p.proj_w, G + p.proj_b, a.atty, m->dresid, nullptr, ow, l),
         {{m->dresid, WHOLE, false}, {a.atty, WHOLE, false}}, {{G + p.proj_w, WHOLE, false}}));
-    // dQ first: its tiles form delta = rowsum(d_atty o atty) for their own rows and leave it for the dK / dV pass
+    if (m->attn_flash) {  // the other attention implementations compute their row terms themselves
+      OpSpec s = row_spec(OPK_ROWDOT, M, BM, l);
+      s.ra.in0 = st->d_atty; s.ra.in1 = a.atty; s.ra.out0 = m->delta; s.ra.i0 = M; s.ra.i1 = C; s.ra.i2 = T; s.ra.i3 = NH;
+      b.emit(s, {{st->d_atty, ROW, false}, {a.atty, ROW, false}}, {{m->delta, ROW, false}});
+    }
     for (int pass = 0; pass < 2; ++pass) {
-      OpSpec s = row_spec(pass == 0 ? OPK_ATTN_BWD_Q : OPK_ATTN_BWD_KV, M, BM, l);
+      OpSpec s = row_spec(pass == 0 ? OPK_ATTN_BWD_KV : OPK_ATTN_BWD_Q, M, BM, l);
       s.rb_per_seq = rb_per_seq;
       s.ra.in0 = a.qkv; s.ra.in1 = st->d_atty; s.ra.in2 = a.lse; s.ra.in3 = m->delta; s.ra.out0 = st->dqkv;
-      s.ra.in4 = pass == 0 ? a.atty : nullptr;
       s.ra.i0 = B; s.ra.i1 = C; s.ra.i2 = T; s.ra.i3 = NH;
-      if (pass == 0)
-        b.emit(s, {{a.qkv, SEQ, false}, {st->d_atty, SEQ, false}, {a.atty, ROW, false}},
-               {{st->dqkv, ROW, false}, {m->delta, ROW, false}});
-      else
-        b.emit(s, {{a.qkv, SEQ, false}, {st->d_atty, SEQ, false}, {m->delta, SEQ, false}}, {{st->dqkv, ROW, true}});
+      b.emit(s, {{a.qkv, SEQ, false}, {st->d_atty, SEQ, false}, {m->delta, SEQ, false}}, {{st->dqkv, ROW, pass == 1}});
     }
     b.emit(gemm_spec(GPT2L_OP_BACKWARD_INPUT, M, C, 3 * C, st->d_ln, nullptr, st->dqkv, P + p.qkv_w, nullptr, o, l),
            {{st->dqkv, ROW, false}}, {{st->d_ln, ROW, false}});
@@ -447,7 +446,7 @@ gpt2l_step *gpt2_schedule_instructions(gpt2_model *m, const int *tokens, const i
     const int k = b.ops[i].kind;
     const bool attn = k >= OPK_ATTN_FWD && k <= OPK_ATTN_BWD_Q;
     if (attn && !in_kernel) {
-      if (k == OPK_ATTN_BWD_Q) continue;  // launched together with the key/value pass that follows it
+      if (k == OPK_ATTN_BWD_Q) continue;  // launched together with the key/value pass
       StepItem piece;
       piece.layer = (int)pieces.size() - 1;  // index into `pieces`, resolved below
       order.push_back(piece);
@@ -543,7 +542,7 @@ int gpt2_megakernel_step(gpt2l_step *s, float lr, float beta1, float beta2, floa
       else e = attention_forward(a.atty, a.lse, a.qkv, B, T, C, NH, st);
     } else {
       const LayerActs &a = m->la[it.layer];
-      if (m->attn_flash) e = attention_flash_backward(s->dqkv, m->delta, s->d_atty, a.atty, a.qkv, a.lse, B, T, C, NH, st);
+      if (m->attn_flash) e = attention_flash_backward_core(s->dqkv, m->delta, s->d_atty, a.qkv, a.lse, B, T, C, NH, st);
       else if (m->attn_gemm)
         e = attention_backward_gemm(s->dqkv, m->datt, m->delta, s->d_atty, a.atty, a.att, a.qkv, B, T, C, NH, m->mode, st);
       else e = attention_backward(s->dqkv, m->delta, s->d_atty, a.atty, a.qkv, a.lse, B, T, C, NH, st);
