@@ -124,23 +124,9 @@ int attention_flash_forward(float *out, float *lse, const float *qkv, int B, int
 int attention_flash_backward(float *dqkv, float *delta, const float *dout, const float *out, const float *qkv,
                              const float *lse, int B, int T, int C, int NH, cudaStream_t st) {
   if (!attention_flash_supported(T, C, NH)) return GPT2L_ERR_BAD_ARG;
-  // the dQ pass forms delta = rowsum(dout o out) for its own rows and leaves it for the dK / dV pass behind it
-  FlashMaps maps, maps_kv;  // the two kernels step by different widths: different K-major boxes
-  int e = build_maps(&maps, qkv, dout, B, T, C, NH, Cfg<F_BWD_Q>::FC);
+  int e = attention_row_dot(delta, dout, out, B, T, C, NH, st);
   if (e) return e;
-  e = build_maps(&maps_kv, qkv, dout, B, T, C, NH, Cfg<F_BWD_KV>::FC);
-  if (e) return e;
-  FlashArgs a = {};
-  a.B = B; a.T = T; a.C = C; a.NH = NH;
-  a.lse = const_cast<float *>(lse); a.delta = delta; a.dqkv = dqkv;
-  a.dout = dout; a.out_fwd = out; a.delta_out = delta;
-  a.status = flash_status_ptr();
-  a.wait_limit_ns = 2000000000LL;
-  if (!a.status) return GPT2L_ERR_CUDA;
-  e = launch<F_BWD_Q>(maps, a, st);
-  if (e) return e;
-  a.delta_out = nullptr;
-  return launch<F_BWD_KV>(maps_kv, a, st);
+  return attention_flash_backward_core(dqkv, delta, dout, qkv, lse, B, T, C, NH, st);
 }
 
 // the two backward kernels alone: delta[b][h][t] = rowsum(dout o out) has been computed by the caller

@@ -28,10 +28,6 @@ struct FlashArgs {
   float *out;          // FWD: [B*T][C]
   float *lse;          // [B][NH][T], base-2 log-sum-exp of the scaled scores
   const float *delta;  // [B][NH][T]
-  // BWD_Q, optional: with both set, the pass forms delta = rowsum(dout o out_fwd) for its own rows itself and
-  // leaves it in delta_out ([B][NH][T]) for the dK / dV pass that follows
-  const float *dout, *out_fwd;  // [B*T][C]
-  float *delta_out;
   float *dqkv;         // BWD: [B*T][3C]
   int *status;         // 0, or the site of a wait that gave up
   long long wait_limit_ns;
@@ -427,23 +423,7 @@ __device__ __forceinline__ void attn_tile_body(const FlashMaps &maps, const Flas
       // NCW warp sets share the rows: set k handles columns [HC k, HC k + HC) of every step and of dQ at the end
       constexpr int HC = FC / K::NCW;
       const float lse = a.lse[vbase + grow];
-      float dlt;
-      if (a.delta_out != nullptr) {
-        // this row's 64 output columns and their gradient: two 256-byte rows per thread, once per tile
-        const float *o_ = a.out_fwd + ((long long)b * a.T + grow) * a.C + h * FHS;
-        const float *d_ = a.dout + ((long long)b * a.T + grow) * a.C + h * FHS;
-        dlt = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < FHS; c += 4) {
-          const float4 x = __ldg(reinterpret_cast<const float4 *>(o_ + c));
-          const float4 y = __ldg(reinterpret_cast<const float4 *>(d_ + c));
-          dlt += x.x * y.x + x.y * y.y + x.z * y.z + x.w * y.w;
-        }
-        if (cset == 0) a.delta_out[vbase + grow] = dlt;
-      } else {
-        dlt = a.delta[vbase + grow];
-      }
-      const float dlt8 = dlt * 0.125f;
+      const float dlt8 = a.delta[vbase + grow] * 0.125f;
       for (int it = 0; it < n_it && ok; ++it) {
         ok = w_wait(smem_u32(&ctrl->s_full[(g0 + it) % K::NSB]), ((g0 + it) / K::NSB) & 1u, ctrl, a, 10, lane);
         if (!ok) break;

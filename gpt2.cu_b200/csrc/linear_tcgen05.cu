@@ -324,7 +324,6 @@ __device__ __noinline__ bool attention_tile_mode(const GemmOp *op, int grb, int 
   a.out = ra.out0;
   a.lse = MODE == F_FWD ? ra.out1 : const_cast<float *>(ra.in2);
   a.delta = ra.in3;
-  a.dout = nullptr; a.out_fwd = nullptr; a.delta_out = nullptr;  // a ROWDOT op of the schedule has formed delta
   a.dqkv = ra.out0;
   a.status = nullptr;
   a.wait_limit_ns = p.wait_limit_ns;
