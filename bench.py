@@ -217,9 +217,9 @@ def workload_config(args, rows=M_ROWS):
 # our arm
 # ------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over the
-# 15 launches of one step: the ncu capture of the half-size set (4096 rows: 252.2 MB per launch against
-# 244.2 MB algorithmic, 1.033x) carried to 8192 rows by that ratio (452.5 MB algorithmic per launch).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 467.0e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
+# 15 launches of one step: the ncu capture of the half-size set (4096 rows: 248.1 MB per launch against
+# 244.2 MB algorithmic, 1.016x) carried to 8192 rows by that ratio (452.5 MB algorithmic per launch).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 460.0e6  # profiles/tcgen05_kernel_gemm_set_launch_list_and_traffic.md
 
 
 def init_nccl(torch, dist, local_rank):
