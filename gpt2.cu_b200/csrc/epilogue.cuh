@@ -108,10 +108,6 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
   const int out_tile = m_tile * op->tiles_n + tc.n_tile;
   // one CTA of a pair may hold rows below the matrix: it waits and hands back like the other, and drains nothing
   const bool live = !PAIR || m_tile < op->tiles_m;
-  float *ws_tile = nullptr;
-  if (det_split && live)
-    ws_tile = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn) +
-              (size_t)(q * 32 + lane) * bn;
 
   bool tma_used = false;
   if (live && !det_split) {
@@ -205,19 +201,23 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
       dst[helper ? 1 : 0] = make_float2(st_m, st_s);
       if (n_epi == 1) dst[1] = make_float2(-INFINITY, 0.f);  // no helper twin in this launch / op
     }
-  } else if (live && !helper)  // fixed-order split-K: the quarter's own warp parks whole rows
-  for (int c = 0; c < bn / 32; ++c) {
-    const int nb = n0 + c * 32;
-    if (nb >= Nc) break;  // warp-uniform
-    uint32_t r[32];
-    tmem_ld_32x32(taddr + c * 32, r);
-    tmem_ld_wait();
-    {
-      float4 *dst = reinterpret_cast<float4 *>(ws_tile + c * 32);
+  } else if (live && !helper) {
+    // fixed-order split-K: the quarter's own warp parks its 32 rows of the partial tile in the workspace,
+    // through the staging box so that the stores are whole 128-byte lines (store_chunk)
+    float *ws_rows = op->ws + ((size_t)(tc.split * op->tiles_m * op->tiles_n + out_tile)) * (size_t)(BM * bn);
+    const EpiAux none;
+    AuxRegs ar;
+    uint32_t box = 0u;
+    for (int c = 0; c < bn / 32; ++c) {
+      const int nb = n0 + c * 32;
+      if (nb >= Nc) break;  // warp-uniform
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * 32, r);
+      tmem_ld_wait();
+      float v[32];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      store_chunk(v, (box++ & 1u) ? sbuf_alt : sbuf, ws_rows, bn, q * 32, c * 32, BM, bn, lane, false, none, ar);
     }
   }
   // the accumulator is in registers / memory now: hand the TMEM buffer back
@@ -243,35 +243,39 @@ __device__ __forceinline__ bool epilogue_tile(const GemmOp *op, const Tile &tc, 
       __threadfence();
       if (lane == 0) *sem = 0;  // ready for the next launch
       const size_t split_stride = (size_t)op->tiles_m * op->tiles_n * (size_t)(BM * bn);
-      const float *p0 = op->ws + (size_t)out_tile * (size_t)(BM * bn) + (size_t)(q * 32 + lane) * bn;
-      if (row < Mc) {
-        for (int c4 = 0; c4 < bn / 4; ++c4) {
-          const int col = n0 + c4 * 4;
-          if (col >= Nc) break;
-          // L2 reads: the partials were written by other SMs during this launch
-          float4 acc = __ldcg(reinterpret_cast<const float4 *>(p0 + c4 * 4));
+      // split 0's copy of this quarter's rows; a lane owns four columns, the warp walks the rows four at a time
+      // (whole lines in, whole lines out, 4 x splits loads in flight: read one row per thread, as the partials
+      // are drained, this took one L2 round trip per 16 bytes and 50 - 100 us per tile)
+      const float *t0 = op->ws + (size_t)out_tile * (size_t)(BM * bn) + (size_t)(q * 32) * bn;
+      const int row0q = m_tile * BM + q * 32;
+      for (int cb = 0; cb < bn; cb += 128) {
+        const int lc = cb + lane * 4;
+        const int col = n0 + lc;
+        if (lc >= bn || col >= Nc) continue;  // (Nc is a multiple of four: the four columns are inside together)
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (add_bias) bv = __ldg(reinterpret_cast<const float4 *>(op->bias + col));
+        for (int r = 0; r < 32; r += 4) {
+          float4 acc[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)  // L2 reads: the partials were written by other SMs during this launch
+            acc[i] = __ldcg(reinterpret_cast<const float4 *>(t0 + (size_t)(r + i) * bn + lc));
           for (int sp = 1; sp < op->splits; ++sp) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(p0 + sp * split_stride + c4 * 4));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            float4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              v[i] = __ldcg(reinterpret_cast<const float4 *>(t0 + sp * split_stride + (size_t)(r + i) * bn + lc));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { acc[i].x += v[i].x; acc[i].y += v[i].y; acc[i].z += v[i].z; acc[i].w += v[i].w; }
           }
-          float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-          float *dst = op->C + (long long)row * ldc + col;
-          if (col + 4 <= Nc) {
-            if (add_bias) {
-              const float4 bv = __ldg(reinterpret_cast<const float4 *>(op->bias + col));
-              vals[0] += bv.x; vals[1] += bv.y; vals[2] += bv.z; vals[3] += bv.w;
-            }
-            *reinterpret_cast<float4 *>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int grow = row0q + r + i;
+            if (grow >= Mc) continue;
+            const float4 o = make_float4(acc[i].x + bv.x, acc[i].y + bv.y, acc[i].z + bv.z, acc[i].w + bv.w);
+            *reinterpret_cast<float4 *>(op->C + (long long)grow * ldc + col) = o;
             if (dual)
-              *reinterpret_cast<float4 *>(op->C2 + (long long)row * ldc + col) =
-                  make_float4(gelu_tanh(vals[0]), gelu_tanh(vals[1]), gelu_tanh(vals[2]), gelu_tanh(vals[3]));
-          } else {
-            for (int j = 0; j < 4; ++j)
-              if (col + j < Nc) {
-                float v = vals[j] + (add_bias ? __ldg(op->bias + col + j) : 0.f);
-                dst[j] = v;
-                if (dual) op->C2[(long long)row * ldc + col + j] = gelu_tanh(v);
-              }
+              *reinterpret_cast<float4 *>(op->C2 + (long long)grow * ldc + col) =
+                  make_float4(gelu_tanh(o.x), gelu_tanh(o.y), gelu_tanh(o.z), gelu_tanh(o.w));
           }
         }
       }

@@ -187,7 +187,9 @@ def measure_train(g, dp, torch, local_rank, rank, world, barrier, dist, mode, B=
     if path == "step":
         if world != 1:
             raise SystemExit("the single-launch step includes AdamW: one rank only")
-        sched = g.Step(model, tok, tgt, with_update=True, attention_in_kernel=True)
+        # attention runs as tiles of the same launch where the fused tensor-core attention applies (T % 128 == 0);
+        # otherwise its kernels are launched between pieces of the schedule
+        sched = g.Step(model, tok, tgt, with_update=True, attention_in_kernel=(T % 128 == 0))
         info = sched.info()
 
         def one(t):
