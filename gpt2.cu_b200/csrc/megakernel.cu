@@ -109,6 +109,7 @@ int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
     g.xform = (g.op_kind == OPK_GEMM && (plan->any_3x || (g.colsum != nullptr && g.b_mn && !g.colsum_spread) || g.xent_mode >= 2)) ? 1 : 0;
   plan->arrivals = plan->pair ? NUM_EPI_WARPS : NUM_WORKER_WARPS;
   const unsigned A = (unsigned)plan->arrivals;
+  std::vector<char> waited_for(n_ops, 0);
   for (int i = 0; i < n_ops; ++i) {
     GemmOp &g = plan->ops[i];
     if ((int)specs[i].deps.size() > MAX_WAITS) return GPT2L_ERR_SCHEDULE;
@@ -116,6 +117,7 @@ int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
     for (const auto &dep : specs[i].deps) {
       if (dep.kind == GPT2L_DEP_NONE) continue;
       if (dep.producer < 0 || dep.producer >= i) return GPT2L_ERR_SCHEDULE;  // must point backwards
+      waited_for[dep.producer] = 1;
       const GemmOp &pr = plan->ops[dep.producer];
       // arrivals a complete 128-row block / the complete op shows
       unsigned per_block, whole;
@@ -153,6 +155,10 @@ int make_plan(const std::vector<OpSpec> &specs, int num_sms, Plan *plan) {
       ++w;
     }
   }
+  // an op nobody waits for publishes nothing: its tiles skip the fence, the wait for their stores to land and
+  // the counter updates (the launch's end makes its results visible)
+  for (int i = 0; i < n_ops; ++i)
+    if (!waited_for[i]) plan->ops[i].pub_rb_base = plan->ops[i].pub_op_ctr = -1;
   plan->total_tiles = tile_base;
   plan->n_counters = ctr;
   return GPT2L_OK;
@@ -216,7 +222,7 @@ int replay(const Plan &plan, int grid) {
           }
         }
         if (!ready) break;
-        for (int h = 0; h < n_rb; ++h) {
+        for (int h = 0; h < n_rb && g.pub_rb_base >= 0; ++h) {
           counters[g.pub_rb_base + rb0 + h] += A;
           counters[g.pub_op_ctr] += A;
         }
