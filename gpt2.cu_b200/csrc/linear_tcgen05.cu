@@ -809,9 +809,10 @@ static void choose_tiling(int Mc, int Nc, int kb_total, int num_sms, int forced_
       const int per = ceil_div(kb_total, s);
       if (forced_splits == 0 && s > 1 && (s - 1) * per >= kb_total) continue;  // an empty split
       const double waves = (double)ceil_div(tiles * s, num_sms);
-      // + 6 k-blocks of fixed per-tile overhead (pipeline fill, epilogue); splits pay an
-      // extra pass over the output
-      const double cost = waves * (per + 6.0 + (s > 1 ? 4.0 : 0.0)) * (double)(tile_rows + bn);
+      // + 6 k-blocks of fixed per-tile overhead (pipeline fill, epilogue); splits pay an extra pass over the
+      // output (two k-blocks' worth since the partials go out as reduce-adds of the copy engine; measured on the
+      // qkv weight gradient at M = 16384: 8 splits 153 us, 5 splits 163 us)
+      const double cost = waves * (per + 6.0 + (s > 1 ? 2.0 : 0.0)) * (double)(tile_rows + bn);
       if (cost < best - 1e-9) {
         best = cost;
         best_bn = bn;
